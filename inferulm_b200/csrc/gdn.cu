@@ -1,0 +1,265 @@
+// Gated-DeltaNet recurrence for chain (verify) spans and plain spans.
+//
+// Reference contract: `deltanet` of crates/wein-kernel/src/reference.rs:564-694
+// (device twin crates/wein-kernel/kernels/src/lib.rs:5231-5411).  Per (span,
+// v-head) the state S[v][k] (128x128) is loaded ONCE, kept in registers for all
+// tokens of the span, and written once per chain position (one snapshot row per
+// verify position) or once at the end (plain span).  The reference's chain path
+// re-reads the previous row from HBM for every token.
+//
+// Work split: every v-row of S evolves independently given k-hat, q-hat, beta
+// and decay, so a warp owns R rows; lane l holds the 4-wide k slice [4l, 4l+4)
+// of each of its rows.  The reference's reduction tree for kvm and o -- a
+// 4-term fused chain inside the slice, then a 32-term ascending fold over the
+// slices -- is reproduced exactly: the per-slice partials go through a padded
+// shared-memory transpose and lane r folds row r in slice order.  The state
+// moves between HBM and registers in fully coalesced 512 B (f32) / 256 B (bf16)
+// row segments; HBM traffic is (1 + positions) x 64 KiB per head in f32 mode.
+//
+// Bit parity with the reference holds in the bf16-pool mode (state rounded on
+// every store, as the reference's pool); the f32-pool mode keeps the same tree
+// without that rounding.  Compiled with -fmad=false.
+#include "common.cuh"
+
+struct GdnParams {
+    const bf16_t *q, *k, *v, *a, *b;   // per-token inputs
+    uint32_t q_stride, k_stride, v_stride, ab_stride;  // elements between consecutive tokens
+    const float *a_log;                // [v_heads]
+    const bf16_t *dt_bias;             // [v_heads]
+    void *state;                       // [rows, v_heads, 128, 128] bf16 or f32
+    bf16_t *out;                       // [tokens, v_heads*128]
+    const uint32_t *row_start, *row_count, *row_id, *specs, *out_base;
+    uint32_t n_rows, k_heads, v_heads;
+    float l2_eps;
+};
+
+template <bool F32>
+struct StateIO;
+template <>
+struct StateIO<true> {
+    static __device__ __forceinline__ void load(const void *p, size_t e, float s[4]) {
+        float4 v = *reinterpret_cast<const float4 *>((const float *)p + e);
+        s[0] = v.x; s[1] = v.y; s[2] = v.z; s[3] = v.w;
+    }
+    static __device__ __forceinline__ void store(void *p, size_t e, const float s[4]) {
+        *reinterpret_cast<float4 *>((float *)p + e) = make_float4(s[0], s[1], s[2], s[3]);
+    }
+};
+template <>
+struct StateIO<false> {
+    static __device__ __forceinline__ void load(const void *p, size_t e, float s[4]) {
+        uint2 v = *reinterpret_cast<const uint2 *>((const bf16_t *)p + e);
+        s[0] = __uint_as_float(v.x << 16); s[1] = __uint_as_float(v.x & 0xffff0000u);
+        s[2] = __uint_as_float(v.y << 16); s[3] = __uint_as_float(v.y & 0xffff0000u);
+    }
+    static __device__ __forceinline__ void store(void *p, size_t e, const float s[4]) {
+        uint2 v;  // values are already bf16-representable: narrowing is exact
+        v.x = (__float_as_uint(s[0]) >> 16) | (__float_as_uint(s[1]) & 0xffff0000u);
+        v.y = (__float_as_uint(s[2]) >> 16) | (__float_as_uint(s[3]) & 0xffff0000u);
+        *reinterpret_cast<uint2 *>((bf16_t *)p + e) = v;
+    }
+};
+
+template <int R, bool F32>
+__global__ void __launch_bounds__(128) gdn_kernel(const GdnParams P) {
+    constexpr int KD = 128, VD = 128, WARPS = 4;
+    constexpr int SLABS = VD / (WARPS * R);
+    __shared__ float T[WARPS][R][33];
+    const unsigned full = 0xffffffffu;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    uint32_t unit = blockIdx.x / SLABS, slab = blockIdx.x % SLABS;
+    uint32_t r = unit / P.v_heads, h = unit % P.v_heads;
+    if (r >= P.n_rows) return;
+    const uint32_t t0 = P.row_start[r], cnt = P.row_count[r];
+    if (cnt == 0) return;
+    const uint32_t spec = P.specs ? P.specs[r] : 1u;
+    const size_t in_row = P.row_id[r];
+    // snapshot i goes to row base+i (chain span); a plain span writes only its own row at the end
+    const size_t base = P.out_base ? P.out_base[r] : (spec ? in_row + 1 : in_row);
+    const uint32_t kh = h * P.k_heads / P.v_heads;
+    const uint32_t row0 = slab * (WARPS * R) + w * R;
+    const size_t head_elems = (size_t)VD * KD, row_elems = (size_t)P.v_heads * head_elems;
+
+    // the one HBM read of the state: issue all loads first, latency is hidden behind the norms below
+    float S[R][4];
+    {
+        size_t e0 = in_row * row_elems + (size_t)h * head_elems + (size_t)row0 * KD + lane * 4;
+#pragma unroll
+        for (int i = 0; i < R; i++) StateIO<F32>::load(P.state, e0 + (size_t)i * KD, S[i]);
+    }
+    const float big_a = expf_ref(P.a_log[h]);
+    const float dtb = bf2f(P.dt_bias[h]);
+    const float kd_sqrt = sqrtf((float)KD);
+
+    for (uint32_t tb = 0; tb < cnt; tb += 16) {
+        // l2 norms of q and k for up to 16 tokens: lane 2i sums q of token tb+i, lane 2i+1 sums k, j ascending,
+        // s = x*x + s as two roundings (reference.rs:629-637)
+        float inv_mine = 0.0f;
+        {
+            uint32_t ti = tb + (lane >> 1);
+            if (ti < cnt) {
+                const bf16_t *src = (lane & 1) ? P.k + (size_t)(t0 + ti) * P.k_stride + kh * KD
+                                               : P.q + (size_t)(t0 + ti) * P.q_stride + kh * KD;
+                float s = 0.0f;
+                for (int j = 0; j < KD; j += 8) {
+                    uint4 vv = *reinterpret_cast<const uint4 *>(src + j);
+                    uint32_t wv[4] = {vv.x, vv.y, vv.z, vv.w};
+#pragma unroll
+                    for (int u = 0; u < 4; u++) {
+                        float x0 = __uint_as_float(wv[u] << 16), x1 = __uint_as_float(wv[u] & 0xffff0000u);
+                        s = __fadd_rn(__fmul_rn(x0, x0), s);
+                        s = __fadd_rn(__fmul_rn(x1, x1), s);
+                    }
+                }
+                inv_mine = __fdiv_rn(1.0f, sqrtf(__fadd_rn(s, P.l2_eps)));
+            }
+        }
+        uint32_t tend = min(cnt, tb + 16);
+        for (uint32_t i = tb; i < tend; i++) {
+            const size_t g = t0 + i;
+            const float invq = __shfl_sync(full, inv_mine, (int)(2 * (i - tb)));
+            const float invk = __shfl_sync(full, inv_mine, (int)(2 * (i - tb) + 1));
+            // gates (reference.rs:624-626): decay = exp(-A * softplus(a + dt_bias)); beta = bf16(sigmoid(b))
+            const float av = bf2f(P.a[g * P.ab_stride + h]), bv = bf2f(P.b[g * P.ab_stride + h]);
+            const float decay = expf_ref(__fsub_rn(0.0f, __fmul_rn(big_a, softplus_ref(__fadd_rn(av, dtb)))));
+            const float beta = rbf(sigmoid_ref(bv));
+            float kk[4], qq[4];
+            {
+                uint2 kv = *reinterpret_cast<const uint2 *>(P.k + g * P.k_stride + kh * KD + lane * 4);
+                uint2 qv = *reinterpret_cast<const uint2 *>(P.q + g * P.q_stride + kh * KD + lane * 4);
+                kk[0] = __fmul_rn(__uint_as_float(kv.x << 16), invk); kk[1] = __fmul_rn(__uint_as_float(kv.x & 0xffff0000u), invk);
+                kk[2] = __fmul_rn(__uint_as_float(kv.y << 16), invk); kk[3] = __fmul_rn(__uint_as_float(kv.y & 0xffff0000u), invk);
+                qq[0] = __fdiv_rn(__fmul_rn(__uint_as_float(qv.x << 16), invq), kd_sqrt);
+                qq[1] = __fdiv_rn(__fmul_rn(__uint_as_float(qv.x & 0xffff0000u), invq), kd_sqrt);
+                qq[2] = __fdiv_rn(__fmul_rn(__uint_as_float(qv.y << 16), invq), kd_sqrt);
+                qq[3] = __fdiv_rn(__fmul_rn(__uint_as_float(qv.y & 0xffff0000u), invq), kd_sqrt);
+            }
+            float vin = 0.0f;
+            if (lane < R) vin = bf2f(P.v[g * P.v_stride + h * VD + row0 + lane]);
+            // decay, then kvm partial of this lane's slice for each row
+#pragma unroll
+            for (int rr = 0; rr < R; rr++) {
+                float p = 0.0f;
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    S[rr][u] = __fmul_rn(S[rr][u], decay);
+                    p = fmaf(S[rr][u], kk[u], p);
+                }
+                T[w][rr][lane] = p;
+            }
+            __syncwarp();
+            float delta = 0.0f;
+            if (lane < R) {
+                float kvm = 0.0f;
+#pragma unroll 8
+                for (int sl = 0; sl < 32; sl++) kvm = __fadd_rn(T[w][lane][sl], kvm);
+                delta = __fmul_rn(__fsub_rn(vin, kvm), beta);
+            }
+            __syncwarp();
+            // rank-1 update S += k-hat (x) delta (rounded to bf16 in the bf16 pool mode), then o partials
+#pragma unroll
+            for (int rr = 0; rr < R; rr++) {
+                float d = __shfl_sync(full, delta, rr);
+                float p = 0.0f;
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    float s = fmaf(kk[u], d, S[rr][u]);
+                    if (!F32) s = rbf(s);
+                    S[rr][u] = s;
+                    p = fmaf(s, qq[u], p);
+                }
+                T[w][rr][lane] = p;
+            }
+            __syncwarp();
+            if (lane < R) {
+                float o = 0.0f;
+#pragma unroll 8
+                for (int sl = 0; sl < 32; sl++) o = __fadd_rn(T[w][lane][sl], o);
+                P.out[g * ((size_t)P.v_heads * VD) + h * VD + row0 + lane] = f2bf(o);
+            }
+            __syncwarp();
+            if (spec) {
+                size_t e0 = (base + i) * row_elems + (size_t)h * head_elems + (size_t)row0 * KD + lane * 4;
+#pragma unroll
+                for (int rr = 0; rr < R; rr++) StateIO<F32>::store(P.state, e0 + (size_t)rr * KD, S[rr]);
+            }
+        }
+    }
+    if (!spec) {
+        size_t e0 = base * row_elems + (size_t)h * head_elems + (size_t)row0 * KD + lane * 4;
+#pragma unroll
+        for (int rr = 0; rr < R; rr++) StateIO<F32>::store(P.state, e0 + (size_t)rr * KD, S[rr]);
+    }
+}
+
+template <int R>
+static void launch_gdn(const GdnParams &p, bool f32, cudaStream_t st) {
+    unsigned grid = p.n_rows * p.v_heads * (128 / (4 * R));
+    if (f32) gdn_kernel<R, true><<<grid, 128, 0, st>>>(p);
+    else gdn_kernel<R, false><<<grid, 128, 0, st>>>(p);
+}
+
+static int32_t gdn_dispatch(GdnParams &p, uint32_t k_dim, uint32_t v_dim, bool f32, uint32_t rows_per_warp, cudaStream_t st) {
+    if (k_dim != 128 || v_dim != 128) {
+        wb_set_error("deltanet: built for k_dim = v_dim = 128, got %u x %u", k_dim, v_dim);
+        return WB_ERR_SHAPE;
+    }
+    WB_CHECK_ARG(p.q && p.k && p.v && p.a && p.b && p.a_log && p.dt_bias && p.state && p.out && p.row_start && p.row_count && p.row_id,
+                 "deltanet: null pointer");
+    WB_CHECK_ARG(p.k_heads > 0 && p.v_heads > 0 && p.v_heads % p.k_heads == 0, "deltanet: v_heads %u must be a multiple of k_heads %u", p.v_heads, p.k_heads);
+    WB_CHECK_ARG(((p.q_stride | p.k_stride) & 7u) == 0 && ((((uintptr_t)p.q) | ((uintptr_t)p.k)) & 15u) == 0,
+                 "deltanet: q/k rows must be 16-byte aligned");
+    if (p.n_rows == 0) return WB_OK;
+    uint32_t R = rows_per_warp;
+    if (R == 0) {  // enough warps to cover the SMs a few times over, else the fewest (less replicated gate / norm work)
+        uint64_t units = (uint64_t)p.n_rows * p.v_heads;
+        R = units * 4 >= 4096 ? 32 : (units * 8 >= 2048 ? 16 : 8);
+    }
+    if (R == 32) launch_gdn<32>(p, f32, st);
+    else if (R == 16) launch_gdn<16>(p, f32, st);
+    else if (R == 8) launch_gdn<8>(p, f32, st);
+    else { wb_set_error("deltanet: rows_per_warp must be 0, 8, 16 or 32"); return WB_ERR_ARG; }
+    WB_LAUNCH_CHECK();
+    return WB_OK;
+}
+
+extern "C" {
+
+// Same argument order as DeltanetOp::run (crates/wein-kernel/src/ops/mod.rs:888-919); the state pool is bf16.
+int32_t wein_b200_deltanet(const void *q, const void *k, const void *v, const void *a, const void *b, const void *a_log,
+                           const void *dt_bias, void *state, void *core_out, const void *row_start, const void *row_count,
+                           const void *row_id, uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, uint32_t k_dim,
+                           uint32_t v_dim, uint32_t tokens, float l2_eps, const void *specs, uint32_t vsplit, void *stream) {
+    (void)tokens;
+    WB_CHECK_ARG(specs != nullptr, "deltanet: specs is required");
+    GdnParams p{};
+    p.q = (const bf16_t *)q; p.k = (const bf16_t *)k; p.v = (const bf16_t *)v; p.a = (const bf16_t *)a; p.b = (const bf16_t *)b;
+    p.q_stride = p.k_stride = k_heads * k_dim; p.v_stride = v_heads * v_dim; p.ab_stride = v_heads;
+    p.a_log = (const float *)a_log; p.dt_bias = (const bf16_t *)dt_bias; p.state = state; p.out = (bf16_t *)core_out;
+    p.row_start = (const uint32_t *)row_start; p.row_count = (const uint32_t *)row_count; p.row_id = (const uint32_t *)row_id;
+    p.specs = (const uint32_t *)specs; p.out_base = nullptr;
+    p.n_rows = n_rows; p.k_heads = k_heads; p.v_heads = v_heads; p.l2_eps = l2_eps;
+    // vsplit is the caller's upper bound on v-row splitting (1 = never split): 1 -> 32 rows per warp
+    uint32_t R = vsplit <= 1 ? 32 : (vsplit <= 2 ? 16 : 8);
+    return gdn_dispatch(p, k_dim, v_dim, false, R, (cudaStream_t)stream);
+}
+
+// Chain-shaped entry: explicit strides (q/k/v may live inside the conv output, a/b inside the projection
+// output), explicit input row and snapshot base per span, bf16 or f32 state pool.
+int32_t wein_b200_gdn_verify(const void *q, const void *k, const void *v, uint32_t q_stride, uint32_t k_stride, uint32_t v_stride,
+                             const void *a, const void *b, uint32_t ab_stride, const void *a_log, const void *dt_bias,
+                             void *state, uint32_t state_f32, void *core_out, const void *row_start, const void *row_count,
+                             const void *in_row, const void *out_base, const void *specs, uint32_t n_rows, uint32_t k_heads,
+                             uint32_t v_heads, uint32_t k_dim, uint32_t v_dim, float l2_eps, uint32_t rows_per_warp, void *stream) {
+    GdnParams p{};
+    p.q = (const bf16_t *)q; p.k = (const bf16_t *)k; p.v = (const bf16_t *)v; p.a = (const bf16_t *)a; p.b = (const bf16_t *)b;
+    p.q_stride = q_stride; p.k_stride = k_stride; p.v_stride = v_stride; p.ab_stride = ab_stride;
+    p.a_log = (const float *)a_log; p.dt_bias = (const bf16_t *)dt_bias; p.state = state; p.out = (bf16_t *)core_out;
+    p.row_start = (const uint32_t *)row_start; p.row_count = (const uint32_t *)row_count; p.row_id = (const uint32_t *)in_row;
+    p.specs = (const uint32_t *)specs; p.out_base = (const uint32_t *)out_base;
+    p.n_rows = n_rows; p.k_heads = k_heads; p.v_heads = v_heads; p.l2_eps = l2_eps;
+    WB_CHECK_ARG(out_base != nullptr, "gdn_verify: out_base is required");
+    return gdn_dispatch(p, k_dim, v_dim, state_f32 != 0, rows_per_warp, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -1,0 +1,116 @@
+"""Operator-level mirror of the reference's Op traits over the C-ABI.
+
+One function per trait of crates/wein-kernel/src/ops/mod.rs that lies on the
+MTP draft -> verify -> accept path, same argument order and meaning; tensors
+are torch CUDA tensors used only as device buffers (bf16 data travels as
+int16 / bf16 storage, u32 tables as int32).  Every call forwards raw device
+pointers, sizes and the current CUDA stream to libwein_b200.so.
+"""
+import ctypes as C
+
+import torch
+
+from .lib import check, load
+
+U32, U64, F32, VP = C.c_uint32, C.c_uint64, C.c_float, C.c_void_p
+
+
+def _ptr(t):
+    if t is None:
+        return VP(0)
+    assert t.is_cuda and t.is_contiguous(), "operators take contiguous CUDA tensors"
+    return VP(t.data_ptr())
+
+
+def _stream():
+    return VP(torch.cuda.current_stream().cuda_stream)
+
+
+def embed(ids, w, out, hidden, tokens):
+    check(load().wein_b200_embed(_ptr(ids), _ptr(w), _ptr(out), U32(hidden), U32(tokens), _stream()))
+
+
+def rms_norm_zc(x, w, out, rows, hidden, eps):
+    check(load().wein_b200_rms_norm_zc(_ptr(x), _ptr(w), _ptr(out), U32(rows), U32(hidden), F32(eps), _stream()))
+
+
+def add_norm_zc(a, b, w, sum_out, norm_out, rows, hidden, eps):
+    check(load().wein_b200_add_norm_zc(_ptr(a), _ptr(b), _ptr(w), _ptr(sum_out), _ptr(norm_out), U32(rows), U32(hidden),
+                                       F32(eps), _stream()))
+
+
+def rms_norm_gated(x, z, w, out, rows, hidden, eps):
+    check(load().wein_b200_rms_norm_gated(_ptr(x), _ptr(z), _ptr(w), _ptr(out), U32(rows), U32(hidden), F32(eps), _stream()))
+
+
+def rope_pt(x, cos, sin, pos, out, rot_dim, head_dim, heads, tokens):
+    check(load().wein_b200_rope_pt(_ptr(x), _ptr(cos), _ptr(sin), _ptr(pos), _ptr(out), U32(rot_dim), U32(head_dim),
+                                   U32(heads), U32(tokens), _stream()))
+
+
+def add(a, b, out, n):
+    check(load().wein_b200_add(_ptr(a), _ptr(b), _ptr(out), U64(n), _stream()))
+
+
+def mul(a, b, out, n):
+    check(load().wein_b200_mul(_ptr(a), _ptr(b), _ptr(out), U64(n), _stream()))
+
+
+def silu(x, out, n):
+    check(load().wein_b200_silu(_ptr(x), _ptr(out), U64(n), _stream()))
+
+
+def silu_mul(g, u, out, n):
+    check(load().wein_b200_silu_mul(_ptr(g), _ptr(u), _ptr(out), U64(n), _stream()))
+
+
+def sigmul(x, g, out, n):
+    check(load().wein_b200_sigmul(_ptr(x), _ptr(g), _ptr(out), U64(n), _stream()))
+
+
+def kv_scatter(src_k, src_v, block_table, seq_ids, positions, k_dst, v_dst, bpr, block_size, head_elems, tokens, f32=False):
+    fn = load().wein_b200_kv_scatter_f32 if f32 else load().wein_b200_kv_scatter
+    check(fn(_ptr(src_k), _ptr(src_v), _ptr(block_table), _ptr(seq_ids), _ptr(positions), _ptr(k_dst), _ptr(v_dst),
+             U32(bpr), U32(block_size), U32(head_elems), U32(tokens), _stream()))
+
+
+def conv1d_dw(x, w, state_in, out, tok_row, tok_pos, conv_dim, kernel, tokens):
+    check(load().wein_b200_conv1d_dw(_ptr(x), _ptr(w), _ptr(state_in), _ptr(out), _ptr(tok_row), _ptr(tok_pos),
+                                     U32(conv_dim), U32(kernel), U32(tokens), _stream()))
+
+
+def conv_state_roll(x, state, row_start, row_count, row_id, conv_dim, kernel, n_rows, specs):
+    check(load().wein_b200_conv_state_roll(_ptr(x), _ptr(state), _ptr(row_start), _ptr(row_count), _ptr(row_id),
+                                           U32(conv_dim), U32(kernel), U32(n_rows), _ptr(specs), _stream()))
+
+
+def conv_verify(x, x_stride, w, state, out, row_start, row_count, in_row, out_base, conv_dim, kernel, n_rows):
+    check(load().wein_b200_conv_verify(_ptr(x), U32(x_stride), _ptr(w), _ptr(state), _ptr(out), _ptr(row_start),
+                                       _ptr(row_count), _ptr(in_row), _ptr(out_base), U32(conv_dim), U32(kernel),
+                                       U32(n_rows), _stream()))
+
+
+def deltanet(q, k, v, a, b, a_log, dt_bias, state, core_out, row_start, row_count, row_id, n_rows, k_heads, v_heads,
+             k_dim, v_dim, tokens, l2_eps, specs, vsplit):
+    check(load().wein_b200_deltanet(_ptr(q), _ptr(k), _ptr(v), _ptr(a), _ptr(b), _ptr(a_log), _ptr(dt_bias), _ptr(state),
+                                    _ptr(core_out), _ptr(row_start), _ptr(row_count), _ptr(row_id), U32(n_rows),
+                                    U32(k_heads), U32(v_heads), U32(k_dim), U32(v_dim), U32(tokens), F32(l2_eps),
+                                    _ptr(specs), U32(vsplit), _stream()))
+
+
+def gdn_verify(q, k, v, q_stride, k_stride, v_stride, a, b, ab_stride, a_log, dt_bias, state, state_f32, core_out,
+               row_start, row_count, in_row, out_base, specs, n_rows, k_heads, v_heads, k_dim, v_dim, l2_eps,
+               rows_per_warp=0):
+    check(load().wein_b200_gdn_verify(_ptr(q), _ptr(k), _ptr(v), U32(q_stride), U32(k_stride), U32(v_stride), _ptr(a),
+                                      _ptr(b), U32(ab_stride), _ptr(a_log), _ptr(dt_bias), _ptr(state), U32(state_f32),
+                                      _ptr(core_out), _ptr(row_start), _ptr(row_count), _ptr(in_row), _ptr(out_base),
+                                      _ptr(specs), U32(n_rows), U32(k_heads), U32(v_heads), U32(k_dim), U32(v_dim),
+                                      F32(l2_eps), U32(rows_per_warp), _stream()))
+
+
+ARGMAX_SPLIT = 32
+
+
+def argmax_rows(x, rows, scratch, out, n, s):
+    """scratch: at least s * ARGMAX_SPLIT int64 words."""
+    check(load().wein_b200_argmax_rows(_ptr(x), _ptr(rows), _ptr(scratch), _ptr(out), U32(n), U32(s), _stream()))
