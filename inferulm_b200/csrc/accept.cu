@@ -1,0 +1,404 @@
+// Device-side acceptance for MTP speculative decoding.
+//
+// Greedy: the reference accepts on the host after a device argmax, a stream sync and a readback
+// (crates/wein-exec/src/qwen.rs:3676-3702 and :2433-2460): accept while drafts[a] == target[a], then emit the
+// bonus token target[a].  Here the same rule runs on the device, so the step needs no host round trip.
+// Token ids and accept lengths are bit-identical to the reference rule given identical logits (the argmax
+// keeps the reference's total order: value descending, index ascending).
+//
+// Sampled: the reference has no speculative sampling (its chains are forced greedy, qwen.rs:2610-2615).  The
+// kernels below follow the filter of the reference's plain sampler (reference.rs:787-877: scale by 1/temp,
+// top-k <= 64 in the total order, softmax numerators by the reference exp, top-p cut on the running sum) to
+// turn a logits row into a compact distribution of at most 64 (id, probability) pairs, and then apply
+// standard rejection sampling (accept draft x iff u*q(x) < p(x); on the first rejection redraw from
+// max(p-q, 0) renormalised; after k acceptances draw the bonus token from the last row) with Philox4x32-10
+// uniforms keyed by (seed, round, position), so a replayed CUDA graph needs no RNG state on the host.
+// Every floating-point step is written in the oracle's order: results are bit-identical to oracle/.
+// Compiled with -fmad=false.
+#include "common.cuh"
+
+#define DIST_CAP 64
+
+// ---------------------------------------------------------------- Philox4x32-10
+__device__ __forceinline__ void philox4x32_10(uint32_t c0, uint32_t c1, uint32_t c2, uint32_t c3, uint32_t k0, uint32_t k1, uint32_t out[4]) {
+#pragma unroll
+    for (int r = 0; r < 10; r++) {
+        uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+        uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+        uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+        c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+        k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+    }
+    out[0] = c0; out[1] = c1; out[2] = c2; out[3] = c3;
+}
+// uniforms of (sequence seed, round, chain position, stream): lane 0 picks from a distribution, lane 1 is the accept test
+__device__ __forceinline__ void spec_uniforms(uint64_t seed, uint64_t round, uint32_t position, uint32_t stream, float u[4]) {
+    uint32_t o[4];
+    philox4x32_10((uint32_t)round, (uint32_t)(round >> 32), position, stream, (uint32_t)seed, (uint32_t)(seed >> 32), o);
+#pragma unroll
+    for (int i = 0; i < 4; i++) u[i] = __fmul_rn((float)(o[i] >> 8), 1.0f / 16777216.0f);
+}
+__device__ __forceinline__ int pick_from(const float *probs, int n, float u) {
+    float acc = 0.0f;
+    for (int j = 0; j < n; j++) { acc = __fadd_rn(probs[j], acc); if (u < acc) return j; }
+    return n - 1;
+}
+
+// ---------------------------------------------------------------- top-k / top-p filter
+// 16-bit key whose unsigned order is the bf16 value order; -0 folds onto +0 (they compare equal in the reference)
+__device__ __forceinline__ uint32_t ord_key(uint32_t h) {
+    h &= 0xffffu;
+    if (h == 0x8000u) h = 0;
+    return (h & 0x8000u) ? (~h & 0xffffu) : (h | 0x8000u);
+}
+__device__ __forceinline__ bf16_t key_to_bf16(uint32_t key) { return (bf16_t)((key & 0x8000u) ? (key & 0x7fffu) : (~key & 0xffffu)); }
+
+struct FilterParams {
+    const bf16_t *x;           // [*, n] logits
+    const uint32_t *rows;      // [s] logits row of each output row (null: identity)
+    const uint32_t *row_seq;   // [s] sequence (parameter slot) of each row (null: row / rows_per_seq)
+    uint32_t rows_per_seq;
+    const float *temp, *top_p; // per sequence
+    const uint32_t *top_k;
+    uint32_t n, s;
+    uint32_t *out_ids;         // [s, 64]
+    float *out_probs;          // [s, 64]
+    uint32_t *out_n;           // [s]
+    // optional: draw a token from each row's distribution (draft sampling)
+    uint32_t *sample_out;      // [s] or null
+    const uint64_t *seed, *round;  // per sequence
+    uint32_t position;
+};
+
+// Applies fn(key, index) to every element of the row, 8 elements per 16-byte load when aligned.
+template <typename F>
+__device__ __forceinline__ void scan_row(const bf16_t *row, uint32_t n, F fn) {
+    if ((((uintptr_t)row) & 15u) == 0) {
+        uint32_t nv = n / 8;
+        for (uint32_t v = threadIdx.x; v < nv; v += blockDim.x) {
+            uint4 q = *reinterpret_cast<const uint4 *>(row + (size_t)v * 8);
+            uint32_t wv[4] = {q.x, q.y, q.z, q.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) { fn(ord_key(wv[j]), v * 8 + 2 * j); fn(ord_key(wv[j] >> 16), v * 8 + 2 * j + 1); }
+        }
+        for (uint32_t i = nv * 8 + threadIdx.x; i < n; i += blockDim.x) fn(ord_key(row[i]), i);
+    } else {
+        for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) fn(ord_key(row[i]), i);
+    }
+}
+
+// One CTA of 1024 threads per row.
+__global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P) {
+    __shared__ uint32_t lm[1024];
+    __shared__ uint32_t hist[256];
+    __shared__ uint32_t warp_cnt[32];
+    __shared__ uint32_t sh[8];        // 0: bound key, 1: bin hi, 2: k left inside bin, 3: tau, 4: need, 5: count_eq, 6: list length, 7: ties emitted
+    __shared__ uint32_t cand_key[DIST_CAP], cand_idx[DIST_CAP];
+    __shared__ uint32_t srt_idx[DIST_CAP];
+    __shared__ float srt_v[DIST_CAP], e_s[DIST_CAP];
+    const uint32_t r = blockIdx.x, tid = threadIdx.x;
+    const uint32_t seq = P.row_seq ? P.row_seq[r] : r / P.rows_per_seq;
+    const bf16_t *row = P.x + (size_t)(P.rows ? P.rows[r] : r) * P.n;
+    const float temp = P.temp[seq];
+    const bool greedy = !(temp > 0.0f);
+    uint32_t k = greedy ? 1u : min(P.top_k[seq], (uint32_t)DIST_CAP);
+    uint32_t *ids = P.out_ids + (size_t)r * DIST_CAP;
+    float *probs = P.out_probs + (size_t)r * DIST_CAP;
+    if (k == 0 || P.n == 0) {  // top_k = 0 (whole vocabulary) is not supported on the device: in-band error, as the reference
+        if (tid < DIST_CAP) { ids[tid] = 0xffffffffu; probs[tid] = 0.0f; }
+        if (tid == 0) { P.out_n[r] = 0; if (P.sample_out) P.sample_out[r] = 0xffffffffu; }
+        return;
+    }
+    if (k > P.n) k = P.n;
+    // pass 1: a lower bound of the k-th largest key = the k-th largest of the per-thread maxima
+    uint32_t best = 0;
+    scan_row(row, P.n, [&](uint32_t key, uint32_t) { best = max(best, key); });
+    lm[tid] = best;
+    if (tid < 256) hist[tid] = 0;
+    if (tid < 8) sh[tid] = 0;
+    __syncthreads();
+    {
+        uint32_t rank = 0;
+        for (uint32_t u = 0; u < 1024; u++) { uint32_t o = lm[u]; rank += (o > best) || (o == best && u < tid); }
+        if (rank == k - 1) sh[0] = best;
+    }
+    __syncthreads();
+    const uint32_t bound = sh[0];
+    // pass 2: histogram of the high byte over the survivors; find the byte holding the k-th largest
+    scan_row(row, P.n, [&](uint32_t key, uint32_t) { if (key >= bound) atomicAdd(&hist[key >> 8], 1u); });
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t above = 0;
+        int b = 255;
+        for (; b > 0; b--) { if (above + hist[b] >= k) break; above += hist[b]; }
+        sh[1] = (uint32_t)b; sh[2] = k - above;
+    }
+    __syncthreads();
+    const uint32_t bhi = sh[1], kin = sh[2];
+    if (tid < 256) hist[tid] = 0;
+    __syncthreads();
+    // pass 3: low byte inside that bin -> the exact threshold key tau
+    scan_row(row, P.n, [&](uint32_t key, uint32_t) { if ((key >> 8) == bhi && key >= bound) atomicAdd(&hist[key & 255u], 1u); });
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t above = 0;
+        int b = 255;
+        for (; b > 0; b--) { if (above + hist[b] >= kin) break; above += hist[b]; }
+        sh[3] = (bhi << 8) | (uint32_t)b;
+        sh[4] = kin - above;   // ties at tau still to take (lowest indices first)
+        sh[5] = hist[b];       // ties at tau in the row
+    }
+    __syncthreads();
+    const uint32_t tau = sh[3], need = sh[4], count_eq = sh[5];
+    const bool all_ties = count_eq == need;
+    // pass 4: everything above tau, plus the ties when all of them are wanted
+    scan_row(row, P.n, [&](uint32_t key, uint32_t i) {
+        if (key > tau || (all_ties && key == tau)) { uint32_t slot = atomicAdd(&sh[6], 1u); if (slot < DIST_CAP) { cand_key[slot] = key; cand_idx[slot] = i; } }
+    });
+    __syncthreads();
+    if (!all_ties) {
+        // ordered scan for the `need` lowest-index ties, 1024 consecutive indices per round
+        const uint32_t lane = tid & 31, wid = tid >> 5;
+        for (uint32_t base = 0; base < P.n; base += 1024) {
+            uint32_t i = base + tid;
+            bool hit = i < P.n && ord_key(row[i]) == tau;
+            uint32_t bal = __ballot_sync(0xffffffffu, hit);
+            if (lane == 0) warp_cnt[wid] = __popc(bal);
+            __syncthreads();
+            uint32_t before = sh[7];
+            for (uint32_t w2 = 0; w2 < wid; w2++) before += warp_cnt[w2];
+            uint32_t my = before + __popc(bal & ((1u << lane) - 1u));
+            if (hit && my < need) { uint32_t slot = (k - need) + my; cand_key[slot] = tau; cand_idx[slot] = i; }
+            __syncthreads();
+            if (tid == 0) { uint32_t tot = 0; for (int w2 = 0; w2 < 32; w2++) tot += warp_cnt[w2]; sh[7] += tot; }
+            __syncthreads();
+            if (sh[7] >= need) break;
+        }
+    }
+    __syncthreads();
+    // sort the k candidates: value descending, index ascending
+    const float inv_t = greedy ? 1.0f : __fdiv_rn(1.0f, temp);
+    if (tid < k) {
+        uint32_t mk = cand_key[tid], mi = cand_idx[tid], rank = 0;
+        for (uint32_t u = 0; u < k; u++) rank += (cand_key[u] > mk) || (cand_key[u] == mk && cand_idx[u] < mi);
+        srt_idx[rank] = mi;
+        srt_v[rank] = __fmul_rn(bf2f(key_to_bf16(mk)), inv_t);
+    }
+    __syncthreads();
+    if (tid < k) e_s[tid] = expf_ref(__fsub_rn(srt_v[tid], srt_v[0]));
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t keep = 1;
+        if (!greedy) {
+            float pp = P.top_p[seq];
+            pp = (pp > 0.0f && pp < 1.0f) ? pp : 1.0f;
+            float denom = 0.0f;
+            for (uint32_t j = 0; j < k; j++) denom = __fadd_rn(e_s[j], denom);
+            float cacc = 0.0f;
+            for (uint32_t j = 0; j < k; j++) {
+                cacc = __fadd_rn(__fdiv_rn(e_s[j], denom), cacc);
+                keep = j + 1;
+                if (cacc >= pp) break;
+            }
+        }
+        float z = 0.0f;
+        for (uint32_t j = 0; j < keep; j++) z = __fadd_rn(e_s[j], z);
+        for (uint32_t j = 0; j < keep; j++) e_s[j] = __fdiv_rn(e_s[j], z);
+        sh[6] = keep;
+        P.out_n[r] = keep;
+        if (P.sample_out) {
+            uint32_t tok = srt_idx[0];
+            if (!greedy) {
+                float u[4];
+                spec_uniforms(P.seed[seq], P.round[seq], P.position, 0, u);
+                tok = srt_idx[pick_from(e_s, (int)keep, u[0])];
+            }
+            P.sample_out[r] = tok;
+        }
+    }
+    __syncthreads();
+    if (tid < DIST_CAP) {
+        bool live = tid < sh[6];
+        ids[tid] = live ? srt_idx[tid] : 0xffffffffu;
+        probs[tid] = live ? e_s[tid] : 0.0f;
+    }
+}
+
+// ---------------------------------------------------------------- acceptance
+struct AcceptParams {
+    // greedy inputs: per verify row argmax partials [rows][split] (keys of the argmax kernel) -- or null
+    const uint64_t *am_part;
+    uint32_t am_split;
+    // sampled inputs: compact distributions of the verify rows [B*(k+1)] and of the draft rows [B*k] (draft row = b*k + j)
+    const uint32_t *p_ids, *q_ids, *p_n, *q_n;
+    const float *p_probs, *q_probs;
+    const float *temp;              // per sequence; null or <= 0: greedy rule
+    const uint64_t *seed, *round;   // per sequence
+    const uint32_t *drafts;         // [B, k]
+    const uint32_t *n_drafts;       // [B] or null (= k)
+    uint32_t B, k;
+    uint32_t *accept_len;           // [B]
+    uint32_t *out_tokens;           // [B, k+1] emitted tokens, 0xffffffff beyond accept_len + 1
+    uint32_t *target;               // [B, k+1] greedy targets (optional)
+};
+
+__device__ __forceinline__ uint32_t argmax_from_parts(const uint64_t *part, uint32_t split, int lane) {
+    uint64_t best = 0ull;
+    for (uint32_t i = lane; i < split; i += 32) { uint64_t o = part[i]; best = o > best ? o : best; }
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) { uint64_t o = __shfl_xor_sync(0xffffffffu, best, off); best = o > best ? o : best; }
+    return best == 0ull ? 0xffffffffu : ~(uint32_t)best;
+}
+
+// One warp per sequence.
+__global__ void __launch_bounds__(32) accept_kernel(const AcceptParams P) {
+    __shared__ float r_s[DIST_CAP];
+    const uint32_t b = blockIdx.x, lane = threadIdx.x;
+    const uint32_t k = P.k, rows = k + 1;
+    const uint32_t nd = P.n_drafts ? min(P.n_drafts[b], k) : k;
+    uint32_t *out = P.out_tokens + (size_t)b * rows;
+    const bool greedy = !P.temp || !(P.temp[b] > 0.0f);
+    if (greedy) {
+        // target token of each row: from the argmax partials, or entry 0 of the row's compact distribution
+        uint32_t a = 0;
+        bool open = true;
+        uint32_t emitted = 0xffffffffu;
+        for (uint32_t j = 0; j <= nd; j++) {
+            uint32_t t = P.am_part ? argmax_from_parts(P.am_part + ((size_t)b * rows + j) * P.am_split, P.am_split, lane)
+                                   : P.p_ids[((size_t)b * rows + j) * DIST_CAP];
+            if (P.target && lane == 0) P.target[(size_t)b * rows + j] = t;
+            if (open) {
+                if (j < nd && P.drafts[(size_t)b * k + j] == t) { a = j + 1; if (lane == 0) out[j] = t; }
+                else { open = false; emitted = t; if (lane == 0) out[j] = t; }
+            }
+        }
+        (void)emitted;
+        if (lane == 0) {
+            for (uint32_t j = a + 1; j < rows; j++) out[j] = 0xffffffffu;
+            P.accept_len[b] = a;
+        }
+        return;
+    }
+    const uint64_t seed = P.seed[b], round = P.round[b];
+    uint32_t a = 0;
+    for (; a < nd; a++) {
+        const uint32_t *pi = P.p_ids + ((size_t)b * rows + a) * DIST_CAP, *qi = P.q_ids + ((size_t)b * k + a) * DIST_CAP;
+        const float *pp = P.p_probs + ((size_t)b * rows + a) * DIST_CAP, *qp = P.q_probs + ((size_t)b * k + a) * DIST_CAP;
+        const uint32_t pn = P.p_n[(size_t)b * rows + a], qn = P.q_n[(size_t)b * k + a];
+        const uint32_t x = P.drafts[(size_t)b * k + a];
+        float u[4];
+        spec_uniforms(seed, round, a, 1, u);
+        // p(x), q(x): at most one match per list
+        float px = 0.0f, qx = 0.0f;
+        for (uint32_t j = lane; j < DIST_CAP; j += 32) {
+            if (j < pn && pi[j] == x) px = pp[j];
+            if (j < qn && qi[j] == x) qx = qp[j];
+        }
+#pragma unroll
+        for (int off = 16; off >= 1; off >>= 1) { px += __shfl_xor_sync(0xffffffffu, px, off); qx += __shfl_xor_sync(0xffffffffu, qx, off); }
+        if (__fmul_rn(u[1], qx) < px) { if (lane == 0) out[a] = x; continue; }
+        // rejected: residual max(p - q, 0) in target order
+        for (uint32_t j = lane; j < DIST_CAP; j += 32) {
+            float rj = 0.0f;
+            if (j < pn) {
+                float qj = 0.0f;
+                uint32_t id = pi[j];
+                for (uint32_t t = 0; t < qn; t++) if (qi[t] == id) qj = qp[t];
+                float d = __fsub_rn(pp[j], qj);
+                rj = d > 0.0f ? d : 0.0f;
+            }
+            r_s[j] = rj;
+        }
+        __syncwarp();
+        if (lane == 0) {
+            float z = 0.0f;
+            for (uint32_t j = 0; j < pn; j++) z = __fadd_rn(r_s[j], z);
+            uint32_t tok;
+            if (!(z > 0.0f)) tok = pi[0];
+            else {
+                for (uint32_t j = 0; j < pn; j++) r_s[j] = __fdiv_rn(r_s[j], z);
+                tok = pi[pick_from(r_s, (int)pn, u[0])];
+            }
+            out[a] = tok;
+            for (uint32_t j = a + 1; j < rows; j++) out[j] = 0xffffffffu;
+            P.accept_len[b] = a;
+        }
+        return;
+    }
+    if (lane == 0) {
+        float u[4];
+        spec_uniforms(seed, round, nd, 1, u);
+        const uint32_t *pi = P.p_ids + ((size_t)b * rows + nd) * DIST_CAP;
+        const float *pp = P.p_probs + ((size_t)b * rows + nd) * DIST_CAP;
+        out[nd] = pi[pick_from(pp, (int)P.p_n[(size_t)b * rows + nd], u[0])];
+        for (uint32_t j = nd + 1; j < rows; j++) out[j] = 0xffffffffu;
+        P.accept_len[b] = nd;
+    }
+}
+
+// argmax phase 1 lives in ops_exact.cu
+int32_t wein_b200_argmax_partials(const void *x, const void *rows, void *part, uint32_t n, uint32_t s, uint32_t split, cudaStream_t st);
+
+int32_t wb_topk_filter(const FilterParams &p, cudaStream_t st) {
+    WB_CHECK_ARG(p.x && p.temp && p.top_k && p.top_p && p.out_ids && p.out_probs && p.out_n, "topk_filter: null pointer");
+    WB_CHECK_ARG(p.row_seq || p.rows_per_seq > 0, "topk_filter: rows_per_seq must be positive");
+    WB_CHECK_ARG(!p.sample_out || (p.seed && p.round), "topk_filter: sampling needs seed and round");
+    if (p.s == 0) return WB_OK;
+    topk_filter_kernel<<<p.s, 1024, 0, st>>>(p);
+    WB_LAUNCH_CHECK();
+    return WB_OK;
+}
+int32_t wb_accept(const AcceptParams &p, cudaStream_t st) {
+    WB_CHECK_ARG(p.drafts && p.accept_len && p.out_tokens, "accept: null pointer");
+    WB_CHECK_ARG(p.am_part || p.p_ids, "accept: needs argmax partials or target distributions");
+    WB_CHECK_ARG(!p.temp || (p.p_ids && p.p_probs && p.p_n && p.q_ids && p.q_probs && p.q_n && p.seed && p.round),
+                 "accept: sampled mode needs both distributions, seeds and rounds");
+    WB_CHECK_ARG(p.k >= 1 && p.k <= 15, "accept: k = %u outside 1..15", p.k);
+    if (p.B == 0) return WB_OK;
+    accept_kernel<<<p.B, 32, 0, st>>>(p);
+    WB_LAUNCH_CHECK();
+    return WB_OK;
+}
+
+extern "C" {
+
+int32_t wein_b200_topk_filter(const void *logits, const void *rows, const void *row_seq, uint32_t rows_per_seq, const void *temp,
+                              const void *top_k, const void *top_p, uint32_t n, uint32_t s, void *out_ids, void *out_probs,
+                              void *out_n, void *sample_out, const void *seed, const void *round, uint32_t position, void *stream) {
+    FilterParams p{};
+    p.x = (const bf16_t *)logits; p.rows = (const uint32_t *)rows; p.row_seq = (const uint32_t *)row_seq; p.rows_per_seq = rows_per_seq;
+    p.temp = (const float *)temp; p.top_k = (const uint32_t *)top_k; p.top_p = (const float *)top_p; p.n = n; p.s = s;
+    p.out_ids = (uint32_t *)out_ids; p.out_probs = (float *)out_probs; p.out_n = (uint32_t *)out_n;
+    p.sample_out = (uint32_t *)sample_out; p.seed = (const uint64_t *)seed; p.round = (const uint64_t *)round; p.position = position;
+    return wb_topk_filter(p, (cudaStream_t)stream);
+}
+
+// Greedy acceptance straight from logits: argmax of the B*(k+1) verify rows (row b*(k+1)+j of `rows`), then the
+// longest-prefix rule.  scratch: B*(k+1)*32 u64 words.
+int32_t wein_b200_accept_greedy(const void *logits, const void *rows, const void *drafts, const void *n_drafts, uint32_t n,
+                                uint32_t B, uint32_t k, void *scratch, void *accept_len, void *out_tokens, void *target, void *stream) {
+    WB_CHECK_ARG(logits && rows && scratch, "accept_greedy: null pointer");
+    int32_t rc = wein_b200_argmax_partials(logits, rows, scratch, n, B * (k + 1), 32, (cudaStream_t)stream);
+    if (rc != WB_OK) return rc;
+    AcceptParams p{};
+    p.am_part = (const uint64_t *)scratch; p.am_split = 32;
+    p.drafts = (const uint32_t *)drafts; p.n_drafts = (const uint32_t *)n_drafts; p.B = B; p.k = k;
+    p.accept_len = (uint32_t *)accept_len; p.out_tokens = (uint32_t *)out_tokens; p.target = (uint32_t *)target;
+    return wb_accept(p, (cudaStream_t)stream);
+}
+
+// Rejection-sampling acceptance from compact distributions (rows with temp <= 0 use the greedy rule on entry 0).
+int32_t wein_b200_accept_sampled(const void *drafts, const void *n_drafts, const void *p_ids, const void *p_probs, const void *p_n,
+                                 const void *q_ids, const void *q_probs, const void *q_n, const void *temp, const void *seed,
+                                 const void *round, uint32_t B, uint32_t k, void *accept_len, void *out_tokens, void *stream) {
+    WB_CHECK_ARG(temp != nullptr, "accept_sampled: temp is required");
+    AcceptParams p{};
+    p.p_ids = (const uint32_t *)p_ids; p.p_probs = (const float *)p_probs; p.p_n = (const uint32_t *)p_n;
+    p.q_ids = (const uint32_t *)q_ids; p.q_probs = (const float *)q_probs; p.q_n = (const uint32_t *)q_n;
+    p.temp = (const float *)temp; p.seed = (const uint64_t *)seed; p.round = (const uint64_t *)round;
+    p.drafts = (const uint32_t *)drafts; p.n_drafts = (const uint32_t *)n_drafts; p.B = B; p.k = k;
+    p.accept_len = (uint32_t *)accept_len; p.out_tokens = (uint32_t *)out_tokens;
+    return wb_accept(p, (cudaStream_t)stream);
+}
+
+}  // extern "C"

@@ -445,7 +445,21 @@ int32_t wein_b200_conv_verify(const void *x, uint32_t x_stride, const void *w, v
     return WB_OK;
 }
 
-// scratch: s * WEIN_B200_ARGMAX_SPLIT u64 words
+}  // extern "C"
+
+// phase 1 only (the accept kernel merges the slices itself)
+int32_t wein_b200_argmax_partials(const void *x, const void *rows, void *part, uint32_t n, uint32_t s, uint32_t split, cudaStream_t st) {
+    WB_CHECK_ARG(x && rows && part && split > 0, "argmax: null pointer");
+    if (s == 0) return WB_OK;
+    dim3 grid(split, s);
+    argmax_p1_kernel<<<grid, 256, 0, st>>>((const bf16_t *)x, (const uint32_t *)rows, (uint64_t *)part, n, split);
+    WB_LAUNCH_CHECK();
+    return WB_OK;
+}
+
+extern "C" {
+
+// scratch: s * 32 u64 words
 int32_t wein_b200_argmax_rows(const void *x, const void *rows, void *scratch, void *out, uint32_t n, uint32_t s, void *stream) {
     WB_CHECK_ARG(x && rows && scratch && out, "argmax_rows: null pointer");
     if (s == 0) return WB_OK;

@@ -114,3 +114,62 @@ ARGMAX_SPLIT = 32
 def argmax_rows(x, rows, scratch, out, n, s):
     """scratch: at least s * ARGMAX_SPLIT int64 words."""
     check(load().wein_b200_argmax_rows(_ptr(x), _ptr(rows), _ptr(scratch), _ptr(out), U32(n), U32(s), _stream()))
+
+
+def paged_attn(q, k_cache, v_cache, block_table, seq_ids, positions, out, q_scale, bpr, block_size, q_heads, kv_heads,
+               head_dim, tokens, scratch):
+    """PagedAttnOp::run plus the scratch buffer the reference's op object owns (attn_scratch_bytes(tokens, kv_heads,
+    head_dim, 16))."""
+    sb = scratch.numel() * scratch.element_size()
+    check(load().wein_b200_paged_attn(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(seq_ids),
+                                      _ptr(positions), _ptr(out), F32(q_scale), U32(bpr), U32(block_size), U32(q_heads),
+                                      U32(kv_heads), U32(head_dim), U32(tokens), _ptr(scratch), U64(sb), _stream()))
+
+
+def attn_scratch_bytes(n_spans, kv_heads, head_dim, max_segs):
+    fn = load().wein_b200_attn_scratch_bytes
+    fn.restype = U64
+    return int(fn(U32(n_spans), U32(kv_heads), U32(head_dim), U32(max_segs)))
+
+
+def attn_verify(q, k_cache, v_cache, block_table, seq_ids, positions, row_start, row_count, gate, out, q_scale, bpr,
+                block_size, q_heads, kv_heads, head_dim, n_spans, max_count, max_ctx, seg_pages, scratch):
+    sb = scratch.numel() * scratch.element_size()
+    check(load().wein_b200_attn_verify(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(seq_ids),
+                                       _ptr(positions), _ptr(row_start), _ptr(row_count), _ptr(gate), _ptr(out),
+                                       F32(q_scale), U32(bpr), U32(block_size), U32(q_heads), U32(kv_heads),
+                                       U32(head_dim), U32(n_spans), U32(max_count), U32(max_ctx), U32(seg_pages),
+                                       _ptr(scratch), U64(sb), _stream()))
+
+
+def gemm_scratch_bytes(n_max):
+    fn = load().wein_b200_gemm_scratch_bytes
+    fn.restype = U64
+    return int(fn(U32(n_max)))
+
+
+def gemm_wt(a, w, c, m, n, k, scratch=None):
+    """C[m,n] = A[m,k] W[n,k]^T.  scratch (zero-initialised once, gemm_scratch_bytes) enables split-k."""
+    sb = scratch.numel() * scratch.element_size() if scratch is not None else 0
+    check(load().wein_b200_gemm_wt(_ptr(a), _ptr(w), _ptr(c), U32(m), U32(n), U32(k), _ptr(scratch), U64(sb), _stream()))
+
+
+DIST_CAP = 64
+
+
+def topk_filter(logits, rows, row_seq, rows_per_seq, temp, top_k, top_p, n, s, out_ids, out_probs, out_n, sample_out=None,
+                seed=None, rnd=None, position=0):
+    check(load().wein_b200_topk_filter(_ptr(logits), _ptr(rows), _ptr(row_seq), U32(rows_per_seq), _ptr(temp), _ptr(top_k),
+                                       _ptr(top_p), U32(n), U32(s), _ptr(out_ids), _ptr(out_probs), _ptr(out_n),
+                                       _ptr(sample_out), _ptr(seed), _ptr(rnd), U32(position), _stream()))
+
+
+def accept_greedy(logits, rows, drafts, n_drafts, n, B, k, scratch, accept_len, out_tokens, target=None):
+    check(load().wein_b200_accept_greedy(_ptr(logits), _ptr(rows), _ptr(drafts), _ptr(n_drafts), U32(n), U32(B), U32(k),
+                                         _ptr(scratch), _ptr(accept_len), _ptr(out_tokens), _ptr(target), _stream()))
+
+
+def accept_sampled(drafts, n_drafts, p_ids, p_probs, p_n, q_ids, q_probs, q_n, temp, seed, rnd, B, k, accept_len, out_tokens):
+    check(load().wein_b200_accept_sampled(_ptr(drafts), _ptr(n_drafts), _ptr(p_ids), _ptr(p_probs), _ptr(p_n), _ptr(q_ids),
+                                          _ptr(q_probs), _ptr(q_n), _ptr(temp), _ptr(seed), _ptr(rnd), U32(B), U32(k),
+                                          _ptr(accept_len), _ptr(out_tokens), _stream()))
