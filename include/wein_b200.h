@@ -1,0 +1,243 @@
+/*
+ * wein_b200.h -- C-ABI of libwein_b200.so: hand-written sm_100a kernels for wein's MTP speculative-decoding
+ * hot path (draft k tokens with the MTP head -> verify k+1 positions in one forward -> accept on the device).
+ *
+ * Conventions
+ *  - Every pointer is a DEVICE pointer unless its name starts with `host_`.  bf16 tensors are raw 16-bit
+ *    words; index tables are uint32; nothing here is a torch / framework type.
+ *  - `stream` is a CUstream / cudaStream_t passed as void*.  Every entry is stream-ordered, allocation-free
+ *    after engine creation and safe to record into a CUDA graph unless stated otherwise.
+ *  - Return value: 0 = ok, < 0 = rejected before any launch (see the WEIN_B200_ERR_* codes);
+ *    wein_b200_last_error() returns the message of the calling thread's last failure.  Kernels never trap;
+ *    in-band error values are documented per entry.
+ *  - "reference" below is the wein source tree; each entry names the interface it stands in for.
+ */
+#ifndef WEIN_B200_H
+#define WEIN_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define WEIN_B200_OK 0
+#define WEIN_B200_ERR_ARG (-1)
+#define WEIN_B200_ERR_SHAPE (-2)
+#define WEIN_B200_ERR_CUDA (-3)
+#define WEIN_B200_ERR_CAPACITY (-4)
+
+const char *wein_b200_last_error(void);
+uint32_t wein_b200_abi_version(void);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Operator level: one entry per Op trait of crates/wein-kernel/src/ops/mod.rs on the path, same argument
+ * order (DevBuf -> pointer, &Stream -> stream).
+ * ---------------------------------------------------------------------------------------------------- */
+
+/* EmbedOp::run (ops/mod.rs:286-307): out[t,:] = w[ids[t],:] */
+int32_t wein_b200_embed(const void *ids, const void *w, void *out, uint32_t hidden, uint32_t tokens, void *stream);
+
+/* RmsNormZcOp::run (ops/mod.rs:376-515): out = x * rsqrt(mean(x^2)+eps) * (1+w); in place allowed */
+int32_t wein_b200_rms_norm_zc(const void *x, const void *w, void *out, uint32_t rows, uint32_t hidden, float eps, void *stream);
+
+/* AddNormZcOp::run (ops/mod.rs:376-515, kernel kernels/src/lib.rs:4674): sum_out = bf16(a+b); norm_out = norm_zc(sum_out) */
+int32_t wein_b200_add_norm_zc(const void *a, const void *b, const void *w, void *sum_out, void *norm_out, uint32_t rows,
+                              uint32_t hidden, float eps, void *stream);
+
+/* RmsNormGatedOp::run (ops/mod.rs:1308-1327): norm(x) * w_f32 * silu(z), rows of `hidden` */
+int32_t wein_b200_rms_norm_gated(const void *x, const void *z, const void *w, void *out, uint32_t rows, uint32_t hidden,
+                                 float eps, void *stream);
+
+/* RopePtOp::run (ops/mod.rs:657-702): partial rotary on the first rot_dim dims; cos/sin f32 tables [max_pos, rot_dim/2] */
+int32_t wein_b200_rope_pt(const void *x, const void *cosv, const void *sinv, const void *pos, void *out, uint32_t rot_dim,
+                          uint32_t head_dim, uint32_t heads, uint32_t tokens, void *stream);
+
+/* AddOp / MulOp / SiluOp / SiluMulOp / SigmulOp (ops/mod.rs:286-372, :705-725) */
+int32_t wein_b200_add(const void *a, const void *b, void *out, uint64_t n, void *stream);
+int32_t wein_b200_mul(const void *a, const void *b, void *out, uint64_t n, void *stream);
+int32_t wein_b200_silu(const void *x, void *out, uint64_t n, void *stream);
+int32_t wein_b200_silu_mul(const void *g, const void *u, void *out, uint64_t n, void *stream);
+int32_t wein_b200_sigmul(const void *x, const void *g, void *out, uint64_t n, void *stream);
+
+/* KvScatterOp::run / run_f32 (ops/mod.rs:1588-1680) */
+int32_t wein_b200_kv_scatter(const void *src_k, const void *src_v, const void *block_table, const void *seq_ids,
+                             const void *positions, void *k_dst, void *v_dst, uint32_t bpr, uint32_t block_size,
+                             uint32_t head_elems, uint32_t tokens, void *stream);
+int32_t wein_b200_kv_scatter_f32(const void *src_k, const void *src_v, const void *block_table, const void *seq_ids,
+                                 const void *positions, void *k_dst, void *v_dst, uint32_t bpr, uint32_t block_size,
+                                 uint32_t head_elems, uint32_t tokens, void *stream);
+
+/* Conv1dDwOp::run (ops/mod.rs:727-741) and ConvStateRollOp::run (ops/mod.rs:827-843, per-span `specs`) */
+int32_t wein_b200_conv1d_dw(const void *x, const void *w, const void *state_in, void *out, const void *tok_row,
+                            const void *tok_pos, uint32_t conv_dim, uint32_t kernel, uint32_t tokens, void *stream);
+int32_t wein_b200_conv_state_roll(const void *x, void *state, const void *row_start, const void *row_count, const void *row_id,
+                                  uint32_t conv_dim, uint32_t kernel, uint32_t n_rows, const void *specs, void *stream);
+/* Both of the above in one launch for chain spans: span r reads state row in_row[r] and writes the window after its
+ * token t to row out_base[r]+t (the reference contract is out_base = in_row + 1).  x rows are x_stride elements apart. */
+int32_t wein_b200_conv_verify(const void *x, uint32_t x_stride, const void *w, void *state, void *out, const void *row_start,
+                              const void *row_count, const void *in_row, const void *out_base, uint32_t conv_dim,
+                              uint32_t kernel, uint32_t n_rows, void *stream);
+
+/* DeltanetOp::run (ops/mod.rs:888-919), bf16 state pool [rows, v_heads, 128, 128]; k_dim = v_dim = 128 only
+ * (WEIN_B200_ERR_SHAPE otherwise).  The l2-norm pre-kernel of the reference is folded in. */
+int32_t wein_b200_deltanet(const void *q, const void *k, const void *v, const void *a, const void *b, const void *a_log,
+                           const void *dt_bias, void *state, void *core_out, const void *row_start, const void *row_count,
+                           const void *row_id, uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, uint32_t k_dim,
+                           uint32_t v_dim, uint32_t tokens, float l2_eps, const void *specs, uint32_t vsplit, void *stream);
+/* The verify-shaped form: the state of each (span, head) is read once, advanced on chip over the span's tokens and
+ * written once per position.  q/k/v/a/b are read in place with the given token strides (elements); span r reads row
+ * in_row[r] and writes the state after token t to row out_base[r]+t (specs[r] != 0 or specs == NULL) or only the final
+ * state to row out_base[r] (specs[r] == 0).  state_f32: pool element type (0 = bf16 rounded on every store, the
+ * reference's pool; 1 = f32).  rows_per_warp: 0 (auto), 8, 16 or 32; it never changes a result bit. */
+int32_t wein_b200_gdn_verify(const void *q, const void *k, const void *v, uint32_t q_stride, uint32_t k_stride, uint32_t v_stride,
+                             const void *a, const void *b, uint32_t ab_stride, const void *a_log, const void *dt_bias,
+                             void *state, uint32_t state_f32, void *core_out, const void *row_start, const void *row_count,
+                             const void *in_row, const void *out_base, const void *specs, uint32_t n_rows, uint32_t k_heads,
+                             uint32_t v_heads, uint32_t k_dim, uint32_t v_dim, float l2_eps, uint32_t rows_per_warp, void *stream);
+
+/* PagedAttnOp::run (ops/mod.rs:1687-1704) plus the scratch buffer that the reference's op object owns privately
+ * (wein_b200_attn_scratch_bytes(tokens, kv_heads, head_dim, 16) bytes).  16-token pages; head_dim 64 / 128 / 256. */
+uint64_t wein_b200_attn_scratch_bytes(uint32_t n_spans, uint32_t kv_heads, uint32_t head_dim, uint32_t max_segs);
+int32_t wein_b200_paged_attn(const void *q, const void *k_cache, const void *v_cache, const void *block_table, const void *seq_ids,
+                             const void *positions, void *out, float q_scale, uint32_t bpr, uint32_t block_size, uint32_t q_heads,
+                             uint32_t kv_heads, uint32_t head_dim, uint32_t tokens, void *scratch, uint64_t scratch_bytes, void *stream);
+/* Verify attention (stands in for Qwen35Executor::attn_long on chain rows, crates/wein-exec/src/qwen.rs:1134-1422): span r =
+ * rows row_start[r] .. +row_count[r] of one sequence at consecutive positions (<= 32 / group rows).  max_ctx bounds
+ * position+1 over the call (sizes the grid only); seg_pages = pages per context segment (fixes the summation order: keep it
+ * constant between runs that must agree bit for bit); gate (optional) applies out = sigmul(attn, gate).
+ * scratch >= wein_b200_attn_scratch_bytes(n_spans, kv_heads, head_dim, ceil(ceil(max_ctx/16)/seg_pages)). */
+int32_t wein_b200_attn_verify(const void *q, const void *k_cache, const void *v_cache, const void *block_table, const void *seq_ids,
+                              const void *positions, const void *row_start, const void *row_count, const void *gate, void *out,
+                              float q_scale, uint32_t bpr, uint32_t block_size, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
+                              uint32_t n_spans, uint32_t max_count, uint32_t max_ctx, uint32_t seg_pages, void *scratch,
+                              uint64_t scratch_bytes, void *stream);
+
+/* GemmOp::run_wt (ops/mod.rs:3378-3449): C[m,n] = A[m,k] W[n,k]^T, bf16, f32 accumulate.  m <= 32 runs the hand-written
+ * weight-streaming kernel (result of a row independent of the other rows), larger m goes to cuBLASLt like the reference.
+ * scratch (optional, zero-filled once by the caller, wein_b200_gemm_scratch_bytes(n) bytes) enables split-k for narrow n. */
+uint64_t wein_b200_gemm_scratch_bytes(uint32_t n_max);
+int32_t wein_b200_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, void *scratch,
+                          uint64_t scratch_bytes, void *stream);
+
+/* ArgmaxRowsOp::run (ops/mod.rs:1332-1367): total order (value desc, index asc); scratch = s*32 u64 words;
+ * a row with no comparable element yields 0xFFFFFFFF, as the reference. */
+int32_t wein_b200_argmax_rows(const void *x, const void *rows, void *scratch, void *out, uint32_t n, uint32_t s, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Acceptance (stands in for Qwen35Executor::spec_finish, crates/wein-exec/src/qwen.rs:2419-2502, which runs on the
+ * host after a sync and a readback in the reference).
+ * ---------------------------------------------------------------------------------------------------- */
+
+/* Greedy: argmax of the B*(k+1) verify rows rows[b*(k+1)+j] of `logits` [*, n], then accept while drafts[b][a] == target[b][a];
+ * out_tokens[b] = accepted drafts followed by the bonus token target[b][a], padded with 0xFFFFFFFF.  n_drafts (optional)
+ * gives per-sequence draft counts <= k.  scratch = B*(k+1)*32 u64 words.  target (optional) receives the argmax tokens. */
+int32_t wein_b200_accept_greedy(const void *logits, const void *rows, const void *drafts, const void *n_drafts, uint32_t n,
+                                uint32_t B, uint32_t k, void *scratch, void *accept_len, void *out_tokens, void *target, void *stream);
+
+/* Temperature / top-k (<= 64) / top-p filter of one logits row into a compact distribution: out_ids / out_probs [s, 64],
+ * out_n [s].  The filter follows SampleRowsOp (ops/mod.rs:1374-1441, reference.rs:787-877); probabilities are renormalised
+ * over the kept entries.  Row r uses the parameters of sequence row_seq[r] (or r / rows_per_seq).  temp <= 0 yields the
+ * one-hot argmax; top_k == 0 yields out_n = 0 and ids 0xFFFFFFFF (in-band error, as the reference sampler).  If sample_out
+ * is given, a token is drawn from each row's distribution with Philox4x32-10 uniforms keyed by (seed, round, position). */
+int32_t wein_b200_topk_filter(const void *logits, const void *rows, const void *row_seq, uint32_t rows_per_seq, const void *temp,
+                              const void *top_k, const void *top_p, uint32_t n, uint32_t s, void *out_ids, void *out_probs,
+                              void *out_n, void *sample_out, const void *seed, const void *round, uint32_t position, void *stream);
+
+/* Rejection sampling over compact distributions: p_* of the B*(k+1) verify rows, q_* of the B*k draft rows ([B][k]).
+ * Sequences with temp <= 0 follow the greedy rule on entry 0 of their rows.  No counterpart in the reference. */
+int32_t wein_b200_accept_sampled(const void *drafts, const void *n_drafts, const void *p_ids, const void *p_probs, const void *p_n,
+                                 const void *q_ids, const void *q_probs, const void *q_n, const void *temp, const void *seed,
+                                 const void *round, uint32_t B, uint32_t k, void *accept_len, void *out_tokens, void *stream);
+
+/* ------------------------------------------------------------------------------------------------------
+ * Step level: the speculative step of Qwen35Executor (crates/wein-exec/src/qwen.rs:5225-5654: spec_draft_batch ->
+ * forward_batch_mixed -> spec_finish) with every per-round decision on the device, so that one round is a single
+ * CUDA-graph replay with no host synchronisation.
+ * ---------------------------------------------------------------------------------------------------- */
+
+#define WEIN_B200_MAX_LAYERS 64
+
+typedef struct {
+    /* Qwen35Config (crates/wein-model/src/config.rs:17-46) */
+    uint32_t hidden, n_layers, q_heads, kv_heads, head_dim, rot_dim, inter, vocab;
+    uint32_t lin_k_heads, lin_v_heads, lin_k_dim, lin_v_dim, conv_kernel;
+    float rms_eps, l2_eps;
+    double rope_theta;
+    uint8_t layer_is_full[WEIN_B200_MAX_LAYERS];
+    uint32_t has_mtp;
+    /* capacity (CtxConfig of crates/wein-exec/src/ctx.rs) */
+    uint32_t max_seqs;       /* sequence slots */
+    uint32_t k_max;          /* most drafts per round (<= 7); chains and prefill chunks hold k_max+1 rows */
+    uint32_t max_pos;        /* positions per sequence (block-table rows hold ceil(max_pos/16) pages) */
+    uint32_t n_pages;        /* 16-token pages per KV pool */
+    uint32_t state_f32;      /* recurrent state pool: 1 = f32, 0 = bf16 (the reference's pool) */
+    uint32_t attn_seg_pages; /* pages per attention segment (0 = default 4) */
+} wein_b200_model_cfg;
+
+/* Weights stay caller-owned device memory for the life of the engine (bf16 unless noted; layouts as the safetensors
+ * tensors the reference uploads, crates/wein-exec/src/qwen.rs:1483-1579).  When the projection matrices of a layer are
+ * adjacent in memory in the order qkv|z|a|b, qg|k|v and wg|wu, the engine multiplies them in one launch each. */
+typedef struct {
+    const void *ln1, *ln2;            /* [hidden] */
+    const void *wg, *wu, *wd;         /* [inter,hidden] x2, [hidden,inter] */
+    /* full-attention layer */
+    const void *qg, *k, *v;           /* [2*q_heads*head_dim, hidden] (per head q then gate), [kv_heads*head_dim, hidden] x2 */
+    const void *qn, *kn, *o;          /* [head_dim] x2, [hidden, q_heads*head_dim] */
+    /* gated-DeltaNet layer */
+    const void *qkv, *z, *a, *b;      /* [2*kh*kd+vh*vd, hidden], [vh*vd, hidden], [vh, hidden] x2 */
+    const void *conv;                 /* [conv_dim, conv_kernel] */
+    const void *a_log;                /* f32 [vh] */
+    const void *dt_bias;              /* [vh] */
+    const void *norm;                 /* f32 [vd] */
+    const void *out;                  /* [hidden, vh*vd] */
+} wein_b200_layer_weights;
+
+typedef struct {
+    const void *embed;                /* [vocab, hidden], tied lm_head */
+    const void *norm_f;               /* [hidden] */
+    wein_b200_layer_weights layers[WEIN_B200_MAX_LAYERS];
+    /* MTP head (crates/wein-exec/src/qwen.rs:1537-1579): pre-norms, fc [hidden, 2*hidden], one full-attention layer, norm */
+    const void *mtp_pre_e, *mtp_pre_h, *mtp_fc, *mtp_norm;
+    wein_b200_layer_weights mtp_layer;
+} wein_b200_weights;
+
+typedef struct wein_b200_engine wein_b200_engine;
+
+/* Allocates pools (recurrent / conv state rows, KV pages), scratch and tables.  The only entry that allocates. */
+int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const wein_b200_weights *weights, wein_b200_engine **out);
+void wein_b200_engine_destroy(wein_b200_engine *e);
+uint64_t wein_b200_engine_device_bytes(const wein_b200_engine *e);
+
+/* Admission of a sequence into a slot: zeroes its state rows, installs its block-table row (host_pages: n_pages page
+ * ids) and its sampling parameters (SampleParams of crates/wein-engine/src/protocol.rs:50-76; temp <= 0 = greedy). */
+int32_t wein_b200_engine_admit(wein_b200_engine *e, uint32_t slot, const uint32_t *host_pages, uint32_t n_pages, float temp,
+                               uint32_t top_k, float top_p, uint64_t seed, void *stream);
+
+/* Prefill: feeds host_lens[i] prompt tokens of slot host_slots[i] (tokens concatenated in host_tokens) through the verify
+ * forward in chunks of k_max+1 positions, then emits each sequence's first token.  Not graph-captured; synchronises. */
+int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, const uint32_t *host_tokens,
+                                 const uint32_t *host_lens, void *stream);
+
+/* One round for the slots host_slots[0..n): draft k tokens with the MTP head (k = 0: plain decode step), verify the k+1
+ * positions in one forward, accept on the device, commit (position, pending token, state row, hidden, token ring).
+ * ctx_bound = an upper bound of (position + k + 1) over the batch (sizes the attention grid).  use_graph != 0 replays a
+ * CUDA graph cached per (n, k, sampling mode, ctx bucket).  No host synchronisation. */
+int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, uint32_t ctx_bound,
+                                   uint32_t use_graph, void *stream);
+
+/* Synchronises the stream and reads a slot: tokens emitted since admission (up to cap), position, and the counters of
+ * spec_stats() (crates/wein-exec/src/qwen.rs:4257-4259): rounds, drafts, accepted. */
+int32_t wein_b200_engine_read(wein_b200_engine *e, uint32_t slot, uint32_t *host_tokens, uint32_t cap, uint32_t *host_n_tokens,
+                              uint32_t *host_pos, uint64_t *host_stats3, void *stream);
+
+/* Test / profiling access to engine-owned device buffers by name ("logits", "x", "accept_len", "state_row", "lin_state:<i>",
+ * "k_pool:<i>", ...): returns the device pointer and its size in bytes, or NULL. */
+void *wein_b200_engine_buffer(wein_b200_engine *e, const char *name, uint64_t *bytes);
+/* Kernel launches recorded by the most recent spec_step (eager) or captured in the graph it replayed. */
+uint32_t wein_b200_engine_last_launches(const wein_b200_engine *e);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* WEIN_B200_H */

@@ -21,6 +21,7 @@ SOURCES = [
     ("ops_exact.cu", ["-fmad=false"]),
     ("gdn.cu", ["-fmad=false"]),
     ("accept.cu", ["-fmad=false"]),
+    ("fused_glue.cu", ["-fmad=false"]),
     ("attn.cu", []),
     ("gemm.cu", []),
     ("engine.cu", []),

@@ -16,6 +16,7 @@
 // Every floating-point step is written in the oracle's order: results are bit-identical to oracle/.
 // Compiled with -fmad=false.
 #include "common.cuh"
+#include "internal.h"
 
 #define DIST_CAP 64
 
@@ -64,8 +65,10 @@ struct FilterParams {
     uint32_t *out_ids;         // [s, 64]
     float *out_probs;          // [s, 64]
     uint32_t *out_n;           // [s]
-    // optional: draw a token from each row's distribution (draft sampling)
-    uint32_t *sample_out;      // [s] or null
+    uint32_t out_mul, out_off; // row r writes distribution slot r*out_mul + out_off
+    // optional: draw a token from each row's distribution (draft sampling); row r writes sample_out[r*sample_mul + sample_off]
+    uint32_t *sample_out;      // or null
+    uint32_t sample_mul, sample_off;
     const uint64_t *seed, *round;  // per sequence
     uint32_t position;
 };
@@ -102,11 +105,12 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
     const float temp = P.temp[seq];
     const bool greedy = !(temp > 0.0f);
     uint32_t k = greedy ? 1u : min(P.top_k[seq], (uint32_t)DIST_CAP);
-    uint32_t *ids = P.out_ids + (size_t)r * DIST_CAP;
-    float *probs = P.out_probs + (size_t)r * DIST_CAP;
+    const size_t oslot = (size_t)r * P.out_mul + P.out_off, sslot = (size_t)r * P.sample_mul + P.sample_off;
+    uint32_t *ids = P.out_ids + oslot * DIST_CAP;
+    float *probs = P.out_probs + oslot * DIST_CAP;
     if (k == 0 || P.n == 0) {  // top_k = 0 (whole vocabulary) is not supported on the device: in-band error, as the reference
         if (tid < DIST_CAP) { ids[tid] = 0xffffffffu; probs[tid] = 0.0f; }
-        if (tid == 0) { P.out_n[r] = 0; if (P.sample_out) P.sample_out[r] = 0xffffffffu; }
+        if (tid == 0) { P.out_n[oslot] = 0; if (P.sample_out) P.sample_out[sslot] = 0xffffffffu; }
         return;
     }
     if (k > P.n) k = P.n;
@@ -205,7 +209,7 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
         for (uint32_t j = 0; j < keep; j++) z = __fadd_rn(e_s[j], z);
         for (uint32_t j = 0; j < keep; j++) e_s[j] = __fdiv_rn(e_s[j], z);
         sh[6] = keep;
-        P.out_n[r] = keep;
+        P.out_n[oslot] = keep;
         if (P.sample_out) {
             uint32_t tok = srt_idx[0];
             if (!greedy) {
@@ -213,7 +217,7 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
                 spec_uniforms(P.seed[seq], P.round[seq], P.position, 0, u);
                 tok = srt_idx[pick_from(e_s, (int)keep, u[0])];
             }
-            P.sample_out[r] = tok;
+            P.sample_out[sslot] = tok;
         }
     }
     __syncthreads();
@@ -234,7 +238,9 @@ struct AcceptParams {
     const float *p_probs, *q_probs;
     const float *temp;              // per sequence; null or <= 0: greedy rule
     const uint64_t *seed, *round;   // per sequence
-    const uint32_t *drafts;         // [B, k]
+    const uint32_t *slot_of;        // [B] index of batch row b into temp / seed / round (null: b)
+    uint32_t draft_stride;          // elements between the draft rows of consecutive sequences (>= k)
+    const uint32_t *drafts;         // [B, draft_stride]
     const uint32_t *n_drafts;       // [B] or null (= k)
     uint32_t B, k;
     uint32_t *accept_len;           // [B]
@@ -257,7 +263,8 @@ __global__ void __launch_bounds__(32) accept_kernel(const AcceptParams P) {
     const uint32_t k = P.k, rows = k + 1;
     const uint32_t nd = P.n_drafts ? min(P.n_drafts[b], k) : k;
     uint32_t *out = P.out_tokens + (size_t)b * rows;
-    const bool greedy = !P.temp || !(P.temp[b] > 0.0f);
+    const uint32_t ps = P.slot_of ? P.slot_of[b] : b;
+    const bool greedy = !P.temp || !(P.temp[ps] > 0.0f);
     if (greedy) {
         // target token of each row: from the argmax partials, or entry 0 of the row's compact distribution
         uint32_t a = 0;
@@ -268,7 +275,7 @@ __global__ void __launch_bounds__(32) accept_kernel(const AcceptParams P) {
                                    : P.p_ids[((size_t)b * rows + j) * DIST_CAP];
             if (P.target && lane == 0) P.target[(size_t)b * rows + j] = t;
             if (open) {
-                if (j < nd && P.drafts[(size_t)b * k + j] == t) { a = j + 1; if (lane == 0) out[j] = t; }
+                if (j < nd && P.drafts[(size_t)b * P.draft_stride + j] == t) { a = j + 1; if (lane == 0) out[j] = t; }
                 else { open = false; emitted = t; if (lane == 0) out[j] = t; }
             }
         }
@@ -279,13 +286,13 @@ __global__ void __launch_bounds__(32) accept_kernel(const AcceptParams P) {
         }
         return;
     }
-    const uint64_t seed = P.seed[b], round = P.round[b];
+    const uint64_t seed = P.seed[ps], round = P.round[ps];
     uint32_t a = 0;
     for (; a < nd; a++) {
-        const uint32_t *pi = P.p_ids + ((size_t)b * rows + a) * DIST_CAP, *qi = P.q_ids + ((size_t)b * k + a) * DIST_CAP;
-        const float *pp = P.p_probs + ((size_t)b * rows + a) * DIST_CAP, *qp = P.q_probs + ((size_t)b * k + a) * DIST_CAP;
-        const uint32_t pn = P.p_n[(size_t)b * rows + a], qn = P.q_n[(size_t)b * k + a];
-        const uint32_t x = P.drafts[(size_t)b * k + a];
+        const uint32_t *pi = P.p_ids + ((size_t)b * rows + a) * DIST_CAP, *qi = P.q_ids + ((size_t)b * P.draft_stride + a) * DIST_CAP;
+        const float *pp = P.p_probs + ((size_t)b * rows + a) * DIST_CAP, *qp = P.q_probs + ((size_t)b * P.draft_stride + a) * DIST_CAP;
+        const uint32_t pn = P.p_n[(size_t)b * rows + a], qn = P.q_n[(size_t)b * P.draft_stride + a];
+        const uint32_t x = P.drafts[(size_t)b * P.draft_stride + a];
         float u[4];
         spec_uniforms(seed, round, a, 1, u);
         // p(x), q(x): at most one match per list
@@ -336,8 +343,6 @@ __global__ void __launch_bounds__(32) accept_kernel(const AcceptParams P) {
     }
 }
 
-// argmax phase 1 lives in ops_exact.cu
-int32_t wein_b200_argmax_partials(const void *x, const void *rows, void *part, uint32_t n, uint32_t s, uint32_t split, cudaStream_t st);
 
 int32_t wb_topk_filter(const FilterParams &p, cudaStream_t st) {
     WB_CHECK_ARG(p.x && p.temp && p.top_k && p.top_p && p.out_ids && p.out_probs && p.out_n, "topk_filter: null pointer");
@@ -349,15 +354,33 @@ int32_t wb_topk_filter(const FilterParams &p, cudaStream_t st) {
     return WB_OK;
 }
 int32_t wb_accept(const AcceptParams &p, cudaStream_t st) {
-    WB_CHECK_ARG(p.drafts && p.accept_len && p.out_tokens, "accept: null pointer");
+    WB_CHECK_ARG((p.drafts || p.k == 0) && p.accept_len && p.out_tokens, "accept: null pointer");
     WB_CHECK_ARG(p.am_part || p.p_ids, "accept: needs argmax partials or target distributions");
-    WB_CHECK_ARG(!p.temp || (p.p_ids && p.p_probs && p.p_n && p.q_ids && p.q_probs && p.q_n && p.seed && p.round),
+    WB_CHECK_ARG(!p.temp || (p.p_ids && p.p_probs && p.p_n && (p.k == 0 || (p.q_ids && p.q_probs && p.q_n)) && p.seed && p.round),
                  "accept: sampled mode needs both distributions, seeds and rounds");
-    WB_CHECK_ARG(p.k >= 1 && p.k <= 15, "accept: k = %u outside 1..15", p.k);
+    WB_CHECK_ARG(p.k <= 15 && p.draft_stride >= p.k, "accept: k = %u outside 0..15 or draft stride too small", p.k);
     if (p.B == 0) return WB_OK;
     accept_kernel<<<p.B, 32, 0, st>>>(p);
     WB_LAUNCH_CHECK();
     return WB_OK;
+}
+
+int32_t wb_topk_filter_args(const FilterArgs &a, cudaStream_t st) {
+    FilterParams p{};
+    p.x = (const bf16_t *)a.logits; p.rows = a.rows; p.row_seq = a.row_seq; p.rows_per_seq = a.rows_per_seq;
+    p.temp = a.temp; p.top_k = a.top_k; p.top_p = a.top_p; p.n = a.n; p.s = a.s;
+    p.out_ids = a.out_ids; p.out_probs = a.out_probs; p.out_n = a.out_n; p.out_mul = a.out_mul; p.out_off = a.out_off;
+    p.sample_out = a.sample_out; p.sample_mul = a.sample_mul; p.sample_off = a.sample_off; p.seed = a.seed; p.round = a.round;
+    p.position = a.position;
+    return wb_topk_filter(p, st);
+}
+int32_t wb_accept_args(const AcceptArgs &a, cudaStream_t st) {
+    AcceptParams p{};
+    p.am_part = a.am_part; p.am_split = a.am_split; p.p_ids = a.p_ids; p.q_ids = a.q_ids; p.p_n = a.p_n; p.q_n = a.q_n;
+    p.p_probs = a.p_probs; p.q_probs = a.q_probs; p.temp = a.temp; p.seed = a.seed; p.round = a.round; p.slot_of = a.slot_of;
+    p.drafts = a.drafts; p.draft_stride = a.draft_stride; p.n_drafts = a.n_drafts; p.B = a.B; p.k = a.k;
+    p.accept_len = a.accept_len; p.out_tokens = a.out_tokens; p.target = a.target;
+    return wb_accept(p, st);
 }
 
 extern "C" {
@@ -370,6 +393,7 @@ int32_t wein_b200_topk_filter(const void *logits, const void *rows, const void *
     p.temp = (const float *)temp; p.top_k = (const uint32_t *)top_k; p.top_p = (const float *)top_p; p.n = n; p.s = s;
     p.out_ids = (uint32_t *)out_ids; p.out_probs = (float *)out_probs; p.out_n = (uint32_t *)out_n;
     p.sample_out = (uint32_t *)sample_out; p.seed = (const uint64_t *)seed; p.round = (const uint64_t *)round; p.position = position;
+    p.out_mul = 1; p.out_off = 0; p.sample_mul = 1; p.sample_off = 0;
     return wb_topk_filter(p, (cudaStream_t)stream);
 }
 
@@ -382,7 +406,7 @@ int32_t wein_b200_accept_greedy(const void *logits, const void *rows, const void
     if (rc != WB_OK) return rc;
     AcceptParams p{};
     p.am_part = (const uint64_t *)scratch; p.am_split = 32;
-    p.drafts = (const uint32_t *)drafts; p.n_drafts = (const uint32_t *)n_drafts; p.B = B; p.k = k;
+    p.drafts = (const uint32_t *)drafts; p.n_drafts = (const uint32_t *)n_drafts; p.B = B; p.k = k; p.draft_stride = k;
     p.accept_len = (uint32_t *)accept_len; p.out_tokens = (uint32_t *)out_tokens; p.target = (uint32_t *)target;
     return wb_accept(p, (cudaStream_t)stream);
 }
@@ -396,7 +420,7 @@ int32_t wein_b200_accept_sampled(const void *drafts, const void *n_drafts, const
     p.p_ids = (const uint32_t *)p_ids; p.p_probs = (const float *)p_probs; p.p_n = (const uint32_t *)p_n;
     p.q_ids = (const uint32_t *)q_ids; p.q_probs = (const float *)q_probs; p.q_n = (const uint32_t *)q_n;
     p.temp = (const float *)temp; p.seed = (const uint64_t *)seed; p.round = (const uint64_t *)round;
-    p.drafts = (const uint32_t *)drafts; p.n_drafts = (const uint32_t *)n_drafts; p.B = B; p.k = k;
+    p.drafts = (const uint32_t *)drafts; p.n_drafts = (const uint32_t *)n_drafts; p.B = B; p.k = k; p.draft_stride = k;
     p.accept_len = (uint32_t *)accept_len; p.out_tokens = (uint32_t *)out_tokens;
     return wb_accept(p, (cudaStream_t)stream);
 }

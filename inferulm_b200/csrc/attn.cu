@@ -21,6 +21,7 @@
 // own position and seg_pages -- not on the chain length, the batch, or the grid -- so row (seq, pos) of a
 // k+1-row verify chain equals the same row of a plain one-token step bit for bit.
 #include "common.cuh"
+#include "internal.h"
 
 #define ATT_PAGE 16
 
@@ -286,6 +287,22 @@ static int32_t attn_launch(const AttnParams &p, cudaStream_t st) {
     dim3 g2(16 * p.n_mtiles, p.kv_heads, p.n_spans);
     attn_combine_kernel<HD><<<g2, HD / 4, 0, st>>>(p);
     WB_LAUNCH_CHECK();
+    return WB_OK;
+}
+
+int32_t wb_attn_init(uint32_t head_dim) {
+    AttnParams p{};
+    p.n_spans = 0;
+    (void)p;
+    size_t smem;
+    cudaError_t e = cudaSuccess;
+    auto bytes = [](size_t hd) { size_t a = 16 * hd * 2 + 4 * 4 * (size_t)ATT_PAGE * hd * 2, b = 16 * hd * 2 + 4 * 16 * (hd + 4) * 4; return a > b ? a : b; };
+    smem = bytes(head_dim);
+    if (head_dim == 256) e = cudaFuncSetAttribute(attn_verify_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    else if (head_dim == 128) e = cudaFuncSetAttribute(attn_verify_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    else if (head_dim == 64) e = cudaFuncSetAttribute(attn_verify_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    else { wb_set_error("attn: head_dim %u not built", head_dim); return WB_ERR_SHAPE; }
+    if (e != cudaSuccess) { wb_set_error("attn: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return WB_ERR_CUDA; }
     return WB_OK;
 }
 

@@ -1,0 +1,665 @@
+// Step-level host side: the speculative step of wein's executor re-stated for device-resident control.
+//
+// Reference: Qwen35Executor::step and its helpers (crates/wein-exec/src/qwen.rs): spec_draft_batch (:2748-2853, k MTP
+// forwards, each ending in a stream sync and a readback), forward_batch_mixed / run_forward (:3453-3703, :3843-4153, one
+// verify forward over all chain rows), spec_finish (:2419-2502, host-side acceptance, zero-copy state-row swap,
+// hidden stash).  The reference never graph-captures this step (:2235-2237) because acceptance is decided on the host.
+//
+// Here every per-round decision lives on the device: small kernels build the round's row / span tables from the
+// per-slot state (position, pending token, state row), the draft tokens stay in a device buffer, acceptance and
+// commit are kernels.  A round is therefore a fixed launch sequence -- k draft forwards, one verify forward, accept,
+// commit -- which is captured once per (batch, k, mode, context bucket) and replayed as one CUDA graph.
+//
+// State rows.  The reference claims k+2 contiguous rows per chain and commits by re-pointing state_row to head+1+a.
+// Each slot here owns two banks of k_max+1 rows; a round reads the slot's current row and writes its snapshots into
+// the other bank, then commits by setting state_row = bank base + a.  No state bytes are ever copied.
+#include <math.h>
+#include <stdio.h>
+#include <string.h>
+#include <map>
+#include <string>
+#include <tuple>
+#include <vector>
+#include "../../include/wein_b200.h"
+#include "common.cuh"
+#include "internal.h"
+
+extern "C" {
+int32_t wein_b200_embed(const void *, const void *, void *, uint32_t, uint32_t, void *);
+int32_t wein_b200_rms_norm_zc(const void *, const void *, void *, uint32_t, uint32_t, float, void *);
+int32_t wein_b200_add_norm_zc(const void *, const void *, const void *, void *, void *, uint32_t, uint32_t, float, void *);
+}
+
+#define CUDA_TRY(x)                                                                                        \
+    do {                                                                                                   \
+        cudaError_t e__ = (x);                                                                             \
+        if (e__ != cudaSuccess) { wb_set_error("%s:%d %s: %s", __FILE__, __LINE__, #x, cudaGetErrorString(e__)); return WB_ERR_CUDA; } \
+    } while (0)
+#define TRY(x)                       \
+    do {                             \
+        int32_t rc__ = (x);          \
+        if (rc__ != WB_OK) return rc__; \
+    } while (0)
+
+#define RING_CAP 8192u
+
+struct wein_b200_engine {
+    wein_b200_model_cfg cfg;
+    wein_b200_weights w;
+    uint32_t H, II, V, P, T_max, bpr, keyd, vald, cd, lpn, fpn, n_lin, n_full, rows_per_slot, seg_pages;
+    std::vector<void *> allocs;
+    uint64_t bytes = 0;
+    std::vector<void *> lin_state, conv_state, k_pool, v_pool;  // k/v pools: full layers then the MTP layer
+    // per-slot device state
+    uint32_t *d_pos, *d_pending, *d_state_row, *d_bank, *d_out_count, *d_top_k, *d_ring, *d_block_table;
+    uint64_t *d_round, *d_seed, *d_stats;
+    float *d_temp, *d_top_p;
+    bf16_t *d_hid;
+    // per-step tables
+    uint32_t *d_slots, *d_tok, *d_pos_rows, *d_seq_rows, *d_row_start, *d_row_count, *d_in_row, *d_out_base, *d_lg_rows, *d_iota, *d_ones;
+    uint32_t *d_cnt_in, *d_tok_in, *d_last_in, *d_first_tok, *d_lg_of;
+    uint32_t *d_drafts, *d_accept_len, *d_out_tokens, *d_target;
+    uint32_t *d_mtp_tok, *d_mtp_rope, *d_mtp_kvpos;
+    // activations
+    bf16_t *x, *n1, *h2, *n2, *o, *proj, *qkvc, *core, *normed, *qh, *gate, *attn, *gu, *m, *d, *logits, *lg_in, *cat;
+    float *cosv, *sinv;
+    void *gemm_scratch, *attn_scratch, *am_part;
+    uint64_t gemm_scratch_bytes, attn_scratch_bytes;
+    uint32_t *p_ids, *q_ids, *p_n, *q_n;
+    float *p_probs, *q_probs;
+    // host mirrors
+    std::vector<float> h_temp;
+    std::vector<uint32_t> h_slots_cached;
+    uint32_t *h_stage = nullptr;  // pinned
+    size_t h_stage_words = 0;
+    std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint32_t>, cudaGraphExec_t> graphs;
+    uint32_t launches = 0, last_launches = 0;
+    std::map<std::string, std::pair<void *, uint64_t>> named;
+};
+typedef wein_b200_engine Engine;
+
+template <typename T>
+static int32_t dalloc(Engine *e, T **p, size_t n, const char *name, bool zero = true) {
+    size_t bytes = n * sizeof(T);
+    if (bytes == 0) bytes = 16;
+    void *q = nullptr;
+    cudaError_t er = cudaMalloc(&q, bytes);
+    if (er != cudaSuccess) { wb_set_error("engine: cudaMalloc of %zu bytes for %s failed: %s", bytes, name, cudaGetErrorString(er)); return WB_ERR_CUDA; }
+    if (zero) cudaMemset(q, 0, bytes);
+    e->allocs.push_back(q);
+    e->bytes += bytes;
+    e->named[name] = {q, bytes};
+    *p = (T *)q;
+    return WB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ table kernels
+struct SlotState {
+    uint32_t *pos, *pending, *state_row, *bank, *out_count, *ring;
+    uint64_t *round, *stats;
+    bf16_t *hid;
+};
+
+// Rows of a speculative round: batch row b = slot slots[b]; chain row j feeds the pending token (j = 0) or draft j-1.
+__global__ void verify_prep_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ drafts, uint32_t k_max,
+                                   uint32_t n, uint32_t P, uint32_t rows_per_slot, uint32_t bankrows, uint32_t *tok, uint32_t *pos_rows,
+                                   uint32_t *seq_rows, uint32_t *row_start, uint32_t *row_count, uint32_t *in_row, uint32_t *out_base,
+                                   uint32_t *lg_rows) {
+    uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n) return;
+    uint32_t slot = slots[b], p0 = S.pos[slot];
+    for (uint32_t j = 0; j < P; j++) {
+        uint32_t r = b * P + j;
+        tok[r] = j == 0 ? S.pending[slot] : drafts[b * k_max + j - 1];
+        pos_rows[r] = p0 + j;
+        seq_rows[r] = slot;
+        lg_rows[r] = r;
+    }
+    row_start[b] = b * P;
+    row_count[b] = P;
+    in_row[b] = S.state_row[slot];
+    out_base[b] = slot * rows_per_slot + (S.bank[slot] ^ 1u) * bankrows;
+}
+
+// Commit of a round (spec_finish, qwen.rs:2433-2460): emitted tokens to the slot's ring, position += a+1, pending =
+// bonus token, state_row = snapshot a of this round's bank, hidden of chain row a stashed for the next draft.
+__global__ void commit_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ accept_len,
+                              const uint32_t *__restrict__ out_tokens, const uint32_t *__restrict__ out_base, const bf16_t *__restrict__ x,
+                              uint32_t P, uint32_t k, uint32_t H) {
+    uint32_t b = blockIdx.x, slot = slots[b], a = accept_len[b];
+    const bf16_t *src = x + (size_t)(b * P + a) * H;
+    bf16_t *dst = S.hid + (size_t)slot * H;
+    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+    if (threadIdx.x == 0) {
+        uint32_t oc = S.out_count[slot];
+        for (uint32_t j = 0; j <= a; j++) S.ring[(size_t)slot * RING_CAP + ((oc + j) % RING_CAP)] = out_tokens[b * P + j];
+        S.out_count[slot] = oc + a + 1;
+        S.pending[slot] = out_tokens[b * P + a];
+        S.pos[slot] += a + 1;
+        S.state_row[slot] = out_base[b] + a;
+        S.bank[slot] ^= 1u;
+        S.round[slot] += 1;
+        S.stats[slot * 3 + 0] += 1;
+        S.stats[slot * 3 + 1] += k;
+        S.stats[slot * 3 + 2] += a;
+    }
+}
+
+// Prefill chunk tables: span b holds cnt[b] prompt tokens of slot slots[b] (tokens concatenated in tok_in).
+__global__ void prefill_prep_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ cnt,
+                                    const uint32_t *__restrict__ tok_in, const uint32_t *__restrict__ last, uint32_t n, uint32_t rows_per_slot,
+                                    uint32_t bankrows, uint32_t *tok, uint32_t *pos_rows, uint32_t *seq_rows, uint32_t *row_start,
+                                    uint32_t *row_count, uint32_t *in_row, uint32_t *out_base, uint32_t *lg_rows, uint32_t *lg_of) {
+    if (threadIdx.x != 0 || blockIdx.x != 0) return;
+    uint32_t r = 0, nl = 0;
+    for (uint32_t b = 0; b < n; b++) {
+        uint32_t slot = slots[b], c = cnt[b], p0 = S.pos[slot];
+        row_start[b] = r;
+        row_count[b] = c;
+        in_row[b] = S.state_row[slot];
+        out_base[b] = slot * rows_per_slot + (S.bank[slot] ^ 1u) * bankrows;
+        for (uint32_t j = 0; j < c; j++, r++) { tok[r] = tok_in[r]; pos_rows[r] = p0 + j; seq_rows[r] = slot; }
+        lg_of[b] = 0xffffffffu;
+        if (c > 0 && last[b]) { lg_rows[nl] = r - 1; lg_of[b] = nl; nl++; }
+    }
+}
+__global__ void prefill_commit_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ cnt,
+                                      const uint32_t *__restrict__ row_start, const uint32_t *__restrict__ out_base,
+                                      const uint32_t *__restrict__ lg_of, const uint32_t *__restrict__ first_tok, const bf16_t *__restrict__ x,
+                                      uint32_t H) {
+    uint32_t b = blockIdx.x, slot = slots[b], c = cnt[b];
+    if (c == 0) return;
+    const bf16_t *src = x + (size_t)(row_start[b] + c - 1) * H;
+    bf16_t *dst = S.hid + (size_t)slot * H;
+    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+    if (threadIdx.x == 0) {
+        S.pos[slot] += c;
+        S.state_row[slot] = out_base[b] + c - 1;
+        S.bank[slot] ^= 1u;
+        if (lg_of[b] != 0xffffffffu) {
+            uint32_t t = first_tok[lg_of[b]];
+            S.pending[slot] = t;
+            uint32_t oc = S.out_count[slot];
+            S.ring[(size_t)slot * RING_CAP + (oc % RING_CAP)] = t;
+            S.out_count[slot] = oc + 1;
+            S.round[slot] += 1;
+        }
+    }
+}
+// Inputs of draft step i: token = pending (i = 0) or the previous draft; rotary position absolute, KV slot chain-local.
+__global__ void mtp_prep_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ drafts, uint32_t k_max,
+                                uint32_t n, uint32_t i, uint32_t *tok, uint32_t *rope_pos, uint32_t *kv_pos) {
+    uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n) return;
+    uint32_t slot = slots[b];
+    tok[b] = i == 0 ? S.pending[slot] : drafts[b * k_max + i - 1];
+    rope_pos[b] = S.pos[slot] + i;
+    kv_pos[b] = i;
+}
+__global__ void slot_init_kernel(SlotState S, uint32_t slot, uint32_t row0, float *temp, uint32_t *top_k, float *top_p, uint64_t *seed,
+                                 float t, uint32_t k, float p, uint64_t sd) {
+    S.pos[slot] = 0; S.pending[slot] = 0; S.state_row[slot] = row0; S.bank[slot] = 0; S.out_count[slot] = 0; S.round[slot] = 0;
+    S.stats[slot * 3] = S.stats[slot * 3 + 1] = S.stats[slot * 3 + 2] = 0;
+    temp[slot] = t; top_k[slot] = k; top_p[slot] = p; seed[slot] = sd;
+}
+
+static SlotState slot_state(Engine *e) {
+    SlotState s;
+    s.pos = e->d_pos; s.pending = e->d_pending; s.state_row = e->d_state_row; s.bank = e->d_bank; s.out_count = e->d_out_count;
+    s.ring = e->d_ring; s.round = e->d_round; s.stats = e->d_stats; s.hid = e->d_hid;
+    return s;
+}
+
+// ------------------------------------------------------------------------------------------------ create / destroy
+static bool adjacent(const void *a, const void *b, size_t a_elems) { return a && b && (const char *)b == (const char *)a + a_elems * 2; }
+
+extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const wein_b200_weights *weights, wein_b200_engine **out) {
+    WB_CHECK_ARG(cfg && weights && out, "engine_create: null argument");
+    WB_CHECK_ARG(cfg->n_layers >= 1 && cfg->n_layers <= WEIN_B200_MAX_LAYERS, "engine_create: n_layers %u outside 1..%d", cfg->n_layers, WEIN_B200_MAX_LAYERS);
+    WB_CHECK_ARG(cfg->k_max <= 7 && cfg->max_seqs >= 1, "engine_create: k_max %u > 7 or no slots", cfg->k_max);
+    WB_CHECK_ARG(cfg->hidden % 32 == 0 && cfg->inter % 32 == 0 && cfg->hidden >= 256, "engine_create: hidden / inter must be multiples of 32");
+    WB_CHECK_ARG(cfg->lin_k_dim == 128 && cfg->lin_v_dim == 128 && cfg->conv_kernel == 4, "engine_create: DeltaNet heads must be 128x128 with conv width 4");
+    WB_CHECK_ARG(cfg->q_heads % cfg->kv_heads == 0 && (cfg->q_heads / cfg->kv_heads) * (cfg->k_max + 1) <= 32,
+                 "engine_create: (k_max+1) x GQA group exceeds 32 query rows");
+    Engine *e = new Engine();
+    e->cfg = *cfg; e->w = *weights;
+    e->H = cfg->hidden; e->II = cfg->inter; e->V = cfg->vocab; e->P = cfg->k_max + 1; e->T_max = cfg->max_seqs * e->P;
+    e->bpr = (cfg->max_pos + 15) / 16;
+    e->keyd = cfg->lin_k_heads * cfg->lin_k_dim; e->vald = cfg->lin_v_heads * cfg->lin_v_dim; e->cd = 2 * e->keyd + e->vald;
+    e->lpn = e->cd + e->vald + 2 * cfg->lin_v_heads;
+    e->fpn = 2 * cfg->q_heads * cfg->head_dim + 2 * cfg->kv_heads * cfg->head_dim;
+    e->rows_per_slot = 2 * e->P;
+    e->seg_pages = cfg->attn_seg_pages ? cfg->attn_seg_pages : 4;
+    for (uint32_t l = 0; l < cfg->n_layers; l++) (cfg->layer_is_full[l] ? e->n_full : e->n_lin)++;
+    *out = e;
+    const uint32_t S = cfg->max_seqs, T = e->T_max, H = e->H;
+    TRY(wb_gemm_warmup());
+    TRY(wb_attn_init(cfg->head_dim));
+    // pools
+    size_t st_elem = cfg->state_f32 ? 4 : 2;
+    size_t lin_row = (size_t)cfg->lin_v_heads * 128 * 128, conv_row = (size_t)e->cd * 3;
+    for (uint32_t i = 0; i < e->n_lin; i++) {
+        char *p; bf16_t *c;
+        TRY(dalloc(e, &p, (size_t)S * e->rows_per_slot * lin_row * st_elem, ("lin_state:" + std::to_string(i)).c_str(), false));
+        TRY(dalloc(e, &c, (size_t)S * e->rows_per_slot * conv_row, ("conv_state:" + std::to_string(i)).c_str(), false));
+        e->lin_state.push_back(p); e->conv_state.push_back(c);
+    }
+    size_t he = (size_t)cfg->kv_heads * cfg->head_dim;
+    for (uint32_t i = 0; i < e->n_full; i++) {
+        bf16_t *k, *v;
+        TRY(dalloc(e, &k, (size_t)cfg->n_pages * 16 * he, ("k_pool:" + std::to_string(i)).c_str(), false));
+        TRY(dalloc(e, &v, (size_t)cfg->n_pages * 16 * he, ("v_pool:" + std::to_string(i)).c_str(), false));
+        e->k_pool.push_back(k); e->v_pool.push_back(v);
+    }
+    if (cfg->has_mtp) {
+        bf16_t *k, *v;
+        TRY(dalloc(e, &k, (size_t)S * 16 * he, "k_pool:mtp"));
+        TRY(dalloc(e, &v, (size_t)S * 16 * he, "v_pool:mtp"));
+        e->k_pool.push_back(k); e->v_pool.push_back(v);
+    }
+    // slot state
+    TRY(dalloc(e, &e->d_pos, S, "pos")); TRY(dalloc(e, &e->d_pending, S, "pending")); TRY(dalloc(e, &e->d_state_row, S, "state_row"));
+    TRY(dalloc(e, &e->d_bank, S, "bank")); TRY(dalloc(e, &e->d_out_count, S, "out_count")); TRY(dalloc(e, &e->d_top_k, S, "top_k"));
+    TRY(dalloc(e, &e->d_ring, (size_t)S * RING_CAP, "ring")); TRY(dalloc(e, &e->d_block_table, (size_t)S * e->bpr, "block_table"));
+    TRY(dalloc(e, &e->d_round, S, "round")); TRY(dalloc(e, &e->d_seed, S, "seed")); TRY(dalloc(e, &e->d_stats, (size_t)S * 3, "stats"));
+    TRY(dalloc(e, &e->d_temp, S, "temp")); TRY(dalloc(e, &e->d_top_p, S, "top_p")); TRY(dalloc(e, &e->d_hid, (size_t)S * H, "hid"));
+    // step tables
+    TRY(dalloc(e, &e->d_slots, S, "slots")); TRY(dalloc(e, &e->d_tok, T, "tok")); TRY(dalloc(e, &e->d_pos_rows, T, "pos_rows"));
+    TRY(dalloc(e, &e->d_seq_rows, T, "seq_rows")); TRY(dalloc(e, &e->d_row_start, S, "row_start")); TRY(dalloc(e, &e->d_row_count, S, "row_count"));
+    TRY(dalloc(e, &e->d_in_row, S, "in_row")); TRY(dalloc(e, &e->d_out_base, S, "out_base")); TRY(dalloc(e, &e->d_lg_rows, T, "lg_rows"));
+    TRY(dalloc(e, &e->d_iota, T, "iota")); TRY(dalloc(e, &e->d_ones, T, "ones"));
+    TRY(dalloc(e, &e->d_cnt_in, S, "cnt_in")); TRY(dalloc(e, &e->d_tok_in, T, "tok_in")); TRY(dalloc(e, &e->d_last_in, S, "last_in"));
+    TRY(dalloc(e, &e->d_first_tok, S, "first_tok")); TRY(dalloc(e, &e->d_lg_of, S, "lg_of"));
+    TRY(dalloc(e, &e->d_drafts, (size_t)S * (cfg->k_max ? cfg->k_max : 1), "drafts")); TRY(dalloc(e, &e->d_accept_len, S, "accept_len"));
+    TRY(dalloc(e, &e->d_out_tokens, T, "out_tokens")); TRY(dalloc(e, &e->d_target, T, "target"));
+    TRY(dalloc(e, &e->d_mtp_tok, S, "mtp_tok")); TRY(dalloc(e, &e->d_mtp_rope, S, "mtp_rope")); TRY(dalloc(e, &e->d_mtp_kvpos, S, "mtp_kvpos"));
+    {
+        std::vector<uint32_t> iota(T), ones(T, 1);
+        for (uint32_t i = 0; i < T; i++) iota[i] = i;
+        CUDA_TRY(cudaMemcpy(e->d_iota, iota.data(), T * 4, cudaMemcpyHostToDevice));
+        CUDA_TRY(cudaMemcpy(e->d_ones, ones.data(), T * 4, cudaMemcpyHostToDevice));
+    }
+    // activations
+    size_t qd = (size_t)cfg->q_heads * cfg->head_dim;
+    TRY(dalloc(e, &e->x, (size_t)T * H, "x")); TRY(dalloc(e, &e->n1, (size_t)T * H, "n1")); TRY(dalloc(e, &e->h2, (size_t)T * H, "h2"));
+    TRY(dalloc(e, &e->n2, (size_t)T * H, "n2")); TRY(dalloc(e, &e->o, (size_t)T * H, "o"));
+    TRY(dalloc(e, &e->proj, (size_t)T * (e->lpn > e->fpn ? e->lpn : e->fpn), "proj")); TRY(dalloc(e, &e->qkvc, (size_t)T * e->cd, "qkvc"));
+    TRY(dalloc(e, &e->core, (size_t)T * e->vald, "core")); TRY(dalloc(e, &e->normed, (size_t)T * e->vald, "normed"));
+    TRY(dalloc(e, &e->qh, (size_t)T * qd, "qh")); TRY(dalloc(e, &e->gate, (size_t)T * qd, "gate")); TRY(dalloc(e, &e->attn, (size_t)T * qd, "attn"));
+    TRY(dalloc(e, &e->gu, (size_t)T * 2 * e->II, "gu")); TRY(dalloc(e, &e->m, (size_t)T * e->II, "m")); TRY(dalloc(e, &e->d, (size_t)T * H, "d"));
+    TRY(dalloc(e, &e->logits, (size_t)T * e->V, "logits")); TRY(dalloc(e, &e->lg_in, (size_t)T * H, "lg_in"));
+    TRY(dalloc(e, &e->cat, (size_t)S * 2 * H, "cat"));
+    // rope tables, rounded to bf16 as the reference executor does (qwen.rs:1581-1586)
+    {
+        uint32_t half = cfg->rot_dim / 2;
+        std::vector<float> c((size_t)cfg->max_pos * half), s((size_t)cfg->max_pos * half);
+        for (uint32_t p = 0; p < half; p++) {
+            double inv_freq = pow(cfg->rope_theta, -((double)p) / (double)half);
+            for (uint32_t t = 0; t < cfg->max_pos; t++) {
+                double a = (double)t * inv_freq;
+                c[(size_t)t * half + p] = bf2f(f2bf((float)cos(a)));
+                s[(size_t)t * half + p] = bf2f(f2bf((float)sin(a)));
+            }
+        }
+        TRY(dalloc(e, &e->cosv, c.size(), "cos")); TRY(dalloc(e, &e->sinv, s.size(), "sin"));
+        CUDA_TRY(cudaMemcpy(e->cosv, c.data(), c.size() * 4, cudaMemcpyHostToDevice));
+        CUDA_TRY(cudaMemcpy(e->sinv, s.data(), s.size() * 4, cudaMemcpyHostToDevice));
+    }
+    // kernel scratch
+    e->gemm_scratch_bytes = wein_b200_gemm_scratch_bytes(e->V);
+    char *gs; TRY(dalloc(e, &gs, e->gemm_scratch_bytes, "gemm_scratch")); e->gemm_scratch = gs;
+    uint32_t max_segs = (e->bpr + e->seg_pages - 1) / e->seg_pages;
+    e->attn_scratch_bytes = wein_b200_attn_scratch_bytes(S, cfg->kv_heads, cfg->head_dim, max_segs);
+    char *as; TRY(dalloc(e, &as, e->attn_scratch_bytes, "attn_scratch", false)); e->attn_scratch = as;
+    uint64_t *am; TRY(dalloc(e, &am, (size_t)T * 32, "am_part")); e->am_part = am;
+    TRY(dalloc(e, &e->p_ids, (size_t)T * 64, "p_ids")); TRY(dalloc(e, &e->p_probs, (size_t)T * 64, "p_probs")); TRY(dalloc(e, &e->p_n, T, "p_n"));
+    TRY(dalloc(e, &e->q_ids, (size_t)T * 64, "q_ids")); TRY(dalloc(e, &e->q_probs, (size_t)T * 64, "q_probs")); TRY(dalloc(e, &e->q_n, T, "q_n"));
+    e->h_temp.assign(S, 0.0f);
+    e->h_stage_words = (size_t)T + 5 * S + 16;
+    CUDA_TRY(cudaMallocHost((void **)&e->h_stage, e->h_stage_words * 4));
+    CUDA_TRY(cudaDeviceSynchronize());
+    return WB_OK;
+}
+
+extern "C" void wein_b200_engine_destroy(wein_b200_engine *e) {
+    if (!e) return;
+    cudaDeviceSynchronize();
+    for (auto &g : e->graphs) cudaGraphExecDestroy(g.second);
+    for (void *p : e->allocs) cudaFree(p);
+    if (e->h_stage) cudaFreeHost(e->h_stage);
+    delete e;
+}
+extern "C" uint64_t wein_b200_engine_device_bytes(const wein_b200_engine *e) { return e ? e->bytes : 0; }
+extern "C" uint32_t wein_b200_engine_last_launches(const wein_b200_engine *e) { return e ? e->last_launches : 0; }
+extern "C" void *wein_b200_engine_buffer(wein_b200_engine *e, const char *name, uint64_t *bytes) {
+    if (!e || !name) return nullptr;
+    auto it = e->named.find(name);
+    if (it == e->named.end()) return nullptr;
+    if (bytes) *bytes = it->second.second;
+    return it->second.first;
+}
+
+extern "C" int32_t wein_b200_engine_admit(wein_b200_engine *e, uint32_t slot, const uint32_t *host_pages, uint32_t n_pages, float temp,
+                                          uint32_t top_k, float top_p, uint64_t seed, void *stream) {
+    WB_CHECK_ARG(e && slot < e->cfg.max_seqs, "engine_admit: slot %u out of range", slot);
+    WB_CHECK_ARG(host_pages && n_pages >= 1 && n_pages <= e->bpr, "engine_admit: %u pages outside 1..%u", n_pages, e->bpr);
+    for (uint32_t i = 0; i < n_pages; i++) WB_CHECK_ARG(host_pages[i] < e->cfg.n_pages, "engine_admit: page id %u >= pool size %u", host_pages[i], e->cfg.n_pages);
+    WB_CHECK_ARG(!(temp > 0.0f) || (top_k >= 1 && top_k <= 64), "engine_admit: sampling needs 1 <= top_k <= 64 (whole-vocabulary sampling is not built)");
+    cudaStream_t st = (cudaStream_t)stream;
+    uint32_t row0 = slot * e->rows_per_slot;
+    size_t st_elem = e->cfg.state_f32 ? 4 : 2;
+    size_t lin_row = (size_t)e->cfg.lin_v_heads * 128 * 128 * st_elem, conv_row = (size_t)e->cd * 3 * 2;
+    for (uint32_t i = 0; i < e->n_lin; i++) {
+        CUDA_TRY(cudaMemsetAsync((char *)e->lin_state[i] + (size_t)row0 * lin_row, 0, lin_row, st));
+        CUDA_TRY(cudaMemsetAsync((char *)e->conv_state[i] + (size_t)row0 * conv_row, 0, conv_row, st));
+    }
+    CUDA_TRY(cudaMemcpyAsync(e->d_block_table + (size_t)slot * e->bpr, host_pages, (size_t)n_pages * 4, cudaMemcpyHostToDevice, st));
+    slot_init_kernel<<<1, 1, 0, st>>>(slot_state(e), slot, row0, e->d_temp, e->d_top_k, e->d_top_p, e->d_seed, temp, top_k, top_p, seed);
+    WB_LAUNCH_CHECK();
+    CUDA_TRY(cudaStreamSynchronize(st));  // host_pages may be pageable memory
+    e->h_temp[slot] = temp;
+    return WB_OK;
+}
+
+// ------------------------------------------------------------------------------------------------ forward passes
+static int32_t gemm(Engine *e, const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, cudaStream_t st) {
+    e->launches++;
+    return wb_gemm_wt(a, w, c, m, n, k, lda, ldc, e->gemm_scratch, e->gemm_scratch_bytes, st);
+}
+
+// Full-attention block: projections -> fused q/k norm + rope + KV scatter -> paged verify attention (+ gate) -> o_proj.
+static int32_t full_attn_block(Engine *e, const wein_b200_layer_weights &w, void *kp, void *vp, uint32_t T, uint32_t n_spans,
+                               uint32_t max_count, uint32_t max_ctx, uint32_t seg_pages, const uint32_t *rope_pos, const uint32_t *kv_pos,
+                               const uint32_t *seq_ids, const uint32_t *bt, uint32_t bpr, const uint32_t *row_start,
+                               const uint32_t *row_count, cudaStream_t st) {
+    const wein_b200_model_cfg &c = e->cfg;
+    uint32_t H = e->H, qd = c.q_heads * c.head_dim, he = c.kv_heads * c.head_dim;
+    if (adjacent(w.qg, w.k, (size_t)2 * qd * H) && adjacent(w.k, w.v, (size_t)he * H)) {
+        TRY(gemm(e, e->n1, w.qg, e->proj, T, e->fpn, H, H, e->fpn, st));
+    } else {
+        TRY(gemm(e, e->n1, w.qg, e->proj, T, 2 * qd, H, H, e->fpn, st));
+        TRY(gemm(e, e->n1, w.k, e->proj + 2 * qd, T, he, H, H, e->fpn, st));
+        TRY(gemm(e, e->n1, w.v, e->proj + 2 * qd + he, T, he, H, H, e->fpn, st));
+    }
+    TRY(wb_qk_prep(e->proj, e->fpn, w.qn, w.kn, e->cosv, e->sinv, rope_pos, kv_pos, seq_ids, bt, bpr, e->qh, e->gate, kp, vp, T, c.q_heads,
+                   c.kv_heads, c.head_dim, c.rot_dim, c.rms_eps, st));
+    float q_scale = 1.0f / sqrtf((float)c.head_dim);
+    TRY(wb_attn_verify(e->qh, kp, vp, bt, seq_ids, kv_pos, row_start, row_count, e->gate, e->attn, q_scale, bpr, 16, c.q_heads, c.kv_heads,
+                       c.head_dim, n_spans, max_count, max_ctx, seg_pages, e->attn_scratch, e->attn_scratch_bytes, st));
+    e->launches += 3;
+    TRY(gemm(e, e->attn, w.o, e->o, T, H, qd, qd, H, st));
+    return WB_OK;
+}
+
+static int32_t mlp_block(Engine *e, const wein_b200_layer_weights &w, uint32_t T, cudaStream_t st) {
+    uint32_t H = e->H, II = e->II;
+    if (adjacent(w.wg, w.wu, (size_t)II * H)) {
+        TRY(gemm(e, e->n2, w.wg, e->gu, T, 2 * II, H, H, 2 * II, st));
+    } else {
+        TRY(gemm(e, e->n2, w.wg, e->gu, T, II, H, H, 2 * II, st));
+        TRY(gemm(e, e->n2, w.wu, e->gu + II, T, II, H, H, 2 * II, st));
+    }
+    TRY(wb_silu_mul_rows(e->gu, 2 * II, e->m, T, II, st));
+    e->launches++;
+    TRY(gemm(e, e->m, w.wd, e->d, T, H, II, II, H, st));
+    return WB_OK;
+}
+
+// The verify forward (run_forward, qwen.rs:3843-4153) over the T rows described by the step tables.  n_lg rows of
+// lg_rows get logits (all T when lg_all).
+static int32_t forward(Engine *e, uint32_t T, uint32_t n_spans, uint32_t max_count, uint32_t max_ctx, uint32_t n_lg, bool lg_all, cudaStream_t st) {
+    const wein_b200_model_cfg &c = e->cfg;
+    uint32_t H = e->H;
+    TRY(wein_b200_embed(e->d_tok, e->w.embed, e->x, H, T, st));
+    TRY(wein_b200_rms_norm_zc(e->x, e->w.layers[0].ln1, e->n1, T, H, c.rms_eps, st));
+    e->launches += 2;
+    uint32_t li = 0, fi = 0;
+    for (uint32_t l = 0; l < c.n_layers; l++) {
+        const wein_b200_layer_weights &w = e->w.layers[l];
+        if (c.layer_is_full[l]) {
+            TRY(full_attn_block(e, w, e->k_pool[fi], e->v_pool[fi], T, n_spans, max_count, max_ctx, e->seg_pages, e->d_pos_rows, e->d_pos_rows,
+                                e->d_seq_rows, e->d_block_table, e->bpr, e->d_row_start, e->d_row_count, st));
+            fi++;
+        } else {
+            uint32_t vh = c.lin_v_heads;
+            if (adjacent(w.qkv, w.z, (size_t)e->cd * H) && adjacent(w.z, w.a, (size_t)e->vald * H) && adjacent(w.a, w.b, (size_t)vh * H)) {
+                TRY(gemm(e, e->n1, w.qkv, e->proj, T, e->lpn, H, H, e->lpn, st));
+            } else {
+                TRY(gemm(e, e->n1, w.qkv, e->proj, T, e->cd, H, H, e->lpn, st));
+                TRY(gemm(e, e->n1, w.z, e->proj + e->cd, T, e->vald, H, H, e->lpn, st));
+                TRY(gemm(e, e->n1, w.a, e->proj + e->cd + e->vald, T, vh, H, H, e->lpn, st));
+                TRY(gemm(e, e->n1, w.b, e->proj + e->cd + e->vald + vh, T, vh, H, H, e->lpn, st));
+            }
+            TRY(wein_b200_conv_verify(e->proj, e->lpn, w.conv, e->conv_state[li], e->qkvc, e->d_row_start, e->d_row_count, e->d_in_row,
+                                      e->d_out_base, e->cd, 4, n_spans, st));
+            TRY(wein_b200_gdn_verify(e->qkvc, e->qkvc + e->keyd, e->qkvc + 2 * e->keyd, e->cd, e->cd, e->cd, e->proj + e->cd + e->vald,
+                                     e->proj + e->cd + e->vald + vh, e->lpn, w.a_log, w.dt_bias, e->lin_state[li], c.state_f32, e->core,
+                                     e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base, nullptr, n_spans, c.lin_k_heads, vh, 128, 128,
+                                     c.l2_eps, 0, st));
+            TRY(wb_rms_norm_gated_rows(e->core, e->proj + e->cd, e->lpn, (const float *)w.norm, e->normed, T, vh, 128, c.rms_eps, st));
+            e->launches += 3;
+            TRY(gemm(e, e->normed, w.out, e->o, T, H, e->vald, e->vald, H, st));
+            li++;
+        }
+        TRY(wein_b200_add_norm_zc(e->x, e->o, w.ln2, e->h2, e->n2, T, H, c.rms_eps, st));
+        TRY(mlp_block(e, w, T, st));
+        bool last = l + 1 == c.n_layers;
+        TRY(wein_b200_add_norm_zc(e->h2, e->d, last ? e->w.norm_f : e->w.layers[l + 1].ln1, e->x, last ? e->n2 : e->n1, T, H, c.rms_eps, st));
+        e->launches += 2;
+    }
+    if (n_lg == 0) return WB_OK;
+    const bf16_t *src = e->n2;
+    if (!lg_all) {
+        TRY(wein_b200_embed(e->d_lg_rows, e->n2, e->lg_in, H, n_lg, st));
+        e->launches++;
+        src = e->lg_in;
+    }
+    TRY(gemm(e, src, e->w.embed, e->logits, n_lg, e->V, H, H, e->V, st));
+    return WB_OK;
+}
+
+// Draft step i of the MTP head over n batch rows (run_mtp_forward, qwen.rs:4435-4522).
+static int32_t mtp_forward(Engine *e, uint32_t n, uint32_t i, bool sampled, cudaStream_t st) {
+    const wein_b200_model_cfg &c = e->cfg;
+    uint32_t H = e->H, km = c.k_max;
+    const wein_b200_layer_weights &w = e->w.mtp_layer;
+    mtp_prep_kernel<<<(n + 127) / 128, 128, 0, st>>>(e->d_slots, slot_state(e), e->d_drafts, km, n, i, e->d_mtp_tok, e->d_mtp_rope, e->d_mtp_kvpos);
+    WB_LAUNCH_CHECK();
+    // hidden: the stashed target hidden of position pos-1 for the first draft, then the head's own normalised output
+    TRY(wb_mtp_cat(e->d_mtp_tok, 1, e->w.embed, i == 0 ? e->d_hid : e->n2, i == 0 ? e->d_slots : nullptr, e->w.mtp_pre_e, e->w.mtp_pre_h, e->cat,
+                   n, H, c.rms_eps, st));
+    TRY(gemm(e, e->cat, e->w.mtp_fc, e->x, n, H, 2 * H, 2 * H, H, st));
+    TRY(wein_b200_rms_norm_zc(e->x, w.ln1, e->n1, n, H, c.rms_eps, st));
+    e->launches += 3;
+    // each batch row is its own one-page chain: clean per round, chain-local KV slots, absolute rotary positions
+    TRY(full_attn_block(e, w, e->k_pool[e->n_full], e->v_pool[e->n_full], n, n, 1, 16, 1, e->d_mtp_rope, e->d_mtp_kvpos, e->d_iota, e->d_iota, 1,
+                        e->d_iota, e->d_ones, st));
+    TRY(wein_b200_add_norm_zc(e->x, e->o, w.ln2, e->h2, e->n2, n, H, c.rms_eps, st));
+    TRY(mlp_block(e, w, n, st));
+    TRY(wein_b200_add_norm_zc(e->h2, e->d, e->w.mtp_norm, e->x, e->n2, n, H, c.rms_eps, st));
+    e->launches += 2;
+    TRY(gemm(e, e->n2, e->w.embed, e->logits, n, e->V, H, H, e->V, st));
+    if (!sampled) {
+        TRY(wein_b200_argmax_partials(e->logits, e->d_iota, e->am_part, e->V, n, 32, st));
+        TRY(wb_argmax_finish(e->am_part, 32, e->d_drafts, km, i, n, st));
+        e->launches += 2;
+    } else {
+        FilterArgs f{};
+        f.logits = e->logits; f.rows = nullptr; f.row_seq = e->d_slots; f.rows_per_seq = 1; f.temp = e->d_temp; f.top_k = e->d_top_k; f.top_p = e->d_top_p;
+        f.n = e->V; f.s = n; f.out_ids = e->q_ids; f.out_probs = e->q_probs; f.out_n = e->q_n; f.out_mul = km; f.out_off = i;
+        f.sample_out = e->d_drafts; f.sample_mul = km; f.sample_off = i; f.seed = e->d_seed; f.round = e->d_round; f.position = i;
+        TRY(wb_topk_filter_args(f, st));
+        e->launches++;
+    }
+    return WB_OK;
+}
+
+static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32_t max_ctx, cudaStream_t st) {
+    const uint32_t P = k + 1, T = n * P, km = e->cfg.k_max ? e->cfg.k_max : 1;
+    for (uint32_t i = 0; i < k; i++) TRY(mtp_forward(e, n, i, sampled, st));
+    verify_prep_kernel<<<(n + 127) / 128, 128, 0, st>>>(e->d_slots, slot_state(e), e->d_drafts, km, n, P, e->rows_per_slot, e->P, e->d_tok,
+                                                      e->d_pos_rows, e->d_seq_rows, e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base,
+                                                      e->d_lg_rows);
+    WB_LAUNCH_CHECK();
+    e->launches += 1 + k;
+    TRY(forward(e, T, n, P, max_ctx, T, true, st));
+    AcceptArgs a{};
+    a.drafts = e->d_drafts; a.draft_stride = km; a.B = n; a.k = k; a.accept_len = e->d_accept_len; a.out_tokens = e->d_out_tokens; a.target = e->d_target;
+    if (!sampled) {
+        TRY(wein_b200_argmax_partials(e->logits, e->d_lg_rows, e->am_part, e->V, T, 32, st));
+        a.am_part = (const uint64_t *)e->am_part; a.am_split = 32;
+    } else {
+        FilterArgs f{};
+        f.logits = e->logits; f.rows = nullptr; f.row_seq = e->d_seq_rows; f.rows_per_seq = 1; f.temp = e->d_temp; f.top_k = e->d_top_k; f.top_p = e->d_top_p;
+        f.n = e->V; f.s = T; f.out_ids = e->p_ids; f.out_probs = e->p_probs; f.out_n = e->p_n; f.out_mul = 1; f.out_off = 0;
+        TRY(wb_topk_filter_args(f, st));
+        a.p_ids = e->p_ids; a.p_probs = e->p_probs; a.p_n = e->p_n; a.q_ids = e->q_ids; a.q_probs = e->q_probs; a.q_n = e->q_n;
+        a.temp = e->d_temp; a.seed = e->d_seed; a.round = e->d_round; a.slot_of = e->d_slots;
+    }
+    TRY(wb_accept_args(a, st));
+    commit_kernel<<<n, 128, 0, st>>>(e->d_slots, slot_state(e), e->d_accept_len, e->d_out_tokens, e->d_out_base, e->x, P, k, e->H);
+    WB_LAUNCH_CHECK();
+    e->launches += 3;
+    return WB_OK;
+}
+
+static int32_t set_slots(Engine *e, uint32_t n, const uint32_t *host_slots, cudaStream_t st) {
+    bool same = e->h_slots_cached.size() == n;
+    for (uint32_t i = 0; same && i < n; i++) same = e->h_slots_cached[i] == host_slots[i];
+    if (same) return WB_OK;
+    for (uint32_t i = 0; i < n; i++) {
+        WB_CHECK_ARG(host_slots[i] < e->cfg.max_seqs, "slot %u out of range", host_slots[i]);
+        for (uint32_t j = 0; j < i; j++) WB_CHECK_ARG(host_slots[j] != host_slots[i], "slot %u listed twice", host_slots[i]);
+    }
+    CUDA_TRY(cudaStreamSynchronize(st));  // the pinned staging words may still be in flight from an earlier call
+    memcpy(e->h_stage, host_slots, (size_t)n * 4);
+    CUDA_TRY(cudaMemcpyAsync(e->d_slots, e->h_stage, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+    e->h_slots_cached.assign(host_slots, host_slots + n);
+    return WB_OK;
+}
+
+extern "C" int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, uint32_t ctx_bound,
+                                              uint32_t use_graph, void *stream) {
+    WB_CHECK_ARG(e && host_slots && n >= 1 && n <= e->cfg.max_seqs, "spec_step: batch of %u outside 1..max_seqs", n);
+    WB_CHECK_ARG(k <= e->cfg.k_max, "spec_step: k = %u exceeds k_max = %u", k, e->cfg.k_max);
+    WB_CHECK_ARG(k == 0 || e->cfg.has_mtp, "spec_step: drafting needs the MTP head");
+    WB_CHECK_ARG(ctx_bound >= k + 1 && ctx_bound <= e->cfg.max_pos, "spec_step: ctx_bound %u outside k+1..max_pos", ctx_bound);
+    cudaStream_t st = (cudaStream_t)stream;
+    WB_CHECK_ARG(!use_graph || st != nullptr, "spec_step: a CUDA graph cannot be captured on the default stream; pass a created stream");
+    TRY(set_slots(e, n, host_slots, st));
+    bool sampled = false;
+    for (uint32_t i = 0; i < n; i++) sampled |= e->h_temp[host_slots[i]] > 0.0f;
+    // the context bound only sizes the attention grid: round it up to a bucket so graphs are reused
+    uint32_t bucket = 256;
+    while (bucket < ctx_bound) bucket *= 2;
+    if (bucket > e->bpr * 16) bucket = e->bpr * 16;
+    if (!use_graph) {
+        e->launches = 0;
+        TRY(run_round(e, n, k, sampled, bucket, st));
+        e->last_launches = e->launches;
+        return WB_OK;
+    }
+    auto key = std::make_tuple(n, k, (uint32_t)sampled, bucket);
+    auto it = e->graphs.find(key);
+    if (it == e->graphs.end()) {
+        cudaGraph_t g = nullptr;
+        e->launches = 0;
+        CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
+        int32_t rc = run_round(e, n, k, sampled, bucket, st);
+        cudaError_t ce = cudaStreamEndCapture(st, &g);
+        if (rc != WB_OK) { if (g) cudaGraphDestroy(g); return rc; }
+        if (ce != cudaSuccess) { wb_set_error("spec_step: stream capture failed: %s", cudaGetErrorString(ce)); return WB_ERR_CUDA; }
+        cudaGraphExec_t ge = nullptr;
+        ce = cudaGraphInstantiate(&ge, g, 0);
+        cudaGraphDestroy(g);
+        if (ce != cudaSuccess) { wb_set_error("spec_step: graph instantiation failed: %s", cudaGetErrorString(ce)); return WB_ERR_CUDA; }
+        it = e->graphs.emplace(key, ge).first;
+        e->named["graph_launches:" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string((int)sampled) + ":" + std::to_string(bucket)] =
+            {nullptr, e->launches};
+    }
+    e->last_launches = (uint32_t)e->named["graph_launches:" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string((int)sampled) + ":" + std::to_string(bucket)].second;
+    CUDA_TRY(cudaGraphLaunch(it->second, st));
+    return WB_OK;
+}
+
+extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, const uint32_t *host_tokens,
+                                            const uint32_t *host_lens, void *stream) {
+    WB_CHECK_ARG(e && host_slots && host_tokens && host_lens && n >= 1 && n <= e->cfg.max_seqs, "prefill: bad batch");
+    cudaStream_t st = (cudaStream_t)stream;
+    TRY(set_slots(e, n, host_slots, st));
+    std::vector<uint64_t> off(n + 1, 0);
+    uint32_t max_len = 0;
+    bool sampled = false;
+    for (uint32_t i = 0; i < n; i++) {
+        WB_CHECK_ARG(host_lens[i] >= 1 && host_lens[i] < e->cfg.max_pos, "prefill: prompt of %u tokens outside 1..max_pos-1", host_lens[i]);
+        off[i + 1] = off[i] + host_lens[i];
+        max_len = host_lens[i] > max_len ? host_lens[i] : max_len;
+        sampled |= e->h_temp[host_slots[i]] > 0.0f;
+    }
+    for (uint64_t t = 0; t < off[n]; t++) WB_CHECK_ARG(host_tokens[t] < e->V, "prefill: token id %u outside the vocabulary", host_tokens[t]);
+    const uint32_t P = e->P;
+    std::vector<uint32_t> done(n, 0);
+    uint32_t *h_cnt = e->h_stage, *h_last = e->h_stage + n, *h_tok = e->h_stage + 2 * n;
+    for (uint32_t base = 0; base < max_len; base += P) {
+        uint32_t T = 0, n_lg = 0;
+        CUDA_TRY(cudaStreamSynchronize(st));
+        for (uint32_t i = 0; i < n; i++) {
+            uint32_t rem = host_lens[i] - done[i], c = rem < P ? rem : P;
+            h_cnt[i] = c;
+            h_last[i] = (c > 0 && c == rem) ? 1u : 0u;
+            n_lg += h_last[i];
+            for (uint32_t j = 0; j < c; j++) h_tok[T++] = host_tokens[off[i] + done[i] + j];
+            done[i] += c;
+        }
+        uint32_t *h_lgslot = h_tok + T;
+        for (uint32_t i = 0, q = 0; i < n; i++) if (h_last[i]) h_lgslot[q++] = host_slots[i];
+        if (n_lg) CUDA_TRY(cudaMemcpyAsync(e->d_mtp_tok, h_lgslot, (size_t)n_lg * 4, cudaMemcpyHostToDevice, st));
+        CUDA_TRY(cudaMemcpyAsync(e->d_cnt_in, h_cnt, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+        CUDA_TRY(cudaMemcpyAsync(e->d_last_in, h_last, (size_t)n * 4, cudaMemcpyHostToDevice, st));
+        CUDA_TRY(cudaMemcpyAsync(e->d_tok_in, h_tok, (size_t)T * 4, cudaMemcpyHostToDevice, st));
+        prefill_prep_kernel<<<1, 1, 0, st>>>(e->d_slots, slot_state(e), e->d_cnt_in, e->d_tok_in, e->d_last_in, n, e->rows_per_slot, e->P, e->d_tok,
+                                             e->d_pos_rows, e->d_seq_rows, e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base,
+                                             e->d_lg_rows, e->d_lg_of);
+        WB_LAUNCH_CHECK();
+        uint32_t max_ctx = base + P < e->bpr * 16 ? base + P : e->bpr * 16;
+        TRY(forward(e, T, n, P, max_ctx, n_lg, false, st));
+        if (n_lg > 0) {
+            if (!sampled) {
+                TRY(wein_b200_argmax_partials(e->logits, e->d_iota, e->am_part, e->V, n_lg, 32, st));
+                TRY(wb_argmax_finish(e->am_part, 32, e->d_first_tok, 1, 0, n_lg, st));
+            } else {
+                // the first token of a sequence: drawn from the filtered distribution of the last prompt position
+                FilterArgs f{};
+                f.logits = e->logits; f.rows = nullptr; f.rows_per_seq = 1; f.temp = e->d_temp; f.top_k = e->d_top_k; f.top_p = e->d_top_p;
+                f.n = e->V; f.s = n_lg; f.out_ids = e->p_ids; f.out_probs = e->p_probs; f.out_n = e->p_n; f.out_mul = 1; f.out_off = 0;
+                f.sample_out = e->d_first_tok; f.sample_mul = 1; f.sample_off = 0; f.seed = e->d_seed; f.round = e->d_round; f.position = 0;
+                f.row_seq = e->d_mtp_tok;  // slot of each finishing sequence, uploaded with the chunk tables
+                TRY(wb_topk_filter_args(f, st));
+            }
+        }
+        prefill_commit_kernel<<<n, 128, 0, st>>>(e->d_slots, slot_state(e), e->d_cnt_in, e->d_row_start, e->d_out_base, e->d_lg_of, e->d_first_tok,
+                                                e->x, e->H);
+        WB_LAUNCH_CHECK();
+    }
+    CUDA_TRY(cudaStreamSynchronize(st));
+    return WB_OK;
+}
+
+extern "C" int32_t wein_b200_engine_read(wein_b200_engine *e, uint32_t slot, uint32_t *host_tokens, uint32_t cap, uint32_t *host_n_tokens,
+                                         uint32_t *host_pos, uint64_t *host_stats3, void *stream) {
+    WB_CHECK_ARG(e && slot < e->cfg.max_seqs, "engine_read: slot out of range");
+    cudaStream_t st = (cudaStream_t)stream;
+    CUDA_TRY(cudaStreamSynchronize(st));
+    uint32_t oc = 0, pos = 0;
+    CUDA_TRY(cudaMemcpy(&oc, e->d_out_count + slot, 4, cudaMemcpyDeviceToHost));
+    CUDA_TRY(cudaMemcpy(&pos, e->d_pos + slot, 4, cudaMemcpyDeviceToHost));
+    if (host_n_tokens) *host_n_tokens = oc;
+    if (host_pos) *host_pos = pos;
+    if (host_stats3) CUDA_TRY(cudaMemcpy(host_stats3, e->d_stats + (size_t)slot * 3, 24, cudaMemcpyDeviceToHost));
+    if (host_tokens && cap) {
+        WB_CHECK_ARG(oc <= RING_CAP, "engine_read: %u tokens emitted, the ring keeps the last %u", oc, RING_CAP);
+        uint32_t nread = oc < cap ? oc : cap;
+        CUDA_TRY(cudaMemcpy(host_tokens, e->d_ring + (size_t)slot * RING_CAP, (size_t)nread * 4, cudaMemcpyDeviceToHost));
+    }
+    return WB_OK;
+}

@@ -21,6 +21,7 @@
 #include <cublasLt.h>
 #include <mutex>
 #include "common.cuh"
+#include "internal.h"
 
 __device__ __forceinline__ uint4 ld_stream(const void *p) {
     uint4 v;
@@ -194,12 +195,21 @@ struct LtState {
 };
 static LtState g_lt;
 
-static int32_t lt_gemm(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, cudaStream_t st) {
-    std::lock_guard<std::mutex> lk(g_lt.mu);
+static int32_t lt_init() {
     if (!g_lt.h) {
         if (cublasLtCreate(&g_lt.h) != CUBLAS_STATUS_SUCCESS) { wb_set_error("cublasLtCreate failed"); return WB_ERR_CUDA; }
         if (cudaMalloc(&g_lt.ws, g_lt.ws_bytes) != cudaSuccess) { wb_set_error("cuBLASLt workspace allocation failed"); return WB_ERR_CUDA; }
     }
+    return WB_OK;
+}
+int32_t wb_gemm_warmup() {
+    std::lock_guard<std::mutex> lk(g_lt.mu);
+    return lt_init();
+}
+
+static int32_t lt_gemm(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, cudaStream_t st) {
+    std::lock_guard<std::mutex> lk(g_lt.mu);
+    if (lt_init() != WB_OK) return WB_ERR_CUDA;
     // column-major view: C^T [n x m] = W [n x k] * A^T [k x m]  ->  op(W) = T on the stored k x n, op(A) = N on k x m
     cublasLtMatmulDesc_t desc = nullptr;
     cublasLtMatrixLayout_t la = nullptr, lb = nullptr, lc = nullptr;

@@ -5,6 +5,7 @@
 // Each kernel cites the reference function whose arithmetic order it keeps.
 // Compiled with -fmad=false: a*b+c is two roundings unless fmaf() is written.
 #include "common.cuh"
+#include "internal.h"
 
 // ------------------------------------------------------------------ embed
 // out[t, :] = w[ids[t], :]  (reference.rs:298-305).  One block per row.
