@@ -222,11 +222,13 @@ int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, const uint32_t
 /* One round for the slots host_slots[0..n): draft k tokens with the MTP head (k = 0: plain decode step), verify the k+1
  * positions in one forward, accept on the device, commit (position, pending token, state row, hidden, token ring).
  * ctx_bound = an upper bound of (position + k + 1) over the batch (sizes the attention grid).  use_graph != 0 replays a
- * CUDA graph cached per (n, k, sampling mode, ctx bucket).  No host synchronisation. */
+ * CUDA graph cached per (n, k, sampling mode, ctx bucket); bit 1 of use_graph forces the upload of the slot table even
+ * when it is unchanged.  No host synchronisation unless the slot table changes. */
 int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, uint32_t ctx_bound,
                                    uint32_t use_graph, void *stream);
 
-/* Synchronises the stream and reads a slot: tokens emitted since admission (up to cap), position, and the counters of
+/* Synchronises the stream and reads a slot: the most recent min(cap, emitted) tokens (oldest first), the number of
+ * tokens emitted since admission (host_n_tokens), the position, and the counters of
  * spec_stats() (crates/wein-exec/src/qwen.rs:4257-4259): rounds, drafts, accepted. */
 int32_t wein_b200_engine_read(wein_b200_engine *e, uint32_t slot, uint32_t *host_tokens, uint32_t cap, uint32_t *host_n_tokens,
                               uint32_t *host_pos, uint64_t *host_stats3, void *stream);

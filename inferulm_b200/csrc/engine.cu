@@ -523,8 +523,8 @@ static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32
     return WB_OK;
 }
 
-static int32_t set_slots(Engine *e, uint32_t n, const uint32_t *host_slots, cudaStream_t st) {
-    bool same = e->h_slots_cached.size() == n;
+static int32_t set_slots(Engine *e, uint32_t n, const uint32_t *host_slots, cudaStream_t st, bool force = false) {
+    bool same = !force && e->h_slots_cached.size() == n;
     for (uint32_t i = 0; same && i < n; i++) same = e->h_slots_cached[i] == host_slots[i];
     if (same) return WB_OK;
     for (uint32_t i = 0; i < n; i++) {
@@ -546,7 +546,8 @@ extern "C" int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, c
     WB_CHECK_ARG(ctx_bound >= k + 1 && ctx_bound <= e->cfg.max_pos, "spec_step: ctx_bound %u outside k+1..max_pos", ctx_bound);
     cudaStream_t st = (cudaStream_t)stream;
     WB_CHECK_ARG(!use_graph || st != nullptr, "spec_step: a CUDA graph cannot be captured on the default stream; pass a created stream");
-    TRY(set_slots(e, n, host_slots, st));
+    TRY(set_slots(e, n, host_slots, st, (use_graph & 2u) != 0));
+    use_graph &= 1u;
     bool sampled = false;
     for (uint32_t i = 0; i < n; i++) sampled |= e->h_temp[host_slots[i]] > 0.0f;
     // the context bound only sizes the attention grid: round it up to a bucket so graphs are reused
@@ -657,9 +658,13 @@ extern "C" int32_t wein_b200_engine_read(wein_b200_engine *e, uint32_t slot, uin
     if (host_pos) *host_pos = pos;
     if (host_stats3) CUDA_TRY(cudaMemcpy(host_stats3, e->d_stats + (size_t)slot * 3, 24, cudaMemcpyDeviceToHost));
     if (host_tokens && cap) {
-        WB_CHECK_ARG(oc <= RING_CAP, "engine_read: %u tokens emitted, the ring keeps the last %u", oc, RING_CAP);
+        // the most recent min(cap, emitted, ring size) tokens, oldest first
         uint32_t nread = oc < cap ? oc : cap;
-        CUDA_TRY(cudaMemcpy(host_tokens, e->d_ring + (size_t)slot * RING_CAP, (size_t)nread * 4, cudaMemcpyDeviceToHost));
+        if (nread > RING_CAP) nread = RING_CAP;
+        uint32_t start = (oc - nread) % RING_CAP, first = nread < RING_CAP - start ? nread : RING_CAP - start;
+        const uint32_t *ring = e->d_ring + (size_t)slot * RING_CAP;
+        if (first) CUDA_TRY(cudaMemcpy(host_tokens, ring + start, (size_t)first * 4, cudaMemcpyDeviceToHost));
+        if (nread > first) CUDA_TRY(cudaMemcpy(host_tokens + first, ring, (size_t)(nread - first) * 4, cudaMemcpyDeviceToHost));
     }
     return WB_OK;
 }

@@ -219,7 +219,7 @@ class Engine:
         stats = (C.c_uint64 * 3)()
         check(self.lib.wein_b200_engine_read(self.h, C.c_uint32(slot), toks.ctypes.data_as(C.c_void_p), C.c_uint32(cap), C.byref(n),
                                              C.byref(pos), stats, self._stream()))
-        return toks[: min(n.value, cap)].copy(), pos.value, dict(rounds=stats[0], drafts=stats[1], accepted=stats[2])
+        return toks[: min(n.value, cap)].copy(), pos.value, dict(rounds=int(stats[0]), drafts=int(stats[1]), accepted=int(stats[2]))
 
     def last_launches(self):
         return int(self.lib.wein_b200_engine_last_launches(self.h))
