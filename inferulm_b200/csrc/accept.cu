@@ -92,6 +92,7 @@ __device__ __forceinline__ void scan_row(const bf16_t *row, uint32_t n, F fn) {
 
 // One CTA of 1024 threads per row.
 __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P) {
+    PDL_ENTRY();
     __shared__ uint32_t lm[1024];
     __shared__ uint32_t hist[256];
     __shared__ uint32_t warp_cnt[32];
@@ -258,6 +259,7 @@ __device__ __forceinline__ uint32_t argmax_from_parts(const uint64_t *part, uint
 
 // One warp per sequence.
 __global__ void __launch_bounds__(32) accept_kernel(const AcceptParams P) {
+    PDL_ENTRY();
     __shared__ float r_s[DIST_CAP];
     const uint32_t b = blockIdx.x, lane = threadIdx.x;
     const uint32_t k = P.k, rows = k + 1;
@@ -349,7 +351,7 @@ int32_t wb_topk_filter(const FilterParams &p, cudaStream_t st) {
     WB_CHECK_ARG(p.row_seq || p.rows_per_seq > 0, "topk_filter: rows_per_seq must be positive");
     WB_CHECK_ARG(!p.sample_out || (p.seed && p.round), "topk_filter: sampling needs seed and round");
     if (p.s == 0) return WB_OK;
-    topk_filter_kernel<<<p.s, 1024, 0, st>>>(p);
+    WB_LAUNCH((topk_filter_kernel), p.s, 1024, 0, st, p);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }
@@ -360,7 +362,7 @@ int32_t wb_accept(const AcceptParams &p, cudaStream_t st) {
                  "accept: sampled mode needs both distributions, seeds and rounds");
     WB_CHECK_ARG(p.k <= 15 && p.draft_stride >= p.k, "accept: k = %u outside 0..15 or draft stride too small", p.k);
     if (p.B == 0) return WB_OK;
-    accept_kernel<<<p.B, 32, 0, st>>>(p);
+    WB_LAUNCH((accept_kernel), p.B, 32, 0, st, p);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }

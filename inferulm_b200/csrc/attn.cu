@@ -59,6 +59,7 @@ __device__ __forceinline__ uint32_t tile_off(uint32_t r, uint32_t ch) { return r
 
 template <int HD>
 __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
+    PDL_ENTRY();
     constexpr int KS = HD / 16, ND = HD / 8, CH = HD / 8;       // k-steps of QK^T, d n-tiles of PV, 16-byte chunks per row
     constexpr int KL = 4;                                        // the four warps take the segment's pages round-robin
     constexpr int PAGE_BYTES = ATT_PAGE * HD * 2;
@@ -235,6 +236,7 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
 // Merge of the segments in index order: one block per (span, kv head, query row), one thread per 4 output dims.
 template <int HD>
 __global__ void attn_combine_kernel(const AttnParams P) {
+    PDL_ENTRY();
     const uint32_t row = blockIdx.x, kvh = blockIdx.y, span = blockIdx.z;
     const uint32_t group = P.q_heads / P.kv_heads;
     const uint32_t t0 = P.row_start ? P.row_start[span] : span;
@@ -282,10 +284,10 @@ static int32_t attn_launch(const AttnParams &p, cudaStream_t st) {
         attr_done = true;
     }
     dim3 grid(p.max_segs, p.kv_heads, p.n_spans * p.n_mtiles);
-    attn_verify_kernel<HD><<<grid, 128, smem, st>>>(p);
+    WB_LAUNCH((attn_verify_kernel<HD>), grid, 128, smem, st, p);
     WB_LAUNCH_CHECK();
     dim3 g2(16 * p.n_mtiles, p.kv_heads, p.n_spans);
-    attn_combine_kernel<HD><<<g2, HD / 4, 0, st>>>(p);
+    WB_LAUNCH((attn_combine_kernel<HD>), g2, HD / 4, 0, st, p);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }

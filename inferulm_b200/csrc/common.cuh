@@ -116,6 +116,28 @@ __device__ __forceinline__ float block_sum_tree(float v, float *smem /* >= 33 fl
     return smem[32];
 }
 
+// Programmatic dependent launch (sm_90+): a kernel launched with the programmatic-serialization attribute may start
+// while its predecessor in the stream is still running.  Every kernel of this library begins with PDL_ENTRY(): it lets
+// its own successor start early, then waits until the predecessor grid has completed and its writes are visible.  Work
+// that touches no produced data (weight prefetch) may be placed between the two.  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+#define PDL_ENTRY() do { pdl_trigger(); pdl_wait(); } while (0)
+
+// Host-side launch helper: every kernel goes through cudaLaunchKernelEx so the attribute can be switched globally.
+extern bool g_wb_pdl;
+template <typename... KArgs, typename... Args>
+static inline cudaError_t wb_launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at; cfg.numAttrs = g_wb_pdl ? 1 : 0;
+    return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
+}
+#define WB_LAUNCH(kern, grid, block, smem, st, ...) wb_launch_k(kern, grid, block, smem, st, __VA_ARGS__)
+
 // Host-side error plumbing (defined in capi.cu)
 void wb_set_error(const char *fmt, ...);
 const char *wein_b200_last_error_buf();

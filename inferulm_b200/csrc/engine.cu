@@ -105,6 +105,7 @@ __global__ void verify_prep_kernel(const uint32_t *__restrict__ slots, SlotState
                                    uint32_t n, uint32_t P, uint32_t rows_per_slot, uint32_t bankrows, uint32_t *tok, uint32_t *pos_rows,
                                    uint32_t *seq_rows, uint32_t *row_start, uint32_t *row_count, uint32_t *in_row, uint32_t *out_base,
                                    uint32_t *lg_rows) {
+    PDL_ENTRY();
     uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n) return;
     uint32_t slot = slots[b], p0 = S.pos[slot];
@@ -126,6 +127,7 @@ __global__ void verify_prep_kernel(const uint32_t *__restrict__ slots, SlotState
 __global__ void commit_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ accept_len,
                               const uint32_t *__restrict__ out_tokens, const uint32_t *__restrict__ out_base, const bf16_t *__restrict__ x,
                               uint32_t P, uint32_t k, uint32_t H) {
+    PDL_ENTRY();
     uint32_t b = blockIdx.x, slot = slots[b], a = accept_len[b];
     const bf16_t *src = x + (size_t)(b * P + a) * H;
     bf16_t *dst = S.hid + (size_t)slot * H;
@@ -150,6 +152,7 @@ __global__ void prefill_prep_kernel(const uint32_t *__restrict__ slots, SlotStat
                                     const uint32_t *__restrict__ tok_in, const uint32_t *__restrict__ last, uint32_t n, uint32_t rows_per_slot,
                                     uint32_t bankrows, uint32_t *tok, uint32_t *pos_rows, uint32_t *seq_rows, uint32_t *row_start,
                                     uint32_t *row_count, uint32_t *in_row, uint32_t *out_base, uint32_t *lg_rows, uint32_t *lg_of) {
+    PDL_ENTRY();
     if (threadIdx.x != 0 || blockIdx.x != 0) return;
     uint32_t r = 0, nl = 0;
     for (uint32_t b = 0; b < n; b++) {
@@ -167,6 +170,7 @@ __global__ void prefill_commit_kernel(const uint32_t *__restrict__ slots, SlotSt
                                       const uint32_t *__restrict__ row_start, const uint32_t *__restrict__ out_base,
                                       const uint32_t *__restrict__ lg_of, const uint32_t *__restrict__ first_tok, const bf16_t *__restrict__ x,
                                       uint32_t H) {
+    PDL_ENTRY();
     uint32_t b = blockIdx.x, slot = slots[b], c = cnt[b];
     if (c == 0) return;
     const bf16_t *src = x + (size_t)(row_start[b] + c - 1) * H;
@@ -189,6 +193,7 @@ __global__ void prefill_commit_kernel(const uint32_t *__restrict__ slots, SlotSt
 // Inputs of draft step i: token = pending (i = 0) or the previous draft; rotary position absolute, KV slot chain-local.
 __global__ void mtp_prep_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ drafts, uint32_t k_max,
                                 uint32_t n, uint32_t i, uint32_t *tok, uint32_t *rope_pos, uint32_t *kv_pos) {
+    PDL_ENTRY();
     uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n) return;
     uint32_t slot = slots[b];
@@ -198,6 +203,7 @@ __global__ void mtp_prep_kernel(const uint32_t *__restrict__ slots, SlotState S,
 }
 __global__ void slot_init_kernel(SlotState S, uint32_t slot, uint32_t row0, float *temp, uint32_t *top_k, float *top_p, uint64_t *seed,
                                  float t, uint32_t k, float p, uint64_t sd) {
+    PDL_ENTRY();
     S.pos[slot] = 0; S.pending[slot] = 0; S.state_row[slot] = row0; S.bank[slot] = 0; S.out_count[slot] = 0; S.round[slot] = 0;
     S.stats[slot * 3] = S.stats[slot * 3 + 1] = S.stats[slot * 3 + 2] = 0;
     temp[slot] = t; top_k[slot] = k; top_p[slot] = p; seed[slot] = sd;
@@ -354,7 +360,7 @@ extern "C" int32_t wein_b200_engine_admit(wein_b200_engine *e, uint32_t slot, co
         CUDA_TRY(cudaMemsetAsync((char *)e->conv_state[i] + (size_t)row0 * conv_row, 0, conv_row, st));
     }
     CUDA_TRY(cudaMemcpyAsync(e->d_block_table + (size_t)slot * e->bpr, host_pages, (size_t)n_pages * 4, cudaMemcpyHostToDevice, st));
-    slot_init_kernel<<<1, 1, 0, st>>>(slot_state(e), slot, row0, e->d_temp, e->d_top_k, e->d_top_p, e->d_seed, temp, top_k, top_p, seed);
+    WB_LAUNCH((slot_init_kernel), 1, 1, 0, st, slot_state(e), slot, row0, e->d_temp, e->d_top_k, e->d_top_p, e->d_seed, temp, top_k, top_p, seed);
     WB_LAUNCH_CHECK();
     CUDA_TRY(cudaStreamSynchronize(st));  // host_pages may be pageable memory
     e->h_temp[slot] = temp;
@@ -393,6 +399,13 @@ static int32_t full_attn_block(Engine *e, const wein_b200_layer_weights &w, void
 
 static int32_t mlp_block(Engine *e, const wein_b200_layer_weights &w, uint32_t T, cudaStream_t st) {
     uint32_t H = e->H, II = e->II;
+    if (T <= 32 && adjacent(w.wg, w.wu, (size_t)II * H)) {
+        // gate|up projection with the SwiGLU activation in the epilogue: one launch, no [T, 2*inter] round trip
+        e->launches++;
+        TRY(wb_gemm_swiglu(e->n2, w.wg, e->m, T, II, H, H, II, e->gemm_scratch, e->gemm_scratch_bytes, st));
+        TRY(gemm(e, e->m, w.wd, e->d, T, H, II, II, H, st));
+        return WB_OK;
+    }
     if (adjacent(w.wg, w.wu, (size_t)II * H)) {
         TRY(gemm(e, e->n2, w.wg, e->gu, T, 2 * II, H, H, 2 * II, st));
     } else {
@@ -463,7 +476,7 @@ static int32_t mtp_forward(Engine *e, uint32_t n, uint32_t i, bool sampled, cuda
     const wein_b200_model_cfg &c = e->cfg;
     uint32_t H = e->H, km = c.k_max;
     const wein_b200_layer_weights &w = e->w.mtp_layer;
-    mtp_prep_kernel<<<(n + 127) / 128, 128, 0, st>>>(e->d_slots, slot_state(e), e->d_drafts, km, n, i, e->d_mtp_tok, e->d_mtp_rope, e->d_mtp_kvpos);
+    WB_LAUNCH((mtp_prep_kernel), (n + 127) / 128, 128, 0, st, e->d_slots, slot_state(e), e->d_drafts, km, n, i, e->d_mtp_tok, e->d_mtp_rope, e->d_mtp_kvpos);
     WB_LAUNCH_CHECK();
     // hidden: the stashed target hidden of position pos-1 for the first draft, then the head's own normalised output
     TRY(wb_mtp_cat(e->d_mtp_tok, 1, e->w.embed, i == 0 ? e->d_hid : e->n2, i == 0 ? e->d_slots : nullptr, e->w.mtp_pre_e, e->w.mtp_pre_h, e->cat,
@@ -497,7 +510,7 @@ static int32_t mtp_forward(Engine *e, uint32_t n, uint32_t i, bool sampled, cuda
 static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32_t max_ctx, cudaStream_t st) {
     const uint32_t P = k + 1, T = n * P, km = e->cfg.k_max ? e->cfg.k_max : 1;
     for (uint32_t i = 0; i < k; i++) TRY(mtp_forward(e, n, i, sampled, st));
-    verify_prep_kernel<<<(n + 127) / 128, 128, 0, st>>>(e->d_slots, slot_state(e), e->d_drafts, km, n, P, e->rows_per_slot, e->P, e->d_tok,
+    WB_LAUNCH((verify_prep_kernel), (n + 127) / 128, 128, 0, st, e->d_slots, slot_state(e), e->d_drafts, km, n, P, e->rows_per_slot, e->P, e->d_tok,
                                                       e->d_pos_rows, e->d_seq_rows, e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base,
                                                       e->d_lg_rows);
     WB_LAUNCH_CHECK();
@@ -517,7 +530,7 @@ static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32
         a.temp = e->d_temp; a.seed = e->d_seed; a.round = e->d_round; a.slot_of = e->d_slots;
     }
     TRY(wb_accept_args(a, st));
-    commit_kernel<<<n, 128, 0, st>>>(e->d_slots, slot_state(e), e->d_accept_len, e->d_out_tokens, e->d_out_base, e->x, P, k, e->H);
+    WB_LAUNCH((commit_kernel), n, 128, 0, st, e->d_slots, slot_state(e), e->d_accept_len, e->d_out_tokens, e->d_out_base, e->x, P, k, e->H);
     WB_LAUNCH_CHECK();
     e->launches += 3;
     return WB_OK;
@@ -618,7 +631,7 @@ extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, con
         CUDA_TRY(cudaMemcpyAsync(e->d_cnt_in, h_cnt, (size_t)n * 4, cudaMemcpyHostToDevice, st));
         CUDA_TRY(cudaMemcpyAsync(e->d_last_in, h_last, (size_t)n * 4, cudaMemcpyHostToDevice, st));
         CUDA_TRY(cudaMemcpyAsync(e->d_tok_in, h_tok, (size_t)T * 4, cudaMemcpyHostToDevice, st));
-        prefill_prep_kernel<<<1, 1, 0, st>>>(e->d_slots, slot_state(e), e->d_cnt_in, e->d_tok_in, e->d_last_in, n, e->rows_per_slot, e->P, e->d_tok,
+        WB_LAUNCH((prefill_prep_kernel), 1, 1, 0, st, e->d_slots, slot_state(e), e->d_cnt_in, e->d_tok_in, e->d_last_in, n, e->rows_per_slot, e->P, e->d_tok,
                                              e->d_pos_rows, e->d_seq_rows, e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base,
                                              e->d_lg_rows, e->d_lg_of);
         WB_LAUNCH_CHECK();
@@ -638,7 +651,7 @@ extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, con
                 TRY(wb_topk_filter_args(f, st));
             }
         }
-        prefill_commit_kernel<<<n, 128, 0, st>>>(e->d_slots, slot_state(e), e->d_cnt_in, e->d_row_start, e->d_out_base, e->d_lg_of, e->d_first_tok,
+        WB_LAUNCH((prefill_commit_kernel), n, 128, 0, st, e->d_slots, slot_state(e), e->d_cnt_in, e->d_row_start, e->d_out_base, e->d_lg_of, e->d_first_tok,
                                                 e->x, e->H);
         WB_LAUNCH_CHECK();
     }

@@ -14,6 +14,7 @@ __global__ void qk_prep_kernel(const bf16_t *__restrict__ qgkv, uint32_t ld, con
                                const uint32_t *__restrict__ kv_pos, const uint32_t *__restrict__ seq_ids,
                                const uint32_t *__restrict__ block_table, uint32_t bpr, bf16_t *__restrict__ qh, bf16_t *__restrict__ gate,
                                bf16_t *k_pool, bf16_t *v_pool, uint32_t q_heads, uint32_t kv_heads, uint32_t rot_dim, float eps) {
+    PDL_ENTRY();
     __shared__ float red[33];
     __shared__ bf16_t nrm[256];
     const uint32_t hd = blockDim.x, t = blockIdx.y, unit = blockIdx.x, i = threadIdx.x;
@@ -61,7 +62,7 @@ int32_t wb_qk_prep(const void *qgkv, uint32_t ld, const void *qn, const void *kn
     WB_CHECK_ARG(head_dim % 32 == 0 && head_dim <= 256 && rot_dim <= head_dim && rot_dim % 2 == 0, "qk_prep: head_dim %u / rot_dim %u not built", head_dim, rot_dim);
     if (tokens == 0) return WB_OK;
     dim3 grid(q_heads + 2 * kv_heads, tokens);
-    qk_prep_kernel<<<grid, head_dim, 0, st>>>((const bf16_t *)qgkv, ld, (const bf16_t *)qn, (const bf16_t *)kn, cosv, sinv, rope_pos, kv_pos,
+    WB_LAUNCH((qk_prep_kernel), grid, head_dim, 0, st, (const bf16_t *)qgkv, ld, (const bf16_t *)qn, (const bf16_t *)kn, cosv, sinv, rope_pos, kv_pos,
                                               seq_ids, block_table, bpr, (bf16_t *)qh, (bf16_t *)gate, (bf16_t *)k_pool, (bf16_t *)v_pool,
                                               q_heads, kv_heads, rot_dim, eps);
     WB_LAUNCH_CHECK();
@@ -74,6 +75,7 @@ int32_t wb_qk_prep(const void *qgkv, uint32_t ld, const void *qn, const void *kn
 __global__ void mtp_cat_kernel(const uint32_t *__restrict__ tok, uint32_t tok_stride, const bf16_t *__restrict__ embed,
                                const bf16_t *__restrict__ hid, const uint32_t *__restrict__ hid_rows, const bf16_t *__restrict__ pre_e,
                                const bf16_t *__restrict__ pre_h, bf16_t *__restrict__ cat, uint32_t hidden, float eps) {
+    PDL_ENTRY();
     __shared__ float red[33];
     const uint32_t r = blockIdx.x, half = blockIdx.y;
     const bf16_t *src = half == 0 ? embed + (size_t)tok[(size_t)r * tok_stride] * hidden
@@ -91,7 +93,7 @@ int32_t wb_mtp_cat(const uint32_t *tok, uint32_t tok_stride, const void *embed, 
     WB_CHECK_ARG(hidden >= 256, "mtp_cat: hidden %u below 256 is not built", hidden);
     if (rows == 0) return WB_OK;
     dim3 grid(rows, 2);
-    mtp_cat_kernel<<<grid, 256, 0, st>>>(tok, tok_stride, (const bf16_t *)embed, (const bf16_t *)hid, hid_rows, (const bf16_t *)pre_e,
+    WB_LAUNCH((mtp_cat_kernel), grid, 256, 0, st, tok, tok_stride, (const bf16_t *)embed, (const bf16_t *)hid, hid_rows, (const bf16_t *)pre_e,
                                          (const bf16_t *)pre_h, (bf16_t *)cat, hidden, eps);
     WB_LAUNCH_CHECK();
     return WB_OK;
@@ -99,6 +101,7 @@ int32_t wb_mtp_cat(const uint32_t *tok, uint32_t tok_stride, const void *embed, 
 
 // ---- SwiGLU activation on the fused gate|up projection: out[r, i] = bf16(bf16(silu(g)) * u) -----------------
 __global__ void silu_mul_rows_kernel(const bf16_t *__restrict__ gu, uint32_t ld, bf16_t *__restrict__ out, uint32_t inter) {
+    PDL_ENTRY();
     const bf16_t *g = gu + (size_t)blockIdx.y * ld, *u = g + inter;
     uint32_t i = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
     if (i >= inter) return;
@@ -111,13 +114,14 @@ int32_t wb_silu_mul_rows(const void *gu, uint32_t ld, void *out, uint32_t rows, 
     WB_CHECK_ARG(inter % 2 == 0 && ld % 2 == 0, "silu_mul_rows: odd width");
     if (rows == 0) return WB_OK;
     dim3 grid((inter / 2 + 255) / 256, rows);
-    silu_mul_rows_kernel<<<grid, 256, 0, st>>>((const bf16_t *)gu, ld, (bf16_t *)out, inter);
+    WB_LAUNCH((silu_mul_rows_kernel), grid, 256, 0, st, (const bf16_t *)gu, ld, (bf16_t *)out, inter);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }
 
 // ---- argmax phase 2 with a strided destination (draft token j of batch row r lands at out[r*mul + off]) -----
 __global__ void argmax_finish_kernel(const uint64_t *__restrict__ part, uint32_t split, uint32_t *__restrict__ out, uint32_t out_mul, uint32_t out_off) {
+    PDL_ENTRY();
     uint32_t r = blockIdx.x;
     uint64_t k = 0ull;
     for (uint32_t i = threadIdx.x; i < split; i += 32) { uint64_t o = part[(size_t)r * split + i]; k = o > k ? o : k; }
@@ -127,7 +131,7 @@ __global__ void argmax_finish_kernel(const uint64_t *__restrict__ part, uint32_t
 }
 int32_t wb_argmax_finish(const void *part, uint32_t split, uint32_t *out, uint32_t out_mul, uint32_t out_off, uint32_t s, cudaStream_t st) {
     if (s == 0) return WB_OK;
-    argmax_finish_kernel<<<s, 32, 0, st>>>((const uint64_t *)part, split, out, out_mul, out_off);
+    WB_LAUNCH((argmax_finish_kernel), s, 32, 0, st, (const uint64_t *)part, split, out, out_mul, out_off);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }
@@ -136,6 +140,7 @@ int32_t wb_argmax_finish(const void *part, uint32_t split, uint32_t *out, uint32
 // Row (t, h): x = core[t, h, :], z = z_base[t*z_tok_stride + h*hidden + :]  (reference.rs:699-713).
 __global__ void rms_norm_gated_rows_kernel(const bf16_t *__restrict__ x, const bf16_t *__restrict__ z, uint32_t z_tok_stride,
                                            const float *__restrict__ w, bf16_t *__restrict__ out, uint32_t heads, uint32_t hidden, float eps) {
+    PDL_ENTRY();
     __shared__ float red[33];
     const uint32_t t = blockIdx.y, h = blockIdx.x, i = threadIdx.x;
     size_t xb = ((size_t)t * heads + h) * hidden, zb = (size_t)t * z_tok_stride + (size_t)h * hidden;
@@ -151,7 +156,7 @@ int32_t wb_rms_norm_gated_rows(const void *x, const void *z, uint32_t z_tok_stri
     WB_CHECK_ARG(hidden % 32 == 0 && hidden >= 32 && hidden <= 256 && (hidden & (hidden - 1)) == 0, "rms_norm_gated_rows: hidden %u not built", hidden);
     if (tokens == 0) return WB_OK;
     dim3 grid(heads, tokens);
-    rms_norm_gated_rows_kernel<<<grid, hidden, 0, st>>>((const bf16_t *)x, (const bf16_t *)z, z_tok_stride, w, (bf16_t *)out, heads, hidden, eps);
+    WB_LAUNCH((rms_norm_gated_rows_kernel), grid, hidden, 0, st, (const bf16_t *)x, (const bf16_t *)z, z_tok_stride, w, (bf16_t *)out, heads, hidden, eps);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }

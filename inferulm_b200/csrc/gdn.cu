@@ -62,6 +62,7 @@ struct StateIO<false> {
 
 template <int R, bool F32>
 __global__ void __launch_bounds__(128) gdn_kernel(const GdnParams P) {
+    PDL_ENTRY();
     constexpr int KD = 128, VD = 128, WARPS = 4;
     constexpr int SLABS = VD / (WARPS * R);
     __shared__ float T[WARPS][R][33];
@@ -195,8 +196,8 @@ __global__ void __launch_bounds__(128) gdn_kernel(const GdnParams P) {
 template <int R>
 static void launch_gdn(const GdnParams &p, bool f32, cudaStream_t st) {
     unsigned grid = p.n_rows * p.v_heads * (128 / (4 * R));
-    if (f32) gdn_kernel<R, true><<<grid, 128, 0, st>>>(p);
-    else gdn_kernel<R, false><<<grid, 128, 0, st>>>(p);
+    if (f32) WB_LAUNCH((gdn_kernel<R, true>), grid, 128, 0, st, p);
+    else WB_LAUNCH((gdn_kernel<R, false>), grid, 128, 0, st, p);
 }
 
 static int32_t gdn_dispatch(GdnParams &p, uint32_t k_dim, uint32_t v_dim, bool f32, uint32_t rows_per_warp, cudaStream_t st) {

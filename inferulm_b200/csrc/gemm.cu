@@ -6,8 +6,9 @@
 // f64 product (crates/wein-kernel/tests/gemm.rs:11).
 //
 // At these m the product is bound by streaming W from HBM once (arithmetic intensity <= 32 flop/B).  Design:
-//  * one CTA = 16 consecutive weight rows x one k slice; its 8 warps split the slice 8 ways and meet in a
-//    fixed-order shared-memory reduction;
+//  * a row tile is 16 consecutive weight rows; KW warps (1..8, chosen from (n, k) so that about two CTAs per SM are
+//    resident) split the tile's k range and meet in a fixed-order shared-memory reduction; a CTA of 8 warps holds
+//    8/KW tiles;
 //  * W goes HBM -> registers directly: lane (g, c) of a warp loads 16 contiguous bytes of rows g and g+8.
 //    Those 8 bf16 feed two m16n8k16 MMAs as the A operand under a permutation of the k index that the
 //    activation (B operand) loads mirror, so no shared-memory staging or ldmatrix is needed;
@@ -36,24 +37,36 @@ __device__ __forceinline__ void mma_bf16(float c[4], uint32_t a0, uint32_t a1, u
 struct WgemmParams {
     const bf16_t *A, *W;
     bf16_t *C;
-    float *partial;       // [ksplit][n_tiles][MT*8*16] when ksplit > 1
-    uint32_t *counters;   // [n_tiles], zero on entry, left zero
+    float *partial;       // [ksplit][ctas][8/KW tiles * MT*128] when ksplit > 1
+    uint32_t *counters;   // [ctas], zero on entry, left zero
     uint32_t m, n, k, lda, ldc, ksplit, kslice;  // kslice: k elements per CTA slice (multiple of 32)
+    uint32_t swiglu;      // 1: W = [gate; up] (n = 2*inter rows); tile rows 0-7 are gate rows, 8-15 the matching up rows, and
+                          //    the epilogue writes bf16(bf16(silu(bf16 g)) * bf16 u) into C[m, inter]
 };
 
-template <int MT>
+// One CTA = 8 warps = 8/KW row tiles of 16 weight rows; the KW warps of a tile split the CTA's k slice contiguously.
+template <int MT, int KW, int UNR>
 __global__ void __launch_bounds__(256) wgemm_kernel(const WgemmParams P) {
-    constexpr int WARPS = 8, UNR = 4;
+    pdl_trigger();
+    constexpr int WARPS = 8, TPC = WARPS / KW;  // tiles per CTA
     __shared__ float red[WARPS][MT][32][4];
     __shared__ uint32_t is_last;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
-    const uint32_t tile = blockIdx.x, ky = blockIdx.y, n0 = tile * 16;
-    // k blocks (32 elements) of this CTA's slice, split contiguously over the warps
+    const int tic = warp / KW, kp = warp % KW;
+    const uint32_t ky = blockIdx.y;
+    const uint32_t half_n = P.n >> 1;
+    const uint32_t n_tiles = P.swiglu ? (half_n + 7) / 8 : (P.n + 15) / 16;
+    const uint32_t tile = blockIdx.x * TPC + tic;
+    const bool tile_ok = tile < n_tiles;
+    // weight rows of this lane: plain tile = rows n0+g, n0+g+8; SwiGLU tile = gate row j0+g and up row inter+j0+g
+    uint32_t r0, r1;
+    if (P.swiglu) { uint32_t j = min(tile * 8 + g, half_n - 1); r0 = j; r1 = half_n + j; }
+    else { r0 = min(tile * 16 + g, P.n - 1); r1 = min(tile * 16 + g + 8, P.n - 1); }
+    if (!tile_ok) { r0 = 0; r1 = 0; }
     const uint32_t kb0 = ky * (P.kslice / 32), kb1 = min(P.k / 32, kb0 + P.kslice / 32);
-    const uint32_t nb = kb1 - kb0, per = (nb + WARPS - 1) / WARPS;
-    const uint32_t b_lo = min(kb1, kb0 + warp * per), b_hi = min(kb1, b_lo + per);
+    const uint32_t nb = kb1 - kb0, per = (nb + KW - 1) / KW;
+    const uint32_t b_lo = min(kb1, kb0 + kp * per), b_hi = tile_ok ? min(kb1, b_lo + per) : b_lo;
 
-    const uint32_t r0 = min(n0 + g, P.n - 1), r1 = min(n0 + g + 8, P.n - 1);  // clamp: rows past n are loaded but never stored
     const bf16_t *w0 = P.W + (size_t)r0 * P.k + c * 8, *w1 = P.W + (size_t)r1 * P.k + c * 8;
     const bf16_t *ap[MT];
     bool av[MT];
@@ -77,6 +90,20 @@ __global__ void __launch_bounds__(256) wgemm_kernel(const WgemmParams P) {
         }
     };
     if (b_lo < b_hi) issue(b_lo);
+    // Weights are never written by the stream: pull this warp's slab towards L2 while the predecessor kernel is still
+    // running (one 128-byte line per lane and step: lane -> row lane/2 of the tile, line lane%2 + 2*step)
+    {
+        const uint32_t row = lane >> 1;
+        uint32_t rr;
+        if (P.swiglu) { uint32_t j = min(tile * 8 + (row & 7), half_n - 1); rr = (row < 8) ? j : half_n + j; }
+        else rr = min(tile * 16 + row, P.n - 1);
+        const char *base = reinterpret_cast<const char *>(P.W + (size_t)rr * P.k + (size_t)b_lo * 32);
+        const uint32_t bytes = (b_hi - b_lo) * 64;
+        if (tile_ok)
+            for (uint32_t off = (lane & 1) * 128 + 8 * 64; off < bytes; off += 256)
+                asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
+    }
+    pdl_wait();
     for (uint32_t b = b_lo; b < b_hi; b += UNR) {
         uint4 ca[UNR], cb[UNR];
 #pragma unroll
@@ -106,81 +133,128 @@ __global__ void __launch_bounds__(256) wgemm_kernel(const WgemmParams P) {
 #pragma unroll
         for (int j = 0; j < 4; j++) red[warp][mt][lane][j] = acc[mt][j];
     __syncthreads();
-    // fixed-order sum over the warps; element (mt, lane, j) is output (token mt*8 + 2c + (j&1), row g + 8*(j>>1))
-    const uint32_t n_tiles = gridDim.x;
-    for (int idx = threadIdx.x; idx < MT * 128; idx += 256) {
-        int mt = idx >> 7, ln = (idx >> 2) & 31, j = idx & 3;
-        float s = 0.0f;
-#pragma unroll
-        for (int w = 0; w < WARPS; w++) s += red[w][mt][ln][j];
-        if (P.ksplit > 1) {
-            P.partial[((size_t)ky * n_tiles + tile) * (MT * 128) + idx] = s;
+    // element (tile t, mt, lane, j) is output (token mt*8 + 2c + (j&1), tile row g + 8*(j>>1)); fixed-order sum over the tile's warps
+    auto emit = [&](int idx, float s, float s_hi) {
+        int t = idx / (MT * 128), rem = idx % (MT * 128);
+        int mt = rem >> 7, ln = (rem >> 2) & 31, j = rem & 3;
+        uint32_t tl = blockIdx.x * TPC + t, tok = mt * 8 + 2 * (ln & 3) + (j & 1);
+        if (tl >= n_tiles || tok >= P.m) return;
+        if (P.swiglu) {
+            if (j >= 2) return;  // handled together with its gate element
+            uint32_t col = tl * 8 + (ln >> 2);
+            if (col >= half_n) return;
+            float gv = rbf(s), uv = rbf(s_hi);
+            P.C[(size_t)tok * P.ldc + col] = f2bf(__fmul_rn(rbf(silu_ref(gv)), uv));
         } else {
-            uint32_t tok = mt * 8 + 2 * (ln & 3) + (j & 1), row = n0 + (ln >> 2) + 8 * (j >> 1);
-            if (tok < P.m && row < P.n) P.C[(size_t)tok * P.ldc + row] = f2bf(s);
+            uint32_t row = tl * 16 + (ln >> 2) + 8 * (j >> 1);
+            if (row < P.n) P.C[(size_t)tok * P.ldc + row] = f2bf(s);
+        }
+    };
+    constexpr int PER_CTA = TPC * MT * 128;
+    for (int idx = threadIdx.x; idx < PER_CTA; idx += 256) {
+        int t = idx / (MT * 128), rem = idx % (MT * 128);
+        int mt = rem >> 7, ln = (rem >> 2) & 31, j = rem & 3;
+        float s = 0.0f, s_hi = 0.0f;
+#pragma unroll
+        for (int w = 0; w < KW; w++) s += red[t * KW + w][mt][ln][j];
+        if (P.ksplit > 1) {
+            P.partial[((size_t)ky * gridDim.x + blockIdx.x) * PER_CTA + idx] = s;
+        } else {
+            if (P.swiglu && j < 2) {
+#pragma unroll
+                for (int w = 0; w < KW; w++) s_hi += red[t * KW + w][mt][ln][j + 2];
+            }
+            emit(idx, s, s_hi);
         }
     }
     if (P.ksplit > 1) {
         __threadfence();
         __syncthreads();
         if (threadIdx.x == 0) {
-            uint32_t prev = atomicAdd(&P.counters[tile], 1u);
+            uint32_t prev = atomicAdd(&P.counters[blockIdx.x], 1u);
             is_last = (prev == P.ksplit - 1);
-            if (is_last) P.counters[tile] = 0;  // every slice has arrived: safe to re-arm for the next launch
+            if (is_last) P.counters[blockIdx.x] = 0;  // every slice has arrived: safe to re-arm for the next launch
         }
         __syncthreads();
         if (is_last) {
             __threadfence();
-            for (int idx = threadIdx.x; idx < MT * 128; idx += 256) {
-                float s = 0.0f;
-                for (uint32_t y = 0; y < P.ksplit; y++) s += __ldcg(&P.partial[((size_t)y * n_tiles + tile) * (MT * 128) + idx]);
-                int mt = idx >> 7, ln = (idx >> 2) & 31, j = idx & 3;
-                uint32_t tok = mt * 8 + 2 * (ln & 3) + (j & 1), row = n0 + (ln >> 2) + 8 * (j >> 1);
-                if (tok < P.m && row < P.n) P.C[(size_t)tok * P.ldc + row] = f2bf(s);
+            for (int idx = threadIdx.x; idx < PER_CTA; idx += 256) {
+                float s = 0.0f, s_hi = 0.0f;
+                for (uint32_t y = 0; y < P.ksplit; y++) s += __ldcg(&P.partial[((size_t)y * gridDim.x + blockIdx.x) * PER_CTA + idx]);
+                if (P.swiglu && (idx & 3) < 2)
+                    for (uint32_t y = 0; y < P.ksplit; y++) s_hi += __ldcg(&P.partial[((size_t)y * gridDim.x + blockIdx.x) * PER_CTA + idx + 2]);
+                emit(idx, s, s_hi);
             }
         }
     }
 }
 
-// How many ways to split k over CTAs: only when there are too few row tiles to fill the machine.
-// Depends on (n, k) only -- never on m -- so a row's accumulation order is the same at every batch size.
-static uint32_t pick_ksplit(uint32_t n, uint32_t k) {
-    uint32_t tiles = (n + 15) / 16, kb = k / 32;
-    uint32_t ks = 1;
-    while (tiles * ks < 592 && ks < 8 && kb / (ks * 2) >= 32) ks *= 2;
-    return ks;
+// Decomposition of a product: KW warps per row tile inside a CTA, ksplit k slices over CTAs.  It depends on (n, k)
+// only -- never on m -- so a row's accumulation order is the same at every batch size.
+struct WgemmPlan { uint32_t kw, ksplit; };
+static uint32_t g_force_kw = 0, g_force_ks = 0, g_force_unr = 0;
+extern "C" void wein_b200_gemm_tune(uint32_t kw, uint32_t ksplit, uint32_t unr) { g_force_kw = kw; g_force_ks = ksplit; g_force_unr = unr; }
+
+static WgemmPlan plan_for(uint32_t n_tiles, uint32_t k, bool has_scratch) {
+    // Measured on B200 (graph replay, weights rotated through 3 GB): the fewest warps per tile that still give every
+    // SM a CTA win for the layer projections (kw 2 at 640-1152 tiles: 3.9-5.6 TB/s; kw 8 at 160 tiles: 3.0-3.9 TB/s);
+    // the vocabulary projection (9496 tiles) prefers kw 4 (6.2 TB/s).  Splitting k over CTAs never won: off by default.
+    uint32_t kb = k / 32, kw = 1, ks = 1;
+    while (kw < 8 && (n_tiles * kw + 7) / 8 < 148 && kb / (kw * 2) >= 4) kw *= 2;
+    if (n_tiles >= 4096 && kb >= 32) kw = 4;
+    if (g_force_kw) kw = g_force_kw;
+    if (g_force_ks) ks = has_scratch ? g_force_ks : 1;
+    return {kw, ks};
 }
 
 extern "C" uint64_t wein_b200_gemm_scratch_bytes(uint32_t n_max) {
-    // partials for the split-k shapes (n <= 592*16 rows at most 8 slices, 32 token columns) + tile counters
-    uint64_t tiles = (n_max + 15) / 16;
-    if (tiles > 592) tiles = 592;
-    return 8ull * tiles * (4 * 128) * 4 + 4096 * 4;
+    // split-k partials: at most 8 slices x 296 CTAs x (8 tiles x 4 token tiles x 128) floats, plus the CTA counters
+    (void)n_max;
+    return 8ull * 592 * (8 * 4 * 128) * 4 + 4096 * 4;
+}
+
+template <int MT, int KW>
+static void wgemm_go(const WgemmParams &p, dim3 grid, uint32_t unr, cudaStream_t st) {
+    if constexpr (MT == 1) {
+        if (unr == 8) { WB_LAUNCH((wgemm_kernel<MT, KW, 8>), grid, 256, 0, st, p); return; }
+    }
+    WB_LAUNCH((wgemm_kernel<MT, KW, 4>), grid, 256, 0, st, p);
+}
+template <int MT>
+static void wgemm_go_kw(const WgemmParams &p, dim3 grid, uint32_t kw, uint32_t unr, cudaStream_t st) {
+    switch (kw) {
+        case 1: wgemm_go<MT, 1>(p, grid, unr, st); break;
+        case 2: wgemm_go<MT, 2>(p, grid, unr, st); break;
+        case 4: wgemm_go<MT, 4>(p, grid, unr, st); break;
+        default: wgemm_go<MT, 8>(p, grid, unr, st); break;
+    }
 }
 
 static int32_t wgemm_launch(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc,
-                            void *scratch, uint64_t scratch_bytes, cudaStream_t st) {
+                            void *scratch, uint64_t scratch_bytes, bool swiglu, cudaStream_t st) {
     WgemmParams p{};
     p.A = (const bf16_t *)a; p.W = (const bf16_t *)w; p.C = (bf16_t *)c;
-    p.m = m; p.n = n; p.k = k; p.lda = lda; p.ldc = ldc;
-    uint32_t tiles = (n + 15) / 16;
-    uint32_t ks = scratch ? pick_ksplit(n, k) : 1;
+    p.m = m; p.n = n; p.k = k; p.lda = lda; p.ldc = ldc; p.swiglu = swiglu ? 1 : 0;
+    uint32_t tiles = swiglu ? (n / 2 + 7) / 8 : (n + 15) / 16;
     int mt = (m + 7) / 8;
-    if (ks > 1) {
-        uint64_t need = (uint64_t)ks * tiles * (mt * 128) * 4 + 4096 * 4;
-        if (tiles > 4096 || need > scratch_bytes) ks = 1;
+    WgemmPlan pl = plan_for(tiles, k, scratch != nullptr);
+    uint32_t tpc = 8 / pl.kw, ctas = (tiles + tpc - 1) / tpc;
+    if (pl.ksplit > 1) {
+        uint64_t need = (uint64_t)pl.ksplit * ctas * (tpc * mt * 128) * 4 + 4096 * 4;
+        if (ctas > 4096 || need > scratch_bytes) pl.ksplit = 1;
     }
-    p.ksplit = ks;
+    p.ksplit = pl.ksplit;
     uint32_t kb = k / 32;
-    p.kslice = ((kb + ks - 1) / ks) * 32;
+    p.kslice = ((kb + pl.ksplit - 1) / pl.ksplit) * 32;
     p.counters = (uint32_t *)scratch;
     p.partial = scratch ? (float *)((char *)scratch + 4096 * 4) : nullptr;
-    dim3 grid(tiles, ks);
+    dim3 grid(ctas, pl.ksplit);
+    uint32_t unr = g_force_unr ? g_force_unr : 4;
     switch (mt) {
-        case 1: wgemm_kernel<1><<<grid, 256, 0, st>>>(p); break;
-        case 2: wgemm_kernel<2><<<grid, 256, 0, st>>>(p); break;
-        case 3: wgemm_kernel<3><<<grid, 256, 0, st>>>(p); break;
-        default: wgemm_kernel<4><<<grid, 256, 0, st>>>(p); break;
+        case 1: wgemm_go_kw<1>(p, grid, pl.kw, unr, st); break;
+        case 2: wgemm_go_kw<2>(p, grid, pl.kw, unr, st); break;
+        case 3: wgemm_go_kw<3>(p, grid, pl.kw, unr, st); break;
+        default: wgemm_go_kw<4>(p, grid, pl.kw, unr, st); break;
     }
     WB_LAUNCH_CHECK();
     return WB_OK;
@@ -254,11 +328,28 @@ int32_t wb_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n
     WB_CHECK_ARG(lda >= k && ldc >= n && lda % 8 == 0, "gemm_wt: bad leading dimensions");
     WB_CHECK_ARG(((((uintptr_t)a) | ((uintptr_t)w)) & 15u) == 0, "gemm_wt: operands must be 16-byte aligned");
     if (m == 0) return WB_OK;
-    if (m <= 32) return wgemm_launch(a, w, c, m, n, k, lda, ldc, scratch, scratch_bytes, st);
+    if (m <= 32) return wgemm_launch(a, w, c, m, n, k, lda, ldc, scratch, scratch_bytes, false, st);
     return lt_gemm(a, w, c, m, n, k, lda, ldc, st);
+}
+
+// Fused gate|up projection + SwiGLU activation: W = [gate; up] of shape [2*inter, k]; out[m, inter] =
+// bf16(bf16(silu(bf16(a.gate_j))) * bf16(a.up_j)) -- the values silu_mul produces from the separately rounded
+// projections (kernels/src/lib.rs:576-584 of the reference), without materialising them.  m <= 32 only.
+int32_t wb_gemm_swiglu(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k, uint32_t lda,
+                       uint32_t ldc, void *scratch, uint64_t scratch_bytes, cudaStream_t st) {
+    WB_CHECK_ARG(a && w_gate_up && out, "gemm_swiglu: null pointer");
+    WB_CHECK_ARG(inter > 0 && k > 0 && k % 32 == 0 && m <= 32, "gemm_swiglu: k = %u must be a multiple of 32 and m = %u at most 32", k, m);
+    WB_CHECK_ARG(lda >= k && ldc >= inter && lda % 8 == 0, "gemm_swiglu: bad leading dimensions");
+    if (m == 0) return WB_OK;
+    return wgemm_launch(a, w_gate_up, out, m, 2 * inter, k, lda, ldc, scratch, scratch_bytes, true, st);
 }
 
 extern "C" int32_t wein_b200_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, void *scratch,
                                      uint64_t scratch_bytes, void *stream) {
     return wb_gemm_wt(a, w, c, m, n, k, k, n, scratch, scratch_bytes, (cudaStream_t)stream);
+}
+
+extern "C" int32_t wein_b200_gemm_swiglu(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k,
+                                         void *scratch, uint64_t scratch_bytes, void *stream) {
+    return wb_gemm_swiglu(a, w_gate_up, out, m, inter, k, k, inter, scratch, scratch_bytes, (cudaStream_t)stream);
 }

@@ -5,6 +5,8 @@
 
 int32_t wb_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc,
                    void *scratch, uint64_t scratch_bytes, cudaStream_t st);
+int32_t wb_gemm_swiglu(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k, uint32_t lda,
+                       uint32_t ldc, void *scratch, uint64_t scratch_bytes, cudaStream_t st);
 int32_t wb_gemm_warmup();  // creates the cuBLASLt handle and workspace outside any stream capture
 int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, const void *block_table, const void *seq_ids,
                        const void *positions, const void *row_start, const void *row_count, const void *gate, void *out,

@@ -11,6 +11,7 @@
 // out[t, :] = w[ids[t], :]  (reference.rs:298-305).  One block per row.
 __global__ void embed_kernel(const uint32_t *__restrict__ ids, const bf16_t *__restrict__ w, bf16_t *__restrict__ out,
                              uint32_t hidden) {
+    PDL_ENTRY();
     size_t src = (size_t)ids[blockIdx.x] * hidden, dst = (size_t)blockIdx.x * hidden;
     if ((hidden & 7u) == 0 && ((((uintptr_t)w) | ((uintptr_t)out)) & 15u) == 0) {
         const uint4 *s = reinterpret_cast<const uint4 *>(w + src);
@@ -29,10 +30,31 @@ __global__ void embed_kernel(const uint32_t *__restrict__ ids, const bf16_t *__r
 template <int MODE>
 __global__ void rms_norm_zc_kernel(const bf16_t *a, const bf16_t *b, const bf16_t *__restrict__ w, bf16_t *sum_out,
                                    bf16_t *norm_out, uint32_t hidden, float eps) {
+    PDL_ENTRY();
+    constexpr int CACHE = 12;  // elements per thread kept in registers between the two passes (hidden <= 3072 at 256 threads)
     __shared__ float red[33];
     size_t base = (size_t)blockIdx.x * hidden;
+    float vals[CACHE], wv[CACHE];
     float acc = 0.0f;
-    for (uint32_t i = threadIdx.x; i < hidden; i += blockDim.x) {
+#pragma unroll
+    for (int it = 0; it < CACHE; it++) {
+        uint32_t i = threadIdx.x + it * blockDim.x;
+        vals[it] = 0.0f; wv[it] = 0.0f;
+        if (i < hidden) {
+            float v;
+            if (MODE == 1) {
+                bf16_t s = f2bf(bf2f(a[base + i]) + bf2f(b[base + i]));
+                sum_out[base + i] = s;
+                v = bf2f(s);
+            } else {
+                v = bf2f(a[base + i]);
+            }
+            vals[it] = v;
+            wv[it] = bf2f(w[i]);
+            acc = fmaf(v, v, acc);
+        }
+    }
+    for (uint32_t i = threadIdx.x + CACHE * blockDim.x; i < hidden; i += blockDim.x) {
         float v;
         if (MODE == 1) {
             bf16_t s = f2bf(bf2f(a[base + i]) + bf2f(b[base + i]));
@@ -45,8 +67,13 @@ __global__ void rms_norm_zc_kernel(const bf16_t *a, const bf16_t *b, const bf16_
     }
     float total = block_sum_tree(acc, red);
     float inv = 1.0f / sqrtf(total / (float)hidden + eps);
+#pragma unroll
+    for (int it = 0; it < CACHE; it++) {
+        uint32_t i = threadIdx.x + it * blockDim.x;
+        if (i < hidden) norm_out[base + i] = f2bf(vals[it] * inv * (1.0f + wv[it]));
+    }
     const bf16_t *src = MODE == 1 ? sum_out : a;
-    for (uint32_t i = threadIdx.x; i < hidden; i += blockDim.x)
+    for (uint32_t i = threadIdx.x + CACHE * blockDim.x; i < hidden; i += blockDim.x)
         norm_out[base + i] = f2bf(bf2f(src[base + i]) * inv * (1.0f + bf2f(w[i])));
 }
 
@@ -54,6 +81,7 @@ __global__ void rms_norm_zc_kernel(const bf16_t *a, const bf16_t *b, const bf16_
 // f32); out = bf16(xw * (z*sigmoid(z))).
 __global__ void rms_norm_gated_kernel(const bf16_t *__restrict__ x, const bf16_t *__restrict__ z,
                                       const float *__restrict__ w, bf16_t *__restrict__ out, uint32_t hidden, float eps) {
+    PDL_ENTRY();
     __shared__ float red[33];
     size_t base = (size_t)blockIdx.x * hidden;
     float acc = 0.0f;
@@ -77,6 +105,7 @@ __global__ void rms_norm_gated_kernel(const bf16_t *__restrict__ x, const bf16_t
 __global__ void rope_pt_kernel(const bf16_t *x, const float *__restrict__ cosv, const float *__restrict__ sinv,
                                const uint32_t *__restrict__ pos, bf16_t *out, uint32_t rot_dim, uint32_t head_dim,
                                uint32_t heads, uint32_t tokens) {
+    PDL_ENTRY();
     uint32_t half = rot_dim / 2;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     size_t total = (size_t)tokens * heads * half;
@@ -92,6 +121,7 @@ __global__ void rope_pt_kernel(const bf16_t *x, const float *__restrict__ cosv, 
 }
 // copy of the non-rotated tail when out != x
 __global__ void rope_tail_copy_kernel(const bf16_t *x, bf16_t *out, uint32_t rot_dim, uint32_t head_dim, size_t rows) {
+    PDL_ENTRY();
     uint32_t tail = head_dim - rot_dim;
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * tail) return;
@@ -105,6 +135,7 @@ __global__ void rope_tail_copy_kernel(const bf16_t *x, bf16_t *out, uint32_t rot
 // OP 3 silu_mul (kernels/src/lib.rs:576-584)   4 sigmul (reference.rs:463-472)
 template <int OP>
 __global__ void eltwise_kernel(const bf16_t *__restrict__ a, const bf16_t *__restrict__ b, bf16_t *__restrict__ out, size_t n) {
+    PDL_ENTRY();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     float x = bf2f(a[i]);
@@ -126,6 +157,7 @@ __global__ void kv_scatter_kernel(const bf16_t *__restrict__ src_k, const bf16_t
                                   const uint32_t *__restrict__ block_table, const uint32_t *__restrict__ seq_ids,
                                   const uint32_t *__restrict__ positions, void *k_dst, void *v_dst, uint32_t bpr,
                                   uint32_t block_size, uint32_t head_elems, uint32_t tokens) {
+    PDL_ENTRY();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)tokens * head_elems) return;
     uint32_t t = idx / head_elems, e = idx % head_elems;
@@ -147,6 +179,7 @@ __global__ void conv1d_dw_kernel(const bf16_t *__restrict__ x, const bf16_t *__r
                                  const bf16_t *__restrict__ state_in, const uint32_t *__restrict__ tok_row,
                                  const uint32_t *__restrict__ tok_pos, bf16_t *__restrict__ out, uint32_t conv_dim,
                                  uint32_t kernel, uint32_t tokens) {
+    PDL_ENTRY();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)tokens * conv_dim) return;
     uint32_t g = idx / conv_dim, c = idx % conv_dim;
@@ -169,6 +202,7 @@ __global__ void conv1d_dw_kernel(const bf16_t *__restrict__ x, const bf16_t *__r
 __global__ void conv_state_roll_kernel(const bf16_t *__restrict__ x, bf16_t *state, const uint32_t *__restrict__ row_start,
                                        const uint32_t *__restrict__ row_count, const uint32_t *__restrict__ row_id,
                                        const uint32_t *__restrict__ specs, uint32_t conv_dim, uint32_t kernel, uint32_t n_rows) {
+    PDL_ENTRY();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_rows * conv_dim) return;
     uint32_t r = idx / conv_dim, c = idx % conv_dim;
@@ -202,6 +236,7 @@ __global__ void conv_verify_kernel(const bf16_t *__restrict__ x, uint32_t x_stri
                                    const uint32_t *__restrict__ row_count, const uint32_t *__restrict__ in_row,
                                    const uint32_t *__restrict__ out_base, bf16_t *__restrict__ out, uint32_t conv_dim,
                                    uint32_t n_rows) {
+    PDL_ENTRY();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_rows * conv_dim) return;
     uint32_t r = idx / conv_dim, c = idx % conv_dim;
@@ -248,6 +283,7 @@ __device__ __forceinline__ uint64_t warp_max_u64(uint64_t k) {
 // phase 1: grid (split, s); each block scans one slice of one row
 __global__ void argmax_p1_kernel(const bf16_t *__restrict__ x, const uint32_t *__restrict__ rows, uint64_t *__restrict__ part,
                                  uint32_t n, uint32_t split) {
+    PDL_ENTRY();
     __shared__ uint64_t sm[32];
     uint32_t r = blockIdx.y, sl = blockIdx.x;
     const bf16_t *row = x + (size_t)rows[r] * n;
@@ -284,6 +320,7 @@ __global__ void argmax_p1_kernel(const bf16_t *__restrict__ x, const uint32_t *_
 }
 // phase 2: one warp per row merges the slices
 __global__ void argmax_p2_kernel(const uint64_t *__restrict__ part, uint32_t *__restrict__ out, uint32_t split) {
+    PDL_ENTRY();
     uint32_t r = blockIdx.x;
     uint64_t k = 0ull;
     for (uint32_t i = threadIdx.x; i < split; i += 32) { uint64_t o = part[(size_t)r * split + i]; k = o > k ? o : k; }
@@ -305,7 +342,7 @@ extern "C" {
 int32_t wein_b200_embed(const void *ids, const void *w, void *out, uint32_t hidden, uint32_t tokens, void *stream) {
     WB_CHECK_ARG(ids && w && out && hidden > 0, "embed: null pointer or zero width");
     if (tokens == 0) return WB_OK;
-    embed_kernel<<<tokens, 256, 0, STREAM(stream)>>>((const uint32_t *)ids, (const bf16_t *)w, (bf16_t *)out, hidden);
+    WB_LAUNCH((embed_kernel), tokens, 256, 0, STREAM(stream), (const uint32_t *)ids, (const bf16_t *)w, (bf16_t *)out, hidden);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }
@@ -315,7 +352,7 @@ int32_t wein_b200_rms_norm_zc(const void *x, const void *w, void *out, uint32_t 
     uint32_t bd = norm_bdim(hidden);
     if (bd < 32) { wb_set_error("rms_norm_zc: hidden %u below one warp is not built", hidden); return WB_ERR_SHAPE; }
     if (rows == 0) return WB_OK;
-    rms_norm_zc_kernel<0><<<rows, bd, 0, STREAM(stream)>>>((const bf16_t *)x, nullptr, (const bf16_t *)w, nullptr, (bf16_t *)out, hidden, eps);
+    WB_LAUNCH((rms_norm_zc_kernel<0>), rows, bd, 0, STREAM(stream), (const bf16_t *)x, nullptr, (const bf16_t *)w, nullptr, (bf16_t *)out, hidden, eps);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }
@@ -326,7 +363,7 @@ int32_t wein_b200_add_norm_zc(const void *a, const void *b, const void *w, void 
     uint32_t bd = norm_bdim(hidden);
     if (bd < 32) { wb_set_error("add_norm_zc: hidden %u below one warp is not built", hidden); return WB_ERR_SHAPE; }
     if (rows == 0) return WB_OK;
-    rms_norm_zc_kernel<1><<<rows, bd, 0, STREAM(stream)>>>((const bf16_t *)a, (const bf16_t *)b, (const bf16_t *)w, (bf16_t *)sum_out,
+    WB_LAUNCH((rms_norm_zc_kernel<1>), rows, bd, 0, STREAM(stream), (const bf16_t *)a, (const bf16_t *)b, (const bf16_t *)w, (bf16_t *)sum_out,
                                                           (bf16_t *)norm_out, hidden, eps);
     WB_LAUNCH_CHECK();
     return WB_OK;
@@ -338,7 +375,7 @@ int32_t wein_b200_rms_norm_gated(const void *x, const void *z, const void *w, vo
     uint32_t bd = norm_bdim(hidden);
     if (bd < 32) { wb_set_error("rms_norm_gated: hidden %u below one warp is not built", hidden); return WB_ERR_SHAPE; }
     if (rows == 0) return WB_OK;
-    rms_norm_gated_kernel<<<rows, bd, 0, STREAM(stream)>>>((const bf16_t *)x, (const bf16_t *)z, (const float *)w, (bf16_t *)out, hidden, eps);
+    WB_LAUNCH((rms_norm_gated_kernel), rows, bd, 0, STREAM(stream), (const bf16_t *)x, (const bf16_t *)z, (const float *)w, (bf16_t *)out, hidden, eps);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }
@@ -349,12 +386,12 @@ int32_t wein_b200_rope_pt(const void *x, const void *cosv, const void *sinv, con
     WB_CHECK_ARG(rot_dim % 2 == 0 && rot_dim <= head_dim && rot_dim > 0, "rope_pt: rot_dim %u must be even and <= head_dim %u", rot_dim, head_dim);
     if (tokens == 0 || heads == 0) return WB_OK;
     size_t total = (size_t)tokens * heads * (rot_dim / 2);
-    rope_pt_kernel<<<(unsigned)((total + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16_t *)x, (const float *)cosv, (const float *)sinv,
+    WB_LAUNCH((rope_pt_kernel), (unsigned)((total + 255) / 256), 256, 0, STREAM(stream), (const bf16_t *)x, (const float *)cosv, (const float *)sinv,
                                                                                (const uint32_t *)pos, (bf16_t *)out, rot_dim, head_dim, heads, tokens);
     WB_LAUNCH_CHECK();
     if (out != x && rot_dim < head_dim) {
         size_t rows = (size_t)tokens * heads, n = rows * (head_dim - rot_dim);
-        rope_tail_copy_kernel<<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16_t *)x, (bf16_t *)out, rot_dim, head_dim, rows);
+        WB_LAUNCH((rope_tail_copy_kernel), (unsigned)((n + 255) / 256), 256, 0, STREAM(stream), (const bf16_t *)x, (bf16_t *)out, rot_dim, head_dim, rows);
         WB_LAUNCH_CHECK();
     }
     return WB_OK;
@@ -364,7 +401,7 @@ int32_t wein_b200_rope_pt(const void *x, const void *cosv, const void *sinv, con
     int32_t name(const void *a, const void *b, void *out, uint64_t n, void *stream) {                           \
         WB_CHECK_ARG(a && out && (!(needs_b) || b), #name ": null pointer");                                    \
         if (n == 0) return WB_OK;                                                                               \
-        eltwise_kernel<OP><<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16_t *)a, (const bf16_t *)b, (bf16_t *)out, (size_t)n); \
+        WB_LAUNCH((eltwise_kernel<OP>), (unsigned)((n + 255) / 256), 256, 0, STREAM(stream), (const bf16_t *)a, (const bf16_t *)b, (bf16_t *)out, (size_t)n); \
         WB_LAUNCH_CHECK();                                                                                      \
         return WB_OK;                                                                                           \
     }
@@ -375,7 +412,7 @@ ELTWISE_ENTRY(wein_b200_sigmul, 4, 1)
 int32_t wein_b200_silu(const void *x, void *out, uint64_t n, void *stream) {
     WB_CHECK_ARG(x && out, "silu: null pointer");
     if (n == 0) return WB_OK;
-    eltwise_kernel<2><<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16_t *)x, nullptr, (bf16_t *)out, (size_t)n);
+    WB_LAUNCH((eltwise_kernel<2>), (unsigned)((n + 255) / 256), 256, 0, STREAM(stream), (const bf16_t *)x, nullptr, (bf16_t *)out, (size_t)n);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }
@@ -389,10 +426,10 @@ static int32_t kv_scatter_impl(bool f32, const void *src_k, const void *src_v, c
     size_t n = (size_t)tokens * head_elems;
     unsigned grid = (unsigned)((n + 255) / 256);
     if (f32)
-        kv_scatter_kernel<true><<<grid, 256, 0, STREAM(stream)>>>((const bf16_t *)src_k, (const bf16_t *)src_v, (const uint32_t *)block_table,
+        WB_LAUNCH((kv_scatter_kernel<true>), grid, 256, 0, STREAM(stream), (const bf16_t *)src_k, (const bf16_t *)src_v, (const uint32_t *)block_table,
             (const uint32_t *)seq_ids, (const uint32_t *)positions, k_dst, v_dst, bpr, block_size, head_elems, tokens);
     else
-        kv_scatter_kernel<false><<<grid, 256, 0, STREAM(stream)>>>((const bf16_t *)src_k, (const bf16_t *)src_v, (const uint32_t *)block_table,
+        WB_LAUNCH((kv_scatter_kernel<false>), grid, 256, 0, STREAM(stream), (const bf16_t *)src_k, (const bf16_t *)src_v, (const uint32_t *)block_table,
             (const uint32_t *)seq_ids, (const uint32_t *)positions, k_dst, v_dst, bpr, block_size, head_elems, tokens);
     WB_LAUNCH_CHECK();
     return WB_OK;
@@ -414,7 +451,7 @@ int32_t wein_b200_conv1d_dw(const void *x, const void *w, const void *state_in, 
     WB_CHECK_ARG(kernel >= 2 && kernel <= 9 && conv_dim > 0, "conv1d_dw: kernel %u outside 2..9", kernel);
     if (tokens == 0) return WB_OK;
     size_t n = (size_t)tokens * conv_dim;
-    conv1d_dw_kernel<<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16_t *)x, (const bf16_t *)w, (const bf16_t *)state_in,
+    WB_LAUNCH((conv1d_dw_kernel), (unsigned)((n + 255) / 256), 256, 0, STREAM(stream), (const bf16_t *)x, (const bf16_t *)w, (const bf16_t *)state_in,
         (const uint32_t *)tok_row, (const uint32_t *)tok_pos, (bf16_t *)out, conv_dim, kernel, tokens);
     WB_LAUNCH_CHECK();
     return WB_OK;
@@ -426,7 +463,7 @@ int32_t wein_b200_conv_state_roll(const void *x, void *state, const void *row_st
     WB_CHECK_ARG(kernel >= 2 && kernel <= 9 && conv_dim > 0, "conv_state_roll: kernel %u outside 2..9", kernel);
     if (n_rows == 0) return WB_OK;
     size_t n = (size_t)n_rows * conv_dim;
-    conv_state_roll_kernel<<<(unsigned)((n + 255) / 256), 256, 0, STREAM(stream)>>>((const bf16_t *)x, (bf16_t *)state, (const uint32_t *)row_start,
+    WB_LAUNCH((conv_state_roll_kernel), (unsigned)((n + 255) / 256), 256, 0, STREAM(stream), (const bf16_t *)x, (bf16_t *)state, (const uint32_t *)row_start,
         (const uint32_t *)row_count, (const uint32_t *)row_id, (const uint32_t *)specs, conv_dim, kernel, n_rows);
     WB_LAUNCH_CHECK();
     return WB_OK;
@@ -440,7 +477,7 @@ int32_t wein_b200_conv_verify(const void *x, uint32_t x_stride, const void *w, v
     WB_CHECK_ARG(x_stride >= conv_dim && conv_dim > 0, "conv_verify: x_stride %u < conv_dim %u", x_stride, conv_dim);
     if (n_rows == 0) return WB_OK;
     size_t n = (size_t)n_rows * conv_dim;
-    conv_verify_kernel<<<(unsigned)((n + 127) / 128), 128, 0, STREAM(stream)>>>((const bf16_t *)x, x_stride, (const bf16_t *)w, (bf16_t *)state,
+    WB_LAUNCH((conv_verify_kernel), (unsigned)((n + 127) / 128), 128, 0, STREAM(stream), (const bf16_t *)x, x_stride, (const bf16_t *)w, (bf16_t *)state,
         (const uint32_t *)row_start, (const uint32_t *)row_count, (const uint32_t *)in_row, (const uint32_t *)out_base, (bf16_t *)out, conv_dim, n_rows);
     WB_LAUNCH_CHECK();
     return WB_OK;
@@ -453,7 +490,7 @@ int32_t wein_b200_argmax_partials(const void *x, const void *rows, void *part, u
     WB_CHECK_ARG(x && rows && part && split > 0, "argmax: null pointer");
     if (s == 0) return WB_OK;
     dim3 grid(split, s);
-    argmax_p1_kernel<<<grid, 256, 0, st>>>((const bf16_t *)x, (const uint32_t *)rows, (uint64_t *)part, n, split);
+    WB_LAUNCH((argmax_p1_kernel), grid, 256, 0, st, (const bf16_t *)x, (const uint32_t *)rows, (uint64_t *)part, n, split);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }
@@ -466,9 +503,9 @@ int32_t wein_b200_argmax_rows(const void *x, const void *rows, void *scratch, vo
     if (s == 0) return WB_OK;
     const uint32_t split = 32;
     dim3 grid(split, s);
-    argmax_p1_kernel<<<grid, 256, 0, STREAM(stream)>>>((const bf16_t *)x, (const uint32_t *)rows, (uint64_t *)scratch, n, split);
+    WB_LAUNCH((argmax_p1_kernel), grid, 256, 0, STREAM(stream), (const bf16_t *)x, (const uint32_t *)rows, (uint64_t *)scratch, n, split);
     WB_LAUNCH_CHECK();
-    argmax_p2_kernel<<<s, 32, 0, STREAM(stream)>>>((const uint64_t *)scratch, (uint32_t *)out, split);
+    WB_LAUNCH((argmax_p2_kernel), s, 32, 0, STREAM(stream), (const uint64_t *)scratch, (uint32_t *)out, split);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }

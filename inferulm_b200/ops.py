@@ -173,3 +173,14 @@ def accept_sampled(drafts, n_drafts, p_ids, p_probs, p_n, q_ids, q_probs, q_n, t
     check(load().wein_b200_accept_sampled(_ptr(drafts), _ptr(n_drafts), _ptr(p_ids), _ptr(p_probs), _ptr(p_n), _ptr(q_ids),
                                           _ptr(q_probs), _ptr(q_n), _ptr(temp), _ptr(seed), _ptr(rnd), U32(B), U32(k),
                                           _ptr(accept_len), _ptr(out_tokens), _stream()))
+
+
+def gemm_swiglu(a, w_gate_up, out, m, inter, k, scratch=None):
+    """out[m, inter] = silu_mul(a @ gate^T, a @ up^T) with W = [gate; up] ([2*inter, k]); m <= 32."""
+    sb = scratch.numel() * scratch.element_size() if scratch is not None else 0
+    check(load().wein_b200_gemm_swiglu(_ptr(a), _ptr(w_gate_up), _ptr(out), U32(m), U32(inter), U32(k), _ptr(scratch), U64(sb), _stream()))
+
+
+def gemm_tune(kw=0, ksplit=0, unr=0):
+    """Benchmark hook: force the skinny GEMM's decomposition (0 = automatic)."""
+    load().wein_b200_gemm_tune(U32(kw), U32(ksplit), U32(unr))
