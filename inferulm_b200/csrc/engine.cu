@@ -368,7 +368,13 @@ extern "C" int32_t wein_b200_engine_admit(wein_b200_engine *e, uint32_t slot, co
 }
 
 // ------------------------------------------------------------------------------------------------ forward passes
+// Profiling hook (ablation, as the reference's WEIN_ABLATE): bit 0 skips every GEMM launch, so a timed round shows the
+// cost of everything else; results are then meaningless.  Never set outside measurements.
+static uint32_t g_ablate = 0;
+extern "C" void wein_b200_engine_ablate(uint32_t mask) { g_ablate = mask; }
+
 static int32_t gemm(Engine *e, const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, cudaStream_t st) {
+    if (g_ablate & 1u) return WB_OK;
     e->launches++;
     return wb_gemm_wt(a, w, c, m, n, k, lda, ldc, e->gemm_scratch, e->gemm_scratch_bytes, st);
 }
@@ -402,6 +408,7 @@ static int32_t mlp_block(Engine *e, const wein_b200_layer_weights &w, uint32_t T
     if (T <= 32 && adjacent(w.wg, w.wu, (size_t)II * H)) {
         // gate|up projection with the SwiGLU activation in the epilogue: one launch, no [T, 2*inter] round trip
         e->launches++;
+        if (!(g_ablate & 1u))
         TRY(wb_gemm_swiglu(e->n2, w.wg, e->m, T, II, H, H, II, e->gemm_scratch, e->gemm_scratch_bytes, st));
         TRY(gemm(e, e->m, w.wd, e->d, T, H, II, II, H, st));
         return WB_OK;
