@@ -96,6 +96,16 @@ int32_t wein_b200_gdn_verify(const void *q, const void *k, const void *v, uint32
                              const void *in_row, const void *out_base, const void *specs, uint32_t n_rows, uint32_t k_heads,
                              uint32_t v_heads, uint32_t k_dim, uint32_t v_dim, float l2_eps, uint32_t rows_per_warp, void *stream);
 
+/* The whole token mixer of a gated-DeltaNet layer for chain spans of <= 8 tokens in one launch: conv1d_dw + conv_state_roll +
+ * dn_split_qkv + dn_qk_l2norm + deltanet + rms_norm_gated of the reference's layer (crates/wein-exec/src/qwen.rs:3971-4077), same
+ * values bit for bit.  proj [tokens, ld] = raw qkv (2*k_heads*128 + v_heads*128) | z (v_heads*128) | a (v_heads) | b (v_heads);
+ * out [tokens, v_heads*128] = gated-normalised core output.  Span r reads conv / recurrent state row in_row[r] and writes the
+ * rows after its token t to out_base[r]+t in both pools. */
+int32_t wein_b200_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log,
+                            const void *dt_bias, const void *norm_w, void *state, uint32_t state_f32, void *out,
+                            const void *row_start, const void *row_count, const void *in_row, const void *out_base,
+                            uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps, float rms_eps, void *stream);
+
 /* PagedAttnOp::run (ops/mod.rs:1687-1704) plus the scratch buffer that the reference's op object owns privately
  * (wein_b200_attn_scratch_bytes(tokens, kv_heads, head_dim, 16) bytes).  16-token pages; head_dim 64 / 128 / 256. */
 uint64_t wein_b200_attn_scratch_bytes(uint32_t n_spans, uint32_t kv_heads, uint32_t head_dim, uint32_t max_segs);
@@ -119,6 +129,11 @@ int32_t wein_b200_attn_verify(const void *q, const void *k_cache, const void *v_
 uint64_t wein_b200_gemm_scratch_bytes(uint32_t n_max);
 int32_t wein_b200_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, void *scratch,
                           uint64_t scratch_bytes, void *stream);
+/* Gate|up projection with the SwiGLU activation in the epilogue (GemmOp::run_wt x2 + SiluMulOp of the reference's MLP,
+ * crates/wein-exec/src/qwen.rs:4090-4099): w_gate_up = [gate; up] of shape [2*inter, k]; out[m, inter] holds exactly the
+ * values silu_mul produces from the two separately rounded projections.  m <= 32. */
+int32_t wein_b200_gemm_swiglu(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k,
+                              void *scratch, uint64_t scratch_bytes, void *stream);
 
 /* ArgmaxRowsOp::run (ops/mod.rs:1332-1367): total order (value desc, index asc); scratch = s*32 u64 words;
  * a row with no comparable element yields 0xFFFFFFFF, as the reference. */

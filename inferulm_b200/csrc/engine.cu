@@ -74,6 +74,9 @@ struct wein_b200_engine {
     size_t h_stage_words = 0;
     std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint32_t>, cudaGraphExec_t> graphs;
     uint32_t launches = 0, last_launches = 0;
+    // weight matrices in the order a round multiplies them (for the next-weights L2 prefetch); empty = no prefetch
+    std::vector<std::pair<const void *, uint64_t>> chain;
+    size_t chain_pos = 0;
     std::map<std::string, std::pair<void *, uint64_t>> named;
 };
 typedef wein_b200_engine Engine;
@@ -373,9 +376,19 @@ extern "C" int32_t wein_b200_engine_admit(wein_b200_engine *e, uint32_t slot, co
 static uint32_t g_ablate = 0;
 extern "C" void wein_b200_engine_ablate(uint32_t mask) { g_ablate = mask; }
 
+// Tells the GEMM about to be launched which weights come after it in the round, if this launch is where the chain expects it.
+static void chain_hint(Engine *e, const void *w) {
+    if (e->chain.empty()) return;
+    if (e->chain[e->chain_pos % e->chain.size()].first != w) { e->chain.clear(); return; }  // order differs: stop hinting
+    const auto &nx = e->chain[(e->chain_pos + 1) % e->chain.size()];
+    wb_gemm_set_next(nx.first, nx.second);
+    e->chain_pos++;
+}
+
 static int32_t gemm(Engine *e, const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, cudaStream_t st) {
     if (g_ablate & 1u) return WB_OK;
     e->launches++;
+    chain_hint(e, w);
     return wb_gemm_wt(a, w, c, m, n, k, lda, ldc, e->gemm_scratch, e->gemm_scratch_bytes, st);
 }
 
@@ -408,6 +421,7 @@ static int32_t mlp_block(Engine *e, const wein_b200_layer_weights &w, uint32_t T
     if (T <= 32 && adjacent(w.wg, w.wu, (size_t)II * H)) {
         // gate|up projection with the SwiGLU activation in the epilogue: one launch, no [T, 2*inter] round trip
         e->launches++;
+        chain_hint(e, w.wg);
         if (!(g_ablate & 1u))
         TRY(wb_gemm_swiglu(e->n2, w.wg, e->m, T, II, H, H, II, e->gemm_scratch, e->gemm_scratch_bytes, st));
         TRY(gemm(e, e->m, w.wd, e->d, T, H, II, II, H, st));
@@ -450,14 +464,10 @@ static int32_t forward(Engine *e, uint32_t T, uint32_t n_spans, uint32_t max_cou
                 TRY(gemm(e, e->n1, w.a, e->proj + e->cd + e->vald, T, vh, H, H, e->lpn, st));
                 TRY(gemm(e, e->n1, w.b, e->proj + e->cd + e->vald + vh, T, vh, H, H, e->lpn, st));
             }
-            TRY(wein_b200_conv_verify(e->proj, e->lpn, w.conv, e->conv_state[li], e->qkvc, e->d_row_start, e->d_row_count, e->d_in_row,
-                                      e->d_out_base, e->cd, 4, n_spans, st));
-            TRY(wein_b200_gdn_verify(e->qkvc, e->qkvc + e->keyd, e->qkvc + 2 * e->keyd, e->cd, e->cd, e->cd, e->proj + e->cd + e->vald,
-                                     e->proj + e->cd + e->vald + vh, e->lpn, w.a_log, w.dt_bias, e->lin_state[li], c.state_f32, e->core,
-                                     e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base, nullptr, n_spans, c.lin_k_heads, vh, 128, 128,
-                                     c.l2_eps, 0, st));
-            TRY(wb_rms_norm_gated_rows(e->core, e->proj + e->cd, e->lpn, (const float *)w.norm, e->normed, T, vh, 128, c.rms_eps, st));
-            e->launches += 3;
+            // conv + SiLU + conv rows + l2 norms + gates + chain recurrence + gated norm: one launch per layer
+            TRY(wb_gdn_layer(e->proj, e->lpn, w.conv, e->conv_state[li], w.a_log, w.dt_bias, w.norm, e->lin_state[li], c.state_f32, e->normed,
+                             e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base, n_spans, c.lin_k_heads, vh, c.l2_eps, c.rms_eps, st));
+            e->launches += 1;
             TRY(gemm(e, e->normed, w.out, e->o, T, H, e->vald, e->vald, H, st));
             li++;
         }
@@ -514,8 +524,38 @@ static int32_t mtp_forward(Engine *e, uint32_t n, uint32_t i, bool sampled, cuda
     return WB_OK;
 }
 
+// The order in which a round of k drafts + one verify forward multiplies its weight matrices (fused layouts only).
+static void build_chain(Engine *e, uint32_t k, uint32_t T) {
+    e->chain.clear();
+    e->chain_pos = 0;
+    const wein_b200_model_cfg &c = e->cfg;
+    const uint64_t H = e->H, II = e->II, qd = (uint64_t)c.q_heads * c.head_dim, he = (uint64_t)c.kv_heads * c.head_dim;
+    if (T > 32) return;
+    auto layer_ok = [&](const wein_b200_layer_weights &w, bool full) {
+        if (!adjacent(w.wg, w.wu, II * H)) return false;
+        if (full) return adjacent(w.qg, w.k, 2 * qd * H) && adjacent(w.k, w.v, he * H);
+        return adjacent(w.qkv, w.z, (uint64_t)e->cd * H) && adjacent(w.z, w.a, (uint64_t)e->vald * H) && adjacent(w.a, w.b, (uint64_t)c.lin_v_heads * H);
+    };
+    auto push_layer = [&](const wein_b200_layer_weights &w, bool full) {
+        if (full) { e->chain.push_back({w.qg, (uint64_t)e->fpn * H * 2}); e->chain.push_back({w.o, H * qd * 2}); }
+        else { e->chain.push_back({w.qkv, (uint64_t)e->lpn * H * 2}); e->chain.push_back({w.out, H * e->vald * 2}); }
+        e->chain.push_back({w.wg, 2 * II * H * 2});
+        e->chain.push_back({w.wd, H * II * 2});
+    };
+    for (uint32_t l = 0; l < c.n_layers; l++) if (!layer_ok(e->w.layers[l], c.layer_is_full[l])) return;
+    if (k && !layer_ok(e->w.mtp_layer, true)) return;
+    for (uint32_t i = 0; i < k; i++) {
+        e->chain.push_back({e->w.mtp_fc, 2 * H * H * 2});
+        push_layer(e->w.mtp_layer, true);
+        e->chain.push_back({e->w.embed, (uint64_t)e->V * H * 2});
+    }
+    for (uint32_t l = 0; l < c.n_layers; l++) push_layer(e->w.layers[l], c.layer_is_full[l]);
+    e->chain.push_back({e->w.embed, (uint64_t)e->V * H * 2});
+}
+
 static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32_t max_ctx, cudaStream_t st) {
     const uint32_t P = k + 1, T = n * P, km = e->cfg.k_max ? e->cfg.k_max : 1;
+    build_chain(e, k, T);
     for (uint32_t i = 0; i < k; i++) TRY(mtp_forward(e, n, i, sampled, st));
     WB_LAUNCH((verify_prep_kernel), (n + 127) / 128, 128, 0, st, e->d_slots, slot_state(e), e->d_drafts, km, n, P, e->rows_per_slot, e->P, e->d_tok,
                                                       e->d_pos_rows, e->d_seq_rows, e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base,
@@ -643,6 +683,7 @@ extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, con
                                              e->d_lg_rows, e->d_lg_of);
         WB_LAUNCH_CHECK();
         uint32_t max_ctx = base + P < e->bpr * 16 ? base + P : e->bpr * 16;
+        e->chain.clear();
         TRY(forward(e, T, n, P, max_ctx, n_lg, false, st));
         if (n_lg > 0) {
             if (!sampled) {

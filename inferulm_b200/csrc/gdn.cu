@@ -20,6 +20,7 @@
 // every store, as the reference's pool); the f32-pool mode keeps the same tree
 // without that rounding.  Compiled with -fmad=false.
 #include "common.cuh"
+#include "internal.h"
 
 struct GdnParams {
     const bf16_t *q, *k, *v, *a, *b;   // per-token inputs
@@ -264,3 +265,206 @@ int32_t wein_b200_gdn_verify(const void *q, const void *k, const void *v, uint32
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Whole gated-DeltaNet token mixer of a layer in one launch: causal depthwise conv + SiLU on the k-head's q / k channels and
+// the v-head's v channels (with the per-position conv-state rows), l2 norms, gates, the chain recurrence above, and the
+// gated RMSNorm of the head's output.  Replaces conv1d_dw + conv_state_roll + dn_split_qkv + dn_qk_l2norm + deltanet +
+// rms_norm_gated of the reference's layer (crates/wein-exec/src/qwen.rs:3971-4077) with bit-identical values: every
+// intermediate keeps its bf16 rounding point.  One CTA = (span, v-head): 16 warps x 8 v-rows.  Spans hold <= 8 tokens.
+struct GdnLayerParams {
+    const bf16_t *proj;        // [tokens, ld]: raw qkv (conv_dim) | z (v_heads*128) | a (v_heads) | b (v_heads)
+    uint32_t ld;
+    const bf16_t *conv_w;      // [conv_dim, 4]
+    bf16_t *conv_state;        // [rows, conv_dim, 3]
+    const float *a_log;
+    const bf16_t *dt_bias;
+    const float *norm_w;       // [128]
+    void *state;               // [rows, v_heads, 128, 128]
+    bf16_t *out;               // [tokens, v_heads*128] gated-normalised core output
+    const uint32_t *row_start, *row_count, *in_row, *out_base;
+    uint32_t n_rows, k_heads, v_heads;
+    float l2_eps, rms_eps;
+};
+
+template <bool F32>
+__global__ void __launch_bounds__(512) gdn_layer_kernel(const GdnLayerParams P) {
+    PDL_ENTRY();
+    constexpr int KD = 128, VD = 128, R = 8, WARPS = 16, MAXT = 8;
+    __shared__ float T[WARPS][R][33];
+    __shared__ bf16_t qc[MAXT][KD], kc[MAXT][KD], vc[MAXT][VD];
+    __shared__ float o_s[MAXT][VD];
+    __shared__ float inv_s[MAXT][2], gate_s[MAXT][2], red_s[4][4];
+    const unsigned full = 0xffffffffu;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const uint32_t r = blockIdx.x / P.v_heads, h = blockIdx.x % P.v_heads;
+    const uint32_t t0 = P.row_start[r], cnt = min(P.row_count[r], (uint32_t)MAXT);
+    if (cnt == 0) return;
+    const size_t in_row = P.in_row[r], base = P.out_base[r];
+    const uint32_t group = P.v_heads / P.k_heads, kh = h / group;
+    const uint32_t keyd = P.k_heads * KD, vald = P.v_heads * VD, cd = 2 * keyd + vald;
+    const uint32_t row0 = w * R;
+    const size_t head_elems = (size_t)VD * KD, row_elems = (size_t)P.v_heads * head_elems;
+    // the one HBM read of the state goes out first
+    float S[R][4];
+    {
+        size_t e0 = in_row * row_elems + (size_t)h * head_elems + (size_t)row0 * KD + lane * 4;
+#pragma unroll
+        for (int i = 0; i < R; i++) StateIO<F32>::load(P.state, e0 + (size_t)i * KD, S[i]);
+    }
+    // ---- conv + SiLU (reference.rs:476-506) and conv-state rows (reference.rs:511-562): one thread per channel
+    if (tid < 3 * KD) {
+        const uint32_t part = tid / KD, i = tid % KD;
+        const uint32_t ch = part == 0 ? kh * KD + i : (part == 1 ? keyd + kh * KD + i : 2 * keyd + h * VD + i);
+        const bool owns_state = part == 2 || (h % group) == 0;   // q / k channels are shared by the v-heads of a k-head
+        const bf16_t *sp = P.conv_state + ((size_t)in_row * cd + ch) * 3;
+        bf16_t w0 = sp[0], w1 = sp[1], w2 = sp[2];
+        const float k0 = bf2f(P.conv_w[(size_t)ch * 4 + 0]), k1 = bf2f(P.conv_w[(size_t)ch * 4 + 1]),
+                    k2 = bf2f(P.conv_w[(size_t)ch * 4 + 2]), k3 = bf2f(P.conv_w[(size_t)ch * 4 + 3]);
+        bf16_t (*dst)[KD] = part == 0 ? qc : (part == 1 ? kc : vc);
+        for (uint32_t t = 0; t < cnt; t++) {
+            bf16_t xv = P.proj[(size_t)(t0 + t) * P.ld + ch];
+            float acc = 0.0f;
+            acc = __fadd_rn(__fmul_rn(bf2f(w0), k0), acc);
+            acc = __fadd_rn(__fmul_rn(bf2f(w1), k1), acc);
+            acc = __fadd_rn(__fmul_rn(bf2f(w2), k2), acc);
+            acc = __fadd_rn(__fmul_rn(bf2f(xv), k3), acc);
+            dst[t][i] = f2bf(silu_ref(rbf(acc)));
+            w0 = w1; w1 = w2; w2 = xv;
+            if (owns_state) {
+                bf16_t *dp = P.conv_state + ((size_t)(base + t) * cd + ch) * 3;
+                dp[0] = w0; dp[1] = w1; dp[2] = w2;
+            }
+        }
+    } else if (tid < 3 * KD + MAXT) {
+        // gates (reference.rs:624-626), one thread per token
+        const uint32_t t = tid - 3 * KD;
+        if (t < cnt) {
+            const size_t g = t0 + t;
+            const float av = bf2f(P.proj[g * P.ld + cd + vald + h]), bv = bf2f(P.proj[g * P.ld + cd + vald + P.v_heads + h]);
+            const float big_a = expf_ref(P.a_log[h]);
+            gate_s[t][0] = expf_ref(__fsub_rn(0.0f, __fmul_rn(big_a, softplus_ref(__fadd_rn(av, bf2f(P.dt_bias[h]))))));
+            gate_s[t][1] = rbf(sigmoid_ref(bv));
+        }
+    }
+    __syncthreads();
+    // ---- l2 norms of q and k (reference.rs:629-637): thread (t, which) sums 128 squares in order, two roundings per term
+    if (tid < 2 * (int)cnt) {
+        const bf16_t *src = (tid & 1) ? kc[tid >> 1] : qc[tid >> 1];
+        float s = 0.0f;
+        for (int j = 0; j < KD; j++) { float x = bf2f(src[j]); s = __fadd_rn(__fmul_rn(x, x), s); }
+        inv_s[tid >> 1][tid & 1] = __fdiv_rn(1.0f, sqrtf(__fadd_rn(s, P.l2_eps)));
+    }
+    __syncthreads();
+    const float kd_sqrt = sqrtf((float)KD);
+    for (uint32_t i = 0; i < cnt; i++) {
+        const float invq = inv_s[i][0], invk = inv_s[i][1], decay = gate_s[i][0], beta = gate_s[i][1];
+        float kk[4], qq[4];
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            kk[u] = __fmul_rn(bf2f(kc[i][lane * 4 + u]), invk);
+            qq[u] = __fdiv_rn(__fmul_rn(bf2f(qc[i][lane * 4 + u]), invq), kd_sqrt);
+        }
+        float vin = 0.0f;
+        if (lane < R) vin = bf2f(vc[i][row0 + lane]);
+#pragma unroll
+        for (int rr = 0; rr < R; rr++) {
+            float p = 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                S[rr][u] = __fmul_rn(S[rr][u], decay);
+                p = fmaf(S[rr][u], kk[u], p);
+            }
+            T[w][rr][lane] = p;
+        }
+        __syncwarp();
+        float delta = 0.0f;
+        if (lane < R) {
+            float kvm = 0.0f;
+#pragma unroll 8
+            for (int sl = 0; sl < 32; sl++) kvm = __fadd_rn(T[w][lane][sl], kvm);
+            delta = __fmul_rn(__fsub_rn(vin, kvm), beta);
+        }
+        __syncwarp();
+#pragma unroll
+        for (int rr = 0; rr < R; rr++) {
+            float d = __shfl_sync(full, delta, rr);
+            float p = 0.0f;
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                float s = fmaf(kk[u], d, S[rr][u]);
+                if (!F32) s = rbf(s);
+                S[rr][u] = s;
+                p = fmaf(s, qq[u], p);
+            }
+            T[w][rr][lane] = p;
+        }
+        __syncwarp();
+        if (lane < R) {
+            float o = 0.0f;
+#pragma unroll 8
+            for (int sl = 0; sl < 32; sl++) o = __fadd_rn(T[w][lane][sl], o);
+            o_s[i][row0 + lane] = rbf(o);   // the core output is stored as bf16 by the reference before the norm reads it
+        }
+        __syncwarp();
+        size_t e0 = (base + i) * row_elems + (size_t)h * head_elems + (size_t)row0 * KD + lane * 4;
+#pragma unroll
+        for (int rr = 0; rr < R; rr++) StateIO<F32>::store(P.state, e0 + (size_t)rr * KD, S[rr]);
+    }
+    __syncthreads();
+    // ---- gated RMSNorm over the head (reference.rs:699-713): warp-group g = tid / 128 takes tokens g, g+4
+    {
+        const int grp = tid >> 7, i = tid & 127, wl = (tid >> 5) & 3;
+        for (uint32_t tb = 0; tb < cnt; tb += 4) {
+            const uint32_t t = tb + grp;
+            const bool live = t < cnt;
+            float v = live ? o_s[t][i] : 0.0f;
+            float s = fmaf(v, v, 0.0f);
+#pragma unroll
+            for (int off = 16; off >= 1; off >>= 1) {
+                float o2 = __shfl_down_sync(full, s, off);
+                if (lane + off < 32) s = __fadd_rn(s, o2);
+            }
+            if (lane == 0) red_s[grp][wl] = s;
+            __syncthreads();
+            // second level of the block tree over 4 warp leaders: (w0 + w2) + (w1 + w3)
+            float total = __fadd_rn(__fadd_rn(red_s[grp][0], red_s[grp][2]), __fadd_rn(red_s[grp][1], red_s[grp][3]));
+            __syncthreads();
+            if (live) {
+                float inv = 1.0f / sqrtf(total / (float)VD + P.rms_eps);
+                float xw = P.norm_w[i] * rbf(v * inv);
+                float zv = bf2f(P.proj[(size_t)(t0 + t) * P.ld + cd + h * VD + i]);
+                P.out[((size_t)(t0 + t) * P.v_heads + h) * VD + i] = f2bf(xw * (zv * (1.0f / (1.0f + expf_ref(-zv)))));
+            }
+        }
+    }
+}
+
+int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log, const void *dt_bias,
+                     const void *norm_w, void *state, uint32_t state_f32, void *out, const void *row_start, const void *row_count,
+                     const void *in_row, const void *out_base, uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps,
+                     float rms_eps, cudaStream_t st) {
+    WB_CHECK_ARG(proj && conv_w && conv_state && a_log && dt_bias && norm_w && state && out && row_start && row_count && in_row && out_base,
+                 "gdn_layer: null pointer");
+    WB_CHECK_ARG(k_heads > 0 && v_heads % k_heads == 0, "gdn_layer: v_heads %u must be a multiple of k_heads %u", v_heads, k_heads);
+    if (n_rows == 0) return WB_OK;
+    GdnLayerParams p{};
+    p.proj = (const bf16_t *)proj; p.ld = ld; p.conv_w = (const bf16_t *)conv_w; p.conv_state = (bf16_t *)conv_state;
+    p.a_log = (const float *)a_log; p.dt_bias = (const bf16_t *)dt_bias; p.norm_w = (const float *)norm_w; p.state = state;
+    p.out = (bf16_t *)out; p.row_start = (const uint32_t *)row_start; p.row_count = (const uint32_t *)row_count;
+    p.in_row = (const uint32_t *)in_row; p.out_base = (const uint32_t *)out_base;
+    p.n_rows = n_rows; p.k_heads = k_heads; p.v_heads = v_heads; p.l2_eps = l2_eps; p.rms_eps = rms_eps;
+    if (state_f32) WB_LAUNCH((gdn_layer_kernel<true>), n_rows * v_heads, 512, 0, st, p);
+    else WB_LAUNCH((gdn_layer_kernel<false>), n_rows * v_heads, 512, 0, st, p);
+    WB_LAUNCH_CHECK();
+    return WB_OK;
+}
+
+// Chain spans of at most 8 tokens; 128x128 heads, conv width 4.  See the kernel comment for the layout of `proj`.
+extern "C" int32_t wein_b200_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log,
+                                       const void *dt_bias, const void *norm_w, void *state, uint32_t state_f32, void *out,
+                                       const void *row_start, const void *row_count, const void *in_row, const void *out_base,
+                                       uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps, float rms_eps, void *stream) {
+    return wb_gdn_layer(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state_f32, out, row_start, row_count, in_row, out_base,
+                        n_rows, k_heads, v_heads, l2_eps, rms_eps, (cudaStream_t)stream);
+}

@@ -40,6 +40,8 @@ struct WgemmParams {
     float *partial;       // [ksplit][ctas][8/KW tiles * MT*128] when ksplit > 1
     uint32_t *counters;   // [ctas], zero on entry, left zero
     uint32_t m, n, k, lda, ldc, ksplit, kslice;  // kslice: k elements per CTA slice (multiple of 32)
+    const void *next_w;   // weights of the stream's next product (or null): their head is pulled into L2 by this kernel's
+    uint32_t next_lines;  //   CTAs as they finish, so HBM keeps streaming through the kernels in between; count of 128-byte lines
     uint32_t swiglu;      // 1: W = [gate; up] (n = 2*inter rows); tile rows 0-7 are gate rows, 8-15 the matching up rows, and
                           //    the epilogue writes bf16(bf16(silu(bf16 g)) * bf16 u) into C[m, inter]
 };
@@ -127,6 +129,11 @@ __global__ void __launch_bounds__(256) wgemm_kernel(const WgemmParams P) {
                 }
             }
         }
+    }
+    if (P.next_lines) {
+        const char *nb = reinterpret_cast<const char *>(P.next_w);
+        const uint32_t nthreads = gridDim.x * gridDim.y * 256, me = (blockIdx.y * gridDim.x + blockIdx.x) * 256 + threadIdx.x;
+        for (uint32_t ln = me; ln < P.next_lines; ln += nthreads) asm volatile("prefetch.global.L2 [%0];" ::"l"(nb + (size_t)ln * 128));
     }
 #pragma unroll
     for (int mt = 0; mt < MT; mt++)
@@ -230,11 +237,23 @@ static void wgemm_go_kw(const WgemmParams &p, dim3 grid, uint32_t kw, uint32_t u
     }
 }
 
+// One-shot hint consumed by the next skinny-GEMM launch of this thread: the weights the stream multiplies next.
+static thread_local const void *t_next_w = nullptr;
+static thread_local uint64_t t_next_bytes = 0;
+static uint64_t g_prefetch_cap = 48ull << 20;
+void wb_gemm_set_next(const void *w, uint64_t bytes) { t_next_w = w; t_next_bytes = bytes; }
+extern "C" void wein_b200_gemm_prefetch_cap(uint64_t bytes) { g_prefetch_cap = bytes; }
+
 static int32_t wgemm_launch(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc,
                             void *scratch, uint64_t scratch_bytes, bool swiglu, cudaStream_t st) {
     WgemmParams p{};
     p.A = (const bf16_t *)a; p.W = (const bf16_t *)w; p.C = (bf16_t *)c;
     p.m = m; p.n = n; p.k = k; p.lda = lda; p.ldc = ldc; p.swiglu = swiglu ? 1 : 0;
+    if (t_next_w && g_prefetch_cap) {
+        uint64_t nbytes = t_next_bytes < g_prefetch_cap ? t_next_bytes : g_prefetch_cap;
+        p.next_w = t_next_w; p.next_lines = (uint32_t)(nbytes / 128);
+    }
+    t_next_w = nullptr; t_next_bytes = 0;
     uint32_t tiles = swiglu ? (n / 2 + 7) / 8 : (n + 15) / 16;
     int mt = (m + 7) / 8;
     WgemmPlan pl = plan_for(tiles, k, scratch != nullptr);

@@ -7,6 +7,7 @@ int32_t wb_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n
                    void *scratch, uint64_t scratch_bytes, cudaStream_t st);
 int32_t wb_gemm_swiglu(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k, uint32_t lda,
                        uint32_t ldc, void *scratch, uint64_t scratch_bytes, cudaStream_t st);
+void wb_gemm_set_next(const void *w, uint64_t bytes);  // hint for the next skinny GEMM launch: what the stream multiplies after it
 int32_t wb_gemm_warmup();  // creates the cuBLASLt handle and workspace outside any stream capture
 int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, const void *block_table, const void *seq_ids,
                        const void *positions, const void *row_start, const void *row_count, const void *gate, void *out,
@@ -44,3 +45,7 @@ int32_t wb_silu_mul_rows(const void *gu, uint32_t ld, void *out, uint32_t rows, 
 int32_t wb_argmax_finish(const void *part, uint32_t split, uint32_t *out, uint32_t out_mul, uint32_t out_off, uint32_t s, cudaStream_t st);
 int32_t wb_rms_norm_gated_rows(const void *x, const void *z, uint32_t z_tok_stride, const float *w, void *out, uint32_t tokens,
                                uint32_t heads, uint32_t hidden, float eps, cudaStream_t st);
+int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log, const void *dt_bias,
+                     const void *norm_w, void *state, uint32_t state_f32, void *out, const void *row_start, const void *row_count,
+                     const void *in_row, const void *out_base, uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps,
+                     float rms_eps, cudaStream_t st);

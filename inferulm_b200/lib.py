@@ -33,6 +33,8 @@ def load():
         _lib = C.CDLL(LIB_PATH)
         _lib.wein_b200_last_error.restype = C.c_char_p
         _lib.wein_b200_abi_version.restype = C.c_uint32
+        if os.environ.get("WEIN_B200_PREFETCH_MB"):  # A/B switch: cap of the next-weights L2 prefetch (0 = off)
+            _lib.wein_b200_gemm_prefetch_cap(C.c_uint64(int(os.environ["WEIN_B200_PREFETCH_MB"]) << 20))
         if os.environ.get("WEIN_B200_ABLATE"):  # profiling only: see wein_b200_engine_ablate
             _lib.wein_b200_engine_ablate(C.c_uint32(int(os.environ["WEIN_B200_ABLATE"])))
         if os.environ.get("WEIN_B200_PDL", "1") == "0":  # A/B switch: launch every kernel fully serialised

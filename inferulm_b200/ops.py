@@ -184,3 +184,10 @@ def gemm_swiglu(a, w_gate_up, out, m, inter, k, scratch=None):
 def gemm_tune(kw=0, ksplit=0, unr=0):
     """Benchmark hook: force the skinny GEMM's decomposition (0 = automatic)."""
     load().wein_b200_gemm_tune(U32(kw), U32(ksplit), U32(unr))
+
+
+def gdn_layer(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state_f32, out, row_start, row_count, in_row, out_base,
+              n_rows, k_heads, v_heads, l2_eps, rms_eps):
+    check(load().wein_b200_gdn_layer(_ptr(proj), U32(ld), _ptr(conv_w), _ptr(conv_state), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w),
+                                     _ptr(state), U32(state_f32), _ptr(out), _ptr(row_start), _ptr(row_count), _ptr(in_row),
+                                     _ptr(out_base), U32(n_rows), U32(k_heads), U32(v_heads), F32(l2_eps), F32(rms_eps), _stream()))

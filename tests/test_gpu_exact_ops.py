@@ -229,3 +229,56 @@ def test_argmax_rows_total_order(ops):
         out = torch.empty(s, dtype=torch.int32, device="cuda")
         ops.argmax_rows(dev(x.reshape(-1)), dev(rows), scratch, out, n, s)
         assert np.array_equal(host(out, np.uint32), orc.argmax_rows(x.reshape(-1), rows, n)), (s, n)
+
+
+@pytest.mark.parametrize("state_f32", [1, 0])
+def test_gdn_layer_fusion_equals_operator_chain(ops, state_f32):
+    """The one-launch DeltaNet token mixer against the oracle's operator chain conv1d_dw -> conv_state_roll ->
+    deltanet -> rms_norm_gated on the BASELINE layer shape (16 qk / 32 v heads), ragged chain lengths, bit for bit."""
+    rs = np.random.default_rng(21)
+    kh, vh = 16, 32
+    keyd, vald = kh * 128, vh * 128
+    cd = 2 * keyd + vald
+    ld = cd + vald + 2 * vh
+    counts = [4, 1, 8, 3]
+    n = len(counts)
+    T = sum(counts)
+    row_start = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.uint32)
+    row_count = np.array(counts, np.uint32)
+    pool_rows = n * 16
+    in_row = (np.arange(n) * 16 + 2).astype(np.uint32)
+    out_base = (np.arange(n) * 16 + 8).astype(np.uint32)
+    proj = rand_bf16(rs, T * ld, 1.0).reshape(T, ld)
+    conv_w = rand_bf16(rs, cd * 4, 0.5)
+    conv_state = rand_bf16(rs, pool_rows * cd * 3, 1.0)
+    a_log = (rs.standard_normal(vh) * 0.5).astype(np.float32)
+    dtb = rand_bf16(rs, vh, 0.5)
+    norm_w = (1 + 0.1 * rs.standard_normal(128)).astype(np.float32)
+    st16 = rand_bf16(rs, pool_rows * vh * 128 * 128, 0.3)
+    state = orc.bf16_to_f32(st16).copy() if state_f32 else st16
+    # oracle chain, span by span (rows remapped: the oracle's chain writes head+1.., ours writes out_base..)
+    want_out = np.zeros(T * vald, np.uint16)
+    want_conv = conv_state.reshape(pool_rows, -1).copy()
+    want_state = state.reshape(pool_rows, -1).copy()
+    for s in range(n):
+        t0, c = int(row_start[s]), counts[s]
+        x = proj[t0:t0 + c, :cd].reshape(-1)
+        cs = np.zeros((c + 1, cd * 3), np.uint16); cs[0] = conv_state.reshape(pool_rows, -1)[in_row[s]]
+        convd = orc.conv1d_dw(x, conv_w, cs.reshape(-1), [0] * c, list(range(c)), cd, 4).reshape(c, cd)
+        rolled = orc.conv_state_roll(x, cs.reshape(-1), [0], [c], [0], cd, 4, [1]).reshape(c + 1, -1)
+        want_conv[out_base[s]:out_base[s] + c] = rolled[1:]
+        ls = np.zeros((c + 1, vh * 128 * 128), state.dtype); ls[0] = state.reshape(pool_rows, -1)[in_row[s]]
+        core, st = orc.deltanet(convd[:, :keyd].reshape(-1), convd[:, keyd:2 * keyd].reshape(-1), convd[:, 2 * keyd:].reshape(-1),
+                                proj[t0:t0 + c, cd + vald:cd + vald + vh].reshape(-1), proj[t0:t0 + c, cd + vald + vh:].reshape(-1),
+                                a_log, dtb, ls.reshape(-1), [0], [c], [0], kh, vh, 128, 128, 1e-6, [1], state_mode=state_f32, threads=8)
+        want_state[out_base[s]:out_base[s] + c] = st.reshape(c + 1, -1)[1:]
+        z = proj[t0:t0 + c, cd:cd + vald].reshape(-1)
+        want_out[t0 * vald:(t0 + c) * vald] = orc.rms_norm_gated(core, z, norm_w, c * vh, 128, 1e-6)
+    cs_d, st_d = dev(conv_state), dev(state)
+    out = torch.zeros(T * vald, dtype=torch.int16, device="cuda")
+    ops.gdn_layer(dev(proj.reshape(-1)), ld, dev(conv_w), cs_d, dev(a_log), dev(dtb), dev(norm_w), st_d, state_f32, out, dev(row_start),
+                  dev(row_count), dev(in_row), dev(out_base), n, kh, vh, 1e-6, 1e-6)
+    assert np.array_equal(u16(out), want_out)
+    assert np.array_equal(u16(cs_d), want_conv.reshape(-1))
+    got_state = host(st_d, np.float32 if state_f32 else np.uint16)
+    assert np.array_equal(got_state.view(np.uint32 if state_f32 else np.uint16), want_state.reshape(-1).view(np.uint32 if state_f32 else np.uint16))
