@@ -371,8 +371,9 @@ extern "C" int32_t wein_b200_engine_admit(wein_b200_engine *e, uint32_t slot, co
 }
 
 // ------------------------------------------------------------------------------------------------ forward passes
-// Profiling hook (ablation, as the reference's WEIN_ABLATE): bit 0 skips every GEMM launch, so a timed round shows the
-// cost of everything else; results are then meaningless.  Never set outside measurements.
+// Profiling hook (ablation, as the reference's WEIN_ABLATE): bit 0 skips every GEMM launch, bit 1 the residual-add+norm
+// kernels, bit 2 the DeltaNet layer kernel, bit 3 the attention kernels (q/k prep, attention, combine), so timed rounds
+// attribute the in-graph cost of each class; results are then meaningless.  Never set outside measurements.
 static uint32_t g_ablate = 0;
 extern "C" void wein_b200_engine_ablate(uint32_t mask) { g_ablate = mask; }
 
@@ -406,11 +407,13 @@ static int32_t full_attn_block(Engine *e, const wein_b200_layer_weights &w, void
         TRY(gemm(e, e->n1, w.k, e->proj + 2 * qd, T, he, H, H, e->fpn, st));
         TRY(gemm(e, e->n1, w.v, e->proj + 2 * qd + he, T, he, H, H, e->fpn, st));
     }
+    if (!(g_ablate & 8u)) {
     TRY(wb_qk_prep(e->proj, e->fpn, w.qn, w.kn, e->cosv, e->sinv, rope_pos, kv_pos, seq_ids, bt, bpr, e->qh, e->gate, kp, vp, T, c.q_heads,
                    c.kv_heads, c.head_dim, c.rot_dim, c.rms_eps, st));
     float q_scale = 1.0f / sqrtf((float)c.head_dim);
     TRY(wb_attn_verify(e->qh, kp, vp, bt, seq_ids, kv_pos, row_start, row_count, e->gate, e->attn, q_scale, bpr, 16, c.q_heads, c.kv_heads,
                        c.head_dim, n_spans, max_count, max_ctx, seg_pages, e->attn_scratch, e->attn_scratch_bytes, st));
+    }
     e->launches += 3;
     TRY(gemm(e, e->attn, w.o, e->o, T, H, qd, qd, H, st));
     return WB_OK;
@@ -465,16 +468,16 @@ static int32_t forward(Engine *e, uint32_t T, uint32_t n_spans, uint32_t max_cou
                 TRY(gemm(e, e->n1, w.b, e->proj + e->cd + e->vald + vh, T, vh, H, H, e->lpn, st));
             }
             // conv + SiLU + conv rows + l2 norms + gates + chain recurrence + gated norm: one launch per layer
-            TRY(wb_gdn_layer(e->proj, e->lpn, w.conv, e->conv_state[li], w.a_log, w.dt_bias, w.norm, e->lin_state[li], c.state_f32, e->normed,
+            if (!(g_ablate & 4u)) TRY(wb_gdn_layer(e->proj, e->lpn, w.conv, e->conv_state[li], w.a_log, w.dt_bias, w.norm, e->lin_state[li], c.state_f32, e->normed,
                              e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base, n_spans, c.lin_k_heads, vh, c.l2_eps, c.rms_eps, st));
             e->launches += 1;
             TRY(gemm(e, e->normed, w.out, e->o, T, H, e->vald, e->vald, H, st));
             li++;
         }
-        TRY(wein_b200_add_norm_zc(e->x, e->o, w.ln2, e->h2, e->n2, T, H, c.rms_eps, st));
+        if (!(g_ablate & 2u)) TRY(wein_b200_add_norm_zc(e->x, e->o, w.ln2, e->h2, e->n2, T, H, c.rms_eps, st));
         TRY(mlp_block(e, w, T, st));
         bool last = l + 1 == c.n_layers;
-        TRY(wein_b200_add_norm_zc(e->h2, e->d, last ? e->w.norm_f : e->w.layers[l + 1].ln1, e->x, last ? e->n2 : e->n1, T, H, c.rms_eps, st));
+        if (!(g_ablate & 2u)) TRY(wein_b200_add_norm_zc(e->h2, e->d, last ? e->w.norm_f : e->w.layers[l + 1].ln1, e->x, last ? e->n2 : e->n1, T, H, c.rms_eps, st));
         e->launches += 2;
     }
     if (n_lg == 0) return WB_OK;

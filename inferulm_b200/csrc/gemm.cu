@@ -240,7 +240,7 @@ static void wgemm_go_kw(const WgemmParams &p, dim3 grid, uint32_t kw, uint32_t u
 // One-shot hint consumed by the next skinny-GEMM launch of this thread: the weights the stream multiplies next.
 static thread_local const void *t_next_w = nullptr;
 static thread_local uint64_t t_next_bytes = 0;
-static uint64_t g_prefetch_cap = 48ull << 20;
+static uint64_t g_prefetch_cap = 0;  // measured on B200: a prefetch issued from a bandwidth-bound kernel's tail only moves time around (off)
 void wb_gemm_set_next(const void *w, uint64_t bytes) { t_next_w = w; t_next_bytes = bytes; }
 extern "C" void wein_b200_gemm_prefetch_cap(uint64_t bytes) { g_prefetch_cap = bytes; }
 
