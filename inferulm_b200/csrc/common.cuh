@@ -120,6 +120,8 @@ __device__ __forceinline__ float block_sum_tree(float v, float *smem /* >= 33 fl
 // while its predecessor in the stream is still running.  Every kernel of this library begins with PDL_ENTRY(): it lets
 // its own successor start early, then waits until the predecessor grid has completed and its writes are visible.  Work
 // that touches no produced data (weight prefetch) may be placed between the two.  Without the attribute both are no-ops.
+// Because a kernel's lifetime now overlaps its producer's, data written by earlier kernels must never be read through the
+// non-coherent path: no __ldg and no `const __restrict__` on such pointers (only weights use ld.global.nc).
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 #define PDL_ENTRY() do { pdl_trigger(); pdl_wait(); } while (0)

@@ -104,7 +104,7 @@ struct SlotState {
 };
 
 // Rows of a speculative round: batch row b = slot slots[b]; chain row j feeds the pending token (j = 0) or draft j-1.
-__global__ void verify_prep_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ drafts, uint32_t k_max,
+__global__ void verify_prep_kernel(const uint32_t *slots, SlotState S, const uint32_t *drafts, uint32_t k_max,
                                    uint32_t n, uint32_t P, uint32_t rows_per_slot, uint32_t bankrows, uint32_t *tok, uint32_t *pos_rows,
                                    uint32_t *seq_rows, uint32_t *row_start, uint32_t *row_count, uint32_t *in_row, uint32_t *out_base,
                                    uint32_t *lg_rows) {
@@ -127,8 +127,8 @@ __global__ void verify_prep_kernel(const uint32_t *__restrict__ slots, SlotState
 
 // Commit of a round (spec_finish, qwen.rs:2433-2460): emitted tokens to the slot's ring, position += a+1, pending =
 // bonus token, state_row = snapshot a of this round's bank, hidden of chain row a stashed for the next draft.
-__global__ void commit_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ accept_len,
-                              const uint32_t *__restrict__ out_tokens, const uint32_t *__restrict__ out_base, const bf16_t *__restrict__ x,
+__global__ void commit_kernel(const uint32_t *slots, SlotState S, const uint32_t *accept_len,
+                              const uint32_t *out_tokens, const uint32_t *out_base, const bf16_t *x,
                               uint32_t P, uint32_t k, uint32_t H) {
     PDL_ENTRY();
     uint32_t b = blockIdx.x, slot = slots[b], a = accept_len[b];
@@ -151,8 +151,8 @@ __global__ void commit_kernel(const uint32_t *__restrict__ slots, SlotState S, c
 }
 
 // Prefill chunk tables: span b holds cnt[b] prompt tokens of slot slots[b] (tokens concatenated in tok_in).
-__global__ void prefill_prep_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ cnt,
-                                    const uint32_t *__restrict__ tok_in, const uint32_t *__restrict__ last, uint32_t n, uint32_t rows_per_slot,
+__global__ void prefill_prep_kernel(const uint32_t *slots, SlotState S, const uint32_t *cnt,
+                                    const uint32_t *tok_in, const uint32_t *last, uint32_t n, uint32_t rows_per_slot,
                                     uint32_t bankrows, uint32_t *tok, uint32_t *pos_rows, uint32_t *seq_rows, uint32_t *row_start,
                                     uint32_t *row_count, uint32_t *in_row, uint32_t *out_base, uint32_t *lg_rows, uint32_t *lg_of) {
     PDL_ENTRY();
@@ -169,9 +169,9 @@ __global__ void prefill_prep_kernel(const uint32_t *__restrict__ slots, SlotStat
         if (c > 0 && last[b]) { lg_rows[nl] = r - 1; lg_of[b] = nl; nl++; }
     }
 }
-__global__ void prefill_commit_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ cnt,
-                                      const uint32_t *__restrict__ row_start, const uint32_t *__restrict__ out_base,
-                                      const uint32_t *__restrict__ lg_of, const uint32_t *__restrict__ first_tok, const bf16_t *__restrict__ x,
+__global__ void prefill_commit_kernel(const uint32_t *slots, SlotState S, const uint32_t *cnt,
+                                      const uint32_t *row_start, const uint32_t *out_base,
+                                      const uint32_t *lg_of, const uint32_t *first_tok, const bf16_t *x,
                                       uint32_t H) {
     PDL_ENTRY();
     uint32_t b = blockIdx.x, slot = slots[b], c = cnt[b];
@@ -194,7 +194,7 @@ __global__ void prefill_commit_kernel(const uint32_t *__restrict__ slots, SlotSt
     }
 }
 // Inputs of draft step i: token = pending (i = 0) or the previous draft; rotary position absolute, KV slot chain-local.
-__global__ void mtp_prep_kernel(const uint32_t *__restrict__ slots, SlotState S, const uint32_t *__restrict__ drafts, uint32_t k_max,
+__global__ void mtp_prep_kernel(const uint32_t *slots, SlotState S, const uint32_t *drafts, uint32_t k_max,
                                 uint32_t n, uint32_t i, uint32_t *tok, uint32_t *rope_pos, uint32_t *kv_pos) {
     PDL_ENTRY();
     uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;

@@ -9,10 +9,10 @@
 // kv_scatter of the reference (crates/wein-exec/src/qwen.rs:3888-3950).  Input row t of `qgkv`:
 // [q_heads x (q | gate) x head_dim | kv_heads x head_dim (k) | kv_heads x head_dim (v)].
 // One block of head_dim threads per (token, unit): unit < q_heads: q head; < q_heads + kv_heads: k head; else v head.
-__global__ void qk_prep_kernel(const bf16_t *__restrict__ qgkv, uint32_t ld, const bf16_t *__restrict__ qn, const bf16_t *__restrict__ kn,
-                               const float *__restrict__ cosv, const float *__restrict__ sinv, const uint32_t *__restrict__ rope_pos,
-                               const uint32_t *__restrict__ kv_pos, const uint32_t *__restrict__ seq_ids,
-                               const uint32_t *__restrict__ block_table, uint32_t bpr, bf16_t *__restrict__ qh, bf16_t *__restrict__ gate,
+__global__ void qk_prep_kernel(const bf16_t *qgkv, uint32_t ld, const bf16_t *qn, const bf16_t *kn,
+                               const float *cosv, const float *sinv, const uint32_t *rope_pos,
+                               const uint32_t *kv_pos, const uint32_t *seq_ids,
+                               const uint32_t *block_table, uint32_t bpr, bf16_t *qh, bf16_t *gate,
                                bf16_t *k_pool, bf16_t *v_pool, uint32_t q_heads, uint32_t kv_heads, uint32_t rot_dim, float eps) {
     PDL_ENTRY();
     __shared__ float red[33];
@@ -72,9 +72,9 @@ int32_t wb_qk_prep(const void *qgkv, uint32_t ld, const void *qn, const void *kn
 // ---- MTP head input: embed gather + the two pre-norms + concatenation ---------------------------------------
 // cat[r] = [ norm_zc(embed[tok[r]], pre_e) | norm_zc(hid[hid_rows[r]], pre_h) ]  (crates/wein-exec/src/qwen.rs:4451-4468:
 // 2 gathers, 2 rms_norm_zc and a batched row copy in the reference).  Block (row, half), 256 threads.
-__global__ void mtp_cat_kernel(const uint32_t *__restrict__ tok, uint32_t tok_stride, const bf16_t *__restrict__ embed,
-                               const bf16_t *__restrict__ hid, const uint32_t *__restrict__ hid_rows, const bf16_t *__restrict__ pre_e,
-                               const bf16_t *__restrict__ pre_h, bf16_t *__restrict__ cat, uint32_t hidden, float eps) {
+__global__ void mtp_cat_kernel(const uint32_t *tok, uint32_t tok_stride, const bf16_t *embed,
+                               const bf16_t *hid, const uint32_t *hid_rows, const bf16_t *pre_e,
+                               const bf16_t *pre_h, bf16_t *cat, uint32_t hidden, float eps) {
     PDL_ENTRY();
     __shared__ float red[33];
     const uint32_t r = blockIdx.x, half = blockIdx.y;
@@ -100,7 +100,7 @@ int32_t wb_mtp_cat(const uint32_t *tok, uint32_t tok_stride, const void *embed, 
 }
 
 // ---- SwiGLU activation on the fused gate|up projection: out[r, i] = bf16(bf16(silu(g)) * u) -----------------
-__global__ void silu_mul_rows_kernel(const bf16_t *__restrict__ gu, uint32_t ld, bf16_t *__restrict__ out, uint32_t inter) {
+__global__ void silu_mul_rows_kernel(const bf16_t *gu, uint32_t ld, bf16_t *out, uint32_t inter) {
     PDL_ENTRY();
     const bf16_t *g = gu + (size_t)blockIdx.y * ld, *u = g + inter;
     uint32_t i = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
@@ -120,7 +120,7 @@ int32_t wb_silu_mul_rows(const void *gu, uint32_t ld, void *out, uint32_t rows, 
 }
 
 // ---- argmax phase 2 with a strided destination (draft token j of batch row r lands at out[r*mul + off]) -----
-__global__ void argmax_finish_kernel(const uint64_t *__restrict__ part, uint32_t split, uint32_t *__restrict__ out, uint32_t out_mul, uint32_t out_off) {
+__global__ void argmax_finish_kernel(const uint64_t *part, uint32_t split, uint32_t *out, uint32_t out_mul, uint32_t out_off) {
     PDL_ENTRY();
     uint32_t r = blockIdx.x;
     uint64_t k = 0ull;
@@ -138,8 +138,8 @@ int32_t wb_argmax_finish(const void *part, uint32_t split, uint32_t *out, uint32
 
 // ---- gated RMSNorm with the gate z read in place from the fused projection output --------------------------
 // Row (t, h): x = core[t, h, :], z = z_base[t*z_tok_stride + h*hidden + :]  (reference.rs:699-713).
-__global__ void rms_norm_gated_rows_kernel(const bf16_t *__restrict__ x, const bf16_t *__restrict__ z, uint32_t z_tok_stride,
-                                           const float *__restrict__ w, bf16_t *__restrict__ out, uint32_t heads, uint32_t hidden, float eps) {
+__global__ void rms_norm_gated_rows_kernel(const bf16_t *x, const bf16_t *z, uint32_t z_tok_stride,
+                                           const float *w, bf16_t *out, uint32_t heads, uint32_t hidden, float eps) {
     PDL_ENTRY();
     __shared__ float red[33];
     const uint32_t t = blockIdx.y, h = blockIdx.x, i = threadIdx.x;

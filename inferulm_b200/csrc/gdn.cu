@@ -295,6 +295,7 @@ __global__ void __launch_bounds__(512) gdn_layer_kernel(const GdnLayerParams P) 
     __shared__ bf16_t qc[MAXT][KD], kc[MAXT][KD], vc[MAXT][VD];
     __shared__ float o_s[MAXT][VD];
     __shared__ float inv_s[MAXT][2], gate_s[MAXT][2], red_s[4][4];
+    __shared__ __align__(16) float kk_s[MAXT][KD], qq_s[MAXT][KD];
     const unsigned full = 0xffffffffu;
     const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
     const uint32_t r = blockIdx.x / P.v_heads, h = blockIdx.x % P.v_heads;
@@ -312,6 +313,15 @@ __global__ void __launch_bounds__(512) gdn_layer_kernel(const GdnLayerParams P) 
 #pragma unroll
         for (int i = 0; i < R; i++) StateIO<F32>::load(P.state, e0 + (size_t)i * KD, S[i]);
     }
+    // operands of the closing gated norm (this thread's element of tokens grp and grp+4): fetched now, used last
+    const int n_grp = tid >> 7, n_i = tid & 127;
+    const float n_wv = P.norm_w[n_i];
+    bf16_t n_z[2];
+#pragma unroll
+    for (int q2 = 0; q2 < 2; q2++) {
+        uint32_t t = n_grp + 4 * q2;
+        n_z[q2] = t < cnt ? P.proj[(size_t)(t0 + t) * P.ld + cd + h * VD + n_i] : (bf16_t)0;
+    }
     // ---- conv + SiLU (reference.rs:476-506) and conv-state rows (reference.rs:511-562): one thread per channel
     if (tid < 3 * KD) {
         const uint32_t part = tid / KD, i = tid % KD;
@@ -322,8 +332,13 @@ __global__ void __launch_bounds__(512) gdn_layer_kernel(const GdnLayerParams P) 
         const float k0 = bf2f(P.conv_w[(size_t)ch * 4 + 0]), k1 = bf2f(P.conv_w[(size_t)ch * 4 + 1]),
                     k2 = bf2f(P.conv_w[(size_t)ch * 4 + 2]), k3 = bf2f(P.conv_w[(size_t)ch * 4 + 3]);
         bf16_t (*dst)[KD] = part == 0 ? qc : (part == 1 ? kc : vc);
-        for (uint32_t t = 0; t < cnt; t++) {
-            bf16_t xv = P.proj[(size_t)(t0 + t) * P.ld + ch];
+        bf16_t xs[MAXT];   // all of the span's inputs first: independent loads, one round trip
+#pragma unroll
+        for (int t = 0; t < MAXT; t++) xs[t] = (uint32_t)t < cnt ? P.proj[(size_t)(t0 + t) * P.ld + ch] : (bf16_t)0;
+#pragma unroll
+        for (int t = 0; t < MAXT; t++) {
+            if ((uint32_t)t >= cnt) break;
+            bf16_t xv = xs[t];
             float acc = 0.0f;
             acc = __fadd_rn(__fmul_rn(bf2f(w0), k0), acc);
             acc = __fadd_rn(__fmul_rn(bf2f(w1), k1), acc);
@@ -356,14 +371,23 @@ __global__ void __launch_bounds__(512) gdn_layer_kernel(const GdnLayerParams P) 
         inv_s[tid >> 1][tid & 1] = __fdiv_rn(1.0f, sqrtf(__fadd_rn(s, P.l2_eps)));
     }
     __syncthreads();
-    const float kd_sqrt = sqrtf((float)KD);
+    // k-hat = k * invk and q-hat = (q * invq) / sqrt(128) for every token, in parallel (reference.rs:651, :675)
+    {
+        const float kd_sqrt = sqrtf((float)KD);
+        for (uint32_t idx = tid; idx < cnt * KD; idx += 512) {
+            uint32_t t = idx / KD, j = idx % KD;
+            kk_s[t][j] = __fmul_rn(bf2f(kc[t][j]), inv_s[t][1]);
+            qq_s[t][j] = __fdiv_rn(__fmul_rn(bf2f(qc[t][j]), inv_s[t][0]), kd_sqrt);
+        }
+    }
+    __syncthreads();
     for (uint32_t i = 0; i < cnt; i++) {
-        const float invq = inv_s[i][0], invk = inv_s[i][1], decay = gate_s[i][0], beta = gate_s[i][1];
+        const float decay = gate_s[i][0], beta = gate_s[i][1];
         float kk[4], qq[4];
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            kk[u] = __fmul_rn(bf2f(kc[i][lane * 4 + u]), invk);
-            qq[u] = __fdiv_rn(__fmul_rn(bf2f(qc[i][lane * 4 + u]), invq), kd_sqrt);
+        {
+            const float4 k4 = *reinterpret_cast<const float4 *>(&kk_s[i][lane * 4]), q4 = *reinterpret_cast<const float4 *>(&qq_s[i][lane * 4]);
+            kk[0] = k4.x; kk[1] = k4.y; kk[2] = k4.z; kk[3] = k4.w;
+            qq[0] = q4.x; qq[1] = q4.y; qq[2] = q4.z; qq[3] = q4.w;
         }
         float vin = 0.0f;
         if (lane < R) vin = bf2f(vc[i][row0 + lane]);
@@ -432,8 +456,8 @@ __global__ void __launch_bounds__(512) gdn_layer_kernel(const GdnLayerParams P) 
             __syncthreads();
             if (live) {
                 float inv = 1.0f / sqrtf(total / (float)VD + P.rms_eps);
-                float xw = P.norm_w[i] * rbf(v * inv);
-                float zv = bf2f(P.proj[(size_t)(t0 + t) * P.ld + cd + h * VD + i]);
+                float xw = n_wv * rbf(v * inv);
+                float zv = bf2f(n_z[tb >> 2]);
                 P.out[((size_t)(t0 + t) * P.v_heads + h) * VD + i] = f2bf(xw * (zv * (1.0f / (1.0f + expf_ref(-zv)))));
             }
         }

@@ -29,6 +29,13 @@ __device__ __forceinline__ uint4 ld_stream(const void *p) {
     asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
     return v;
 }
+// Activations are produced by the predecessor kernel, and this kernel starts before that one ends (programmatic dependent
+// launch): they must never go through the non-coherent path.  Coherent load, cached in L1 (re-read by the CTA's 8/KW tiles).
+__device__ __forceinline__ uint4 ld_act(const void *p) {
+    uint4 v;
+    asm volatile("ld.global.ca.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+    return v;
+}
 __device__ __forceinline__ void mma_bf16(float c[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
                  : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
@@ -48,7 +55,7 @@ struct WgemmParams {
 
 // One CTA = 8 warps = 8/KW row tiles of 16 weight rows; the KW warps of a tile split the CTA's k slice contiguously.
 template <int MT, int KW, int UNR>
-__global__ void __launch_bounds__(256) wgemm_kernel(const WgemmParams P) {
+__global__ void __launch_bounds__(256, (MT == 1 && UNR <= 4) ? 3 : (MT <= 2 ? 2 : 1)) wgemm_kernel(const WgemmParams P) {
     pdl_trigger();
     constexpr int WARPS = 8, TPC = WARPS / KW;  // tiles per CTA
     __shared__ float red[WARPS][MT][32][4];
@@ -82,16 +89,14 @@ __global__ void __launch_bounds__(256) wgemm_kernel(const WgemmParams P) {
 #pragma unroll
     for (int mt = 0; mt < MT; mt++) acc[mt][0] = acc[mt][1] = acc[mt][2] = acc[mt][3] = 0.0f;
 
-    uint4 wa[UNR], wb[UNR];
-    auto issue = [&](uint32_t b) {
+    // Rolling register window, UNR k-blocks deep: slot u holds block b+u; as soon as a slot's MMAs are issued its
+    // registers are refilled with block b+u+UNR, so 2*UNR weight loads stay in flight per lane with UNR*8 registers.
+    uint4 wa[UNR], wb[UNR], xa[UNR][MT];
 #pragma unroll
-        for (int u = 0; u < UNR; u++) {
-            uint32_t bb = min(b + u, b_hi - 1);  // tail blocks are re-read and masked below
-            wa[u] = ld_stream(w0 + (size_t)bb * 32);
-            wb[u] = ld_stream(w1 + (size_t)bb * 32);
-        }
-    };
-    if (b_lo < b_hi) issue(b_lo);
+    for (int u = 0; u < UNR; u++) {
+        wa[u] = wb[u] = make_uint4(0, 0, 0, 0);
+        if (b_lo + u < b_hi) { wa[u] = ld_stream(w0 + (size_t)(b_lo + u) * 32); wb[u] = ld_stream(w1 + (size_t)(b_lo + u) * 32); }
+    }
     // Weights are never written by the stream: pull this warp's slab towards L2 while the predecessor kernel is still
     // running (one 128-byte line per lane and step: lane -> row lane/2 of the tile, line lane%2 + 2*step)
     {
@@ -102,31 +107,32 @@ __global__ void __launch_bounds__(256) wgemm_kernel(const WgemmParams P) {
         const char *base = reinterpret_cast<const char *>(P.W + (size_t)rr * P.k + (size_t)b_lo * 32);
         const uint32_t bytes = (b_hi - b_lo) * 64;
         if (tile_ok)
-            for (uint32_t off = (lane & 1) * 128 + 8 * 64; off < bytes; off += 256)
+            for (uint32_t off = (lane & 1) * 128 + UNR * 64; off < bytes; off += 256)
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
     }
     pdl_wait();
+#pragma unroll
+    for (int u = 0; u < UNR; u++)
+#pragma unroll
+        for (int mt = 0; mt < MT; mt++)
+            xa[u][mt] = (av[mt] && b_lo + u < b_hi) ? ld_act(ap[mt] + (size_t)(b_lo + u) * 32) : make_uint4(0, 0, 0, 0);
     for (uint32_t b = b_lo; b < b_hi; b += UNR) {
-        uint4 ca[UNR], cb[UNR];
-#pragma unroll
-        for (int u = 0; u < UNR; u++) { ca[u] = wa[u]; cb[u] = wb[u]; }
-        uint4 xa[UNR][MT];
-#pragma unroll
-        for (int u = 0; u < UNR; u++) {
-            uint32_t bb = min(b + u, b_hi - 1);
-#pragma unroll
-            for (int mt = 0; mt < MT; mt++)
-                xa[u][mt] = av[mt] ? __ldg(reinterpret_cast<const uint4 *>(ap[mt] + (size_t)bb * 32)) : make_uint4(0, 0, 0, 0);
-        }
-        if (b + UNR < b_hi) issue(b + UNR);
 #pragma unroll
         for (int u = 0; u < UNR; u++) {
             if (b + u < b_hi) {
 #pragma unroll
                 for (int mt = 0; mt < MT; mt++) {
-                    mma_bf16(acc[mt], ca[u].x, cb[u].x, ca[u].y, cb[u].y, xa[u][mt].x, xa[u][mt].y);
-                    mma_bf16(acc[mt], ca[u].z, cb[u].z, ca[u].w, cb[u].w, xa[u][mt].z, xa[u][mt].w);
+                    mma_bf16(acc[mt], wa[u].x, wb[u].x, wa[u].y, wb[u].y, xa[u][mt].x, xa[u][mt].y);
+                    mma_bf16(acc[mt], wa[u].z, wb[u].z, wa[u].w, wb[u].w, xa[u][mt].z, xa[u][mt].w);
                 }
+            }
+            const uint32_t nb2 = b + u + UNR;
+            if (nb2 < b_hi) {
+                wa[u] = ld_stream(w0 + (size_t)nb2 * 32);
+                wb[u] = ld_stream(w1 + (size_t)nb2 * 32);
+#pragma unroll
+                for (int mt = 0; mt < MT; mt++)
+                    if (av[mt]) xa[u][mt] = ld_act(ap[mt] + (size_t)nb2 * 32);
             }
         }
     }
@@ -203,11 +209,11 @@ static uint32_t g_force_kw = 0, g_force_ks = 0, g_force_unr = 0;
 extern "C" void wein_b200_gemm_tune(uint32_t kw, uint32_t ksplit, uint32_t unr) { g_force_kw = kw; g_force_ks = ksplit; g_force_unr = unr; }
 
 static WgemmPlan plan_for(uint32_t n_tiles, uint32_t k, bool has_scratch) {
-    // Measured on B200 (graph replay, weights rotated through 3 GB): the fewest warps per tile that still give every
-    // SM a CTA win for the layer projections (kw 2 at 640-1152 tiles: 3.9-5.6 TB/s; kw 8 at 160 tiles: 3.0-3.9 TB/s);
-    // the vocabulary projection (9496 tiles) prefers kw 4 (6.2 TB/s).  Splitting k over CTAs never won: off by default.
+    // Measured on B200 (graph replay, weights rotated through 3 GB, m = 4): the fewest warps per tile that still give
+    // about two CTAs per SM win (tiles 1152 -> kw 2: 5.4 TB/s; 640-772 -> kw 4: 5.3 TB/s; 160 -> kw 8: 4.2-4.3 TB/s); the
+    // vocabulary projection (9496 tiles) prefers kw 4 (6.2 TB/s).  Splitting k over CTAs never won: off by default.
     uint32_t kb = k / 32, kw = 1, ks = 1;
-    while (kw < 8 && (n_tiles * kw + 7) / 8 < 148 && kb / (kw * 2) >= 4) kw *= 2;
+    while (kw < 8 && (n_tiles * kw + 7) / 8 < 280 && kb / (kw * 2) >= 4) kw *= 2;
     if (n_tiles >= 4096 && kb >= 32) kw = 4;
     if (g_force_kw) kw = g_force_kw;
     if (g_force_ks) ks = has_scratch ? g_force_ks : 1;
@@ -220,10 +226,14 @@ extern "C" uint64_t wein_b200_gemm_scratch_bytes(uint32_t n_max) {
     return 8ull * 592 * (8 * 4 * 128) * 4 + 4096 * 4;
 }
 
+extern bool g_wb_pdl_gemm;
+struct PdlScope { bool saved; PdlScope() : saved(g_wb_pdl) { g_wb_pdl = g_wb_pdl && g_wb_pdl_gemm; } ~PdlScope() { g_wb_pdl = saved; } };
 template <int MT, int KW>
 static void wgemm_go(const WgemmParams &p, dim3 grid, uint32_t unr, cudaStream_t st) {
+    PdlScope scope;
     if constexpr (MT == 1) {
         if (unr == 8) { WB_LAUNCH((wgemm_kernel<MT, KW, 8>), grid, 256, 0, st, p); return; }
+        if (unr == 6) { WB_LAUNCH((wgemm_kernel<MT, KW, 6>), grid, 256, 0, st, p); return; }
     }
     WB_LAUNCH((wgemm_kernel<MT, KW, 4>), grid, 256, 0, st, p);
 }
@@ -268,7 +278,7 @@ static int32_t wgemm_launch(const void *a, const void *w, void *c, uint32_t m, u
     p.counters = (uint32_t *)scratch;
     p.partial = scratch ? (float *)((char *)scratch + 4096 * 4) : nullptr;
     dim3 grid(ctas, pl.ksplit);
-    uint32_t unr = g_force_unr ? g_force_unr : 4;
+    uint32_t unr = g_force_unr ? g_force_unr : (ctas * pl.ksplit <= 296 ? 8 : 4);
     switch (mt) {
         case 1: wgemm_go_kw<1>(p, grid, pl.kw, unr, st); break;
         case 2: wgemm_go_kw<2>(p, grid, pl.kw, unr, st); break;

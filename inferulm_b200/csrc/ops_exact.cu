@@ -9,7 +9,7 @@
 
 // ------------------------------------------------------------------ embed
 // out[t, :] = w[ids[t], :]  (reference.rs:298-305).  One block per row.
-__global__ void embed_kernel(const uint32_t *__restrict__ ids, const bf16_t *__restrict__ w, bf16_t *__restrict__ out,
+__global__ void embed_kernel(const uint32_t *ids, const bf16_t *w, bf16_t *out,
                              uint32_t hidden) {
     PDL_ENTRY();
     size_t src = (size_t)ids[blockIdx.x] * hidden, dst = (size_t)blockIdx.x * hidden;
@@ -28,7 +28,7 @@ __global__ void embed_kernel(const uint32_t *__restrict__ ids, const bf16_t *__r
 // MODE 0: out = x*inv*(1+w)                      rms_norm_zc   (reference.rs:418-430)
 // MODE 1: s = bf16(a+b) -> sum_out; norm of s    add_norm_zc   (kernels/src/lib.rs:4674-4755)
 template <int MODE>
-__global__ void rms_norm_zc_kernel(const bf16_t *a, const bf16_t *b, const bf16_t *__restrict__ w, bf16_t *sum_out,
+__global__ void rms_norm_zc_kernel(const bf16_t *a, const bf16_t *b, const bf16_t *w, bf16_t *sum_out,
                                    bf16_t *norm_out, uint32_t hidden, float eps) {
     PDL_ENTRY();
     constexpr int CACHE = 12;  // elements per thread kept in registers between the two passes (hidden <= 3072 at 256 threads)
@@ -79,8 +79,8 @@ __global__ void rms_norm_zc_kernel(const bf16_t *a, const bf16_t *b, const bf16_
 
 // rms_norm_gated (reference.rs:699-713): xb = bf16(x*inv); xw = w*xb (kept
 // f32); out = bf16(xw * (z*sigmoid(z))).
-__global__ void rms_norm_gated_kernel(const bf16_t *__restrict__ x, const bf16_t *__restrict__ z,
-                                      const float *__restrict__ w, bf16_t *__restrict__ out, uint32_t hidden, float eps) {
+__global__ void rms_norm_gated_kernel(const bf16_t *x, const bf16_t *z,
+                                      const float *w, bf16_t *out, uint32_t hidden, float eps) {
     PDL_ENTRY();
     __shared__ float red[33];
     size_t base = (size_t)blockIdx.x * hidden;
@@ -102,8 +102,8 @@ __global__ void rms_norm_gated_kernel(const bf16_t *__restrict__ x, const bf16_t
 // ------------------------------------------------------------------- rope
 // Partial rotary, rotate-half (reference.rs:436-460).  One thread per
 // (token, head, pair); in place allowed.
-__global__ void rope_pt_kernel(const bf16_t *x, const float *__restrict__ cosv, const float *__restrict__ sinv,
-                               const uint32_t *__restrict__ pos, bf16_t *out, uint32_t rot_dim, uint32_t head_dim,
+__global__ void rope_pt_kernel(const bf16_t *x, const float *cosv, const float *sinv,
+                               const uint32_t *pos, bf16_t *out, uint32_t rot_dim, uint32_t head_dim,
                                uint32_t heads, uint32_t tokens) {
     PDL_ENTRY();
     uint32_t half = rot_dim / 2;
@@ -134,7 +134,7 @@ __global__ void rope_tail_copy_kernel(const bf16_t *x, bf16_t *out, uint32_t rot
 // OP 0 add (reference.rs:308-313)   1 mul (:316-321)   2 silu (:141-148)
 // OP 3 silu_mul (kernels/src/lib.rs:576-584)   4 sigmul (reference.rs:463-472)
 template <int OP>
-__global__ void eltwise_kernel(const bf16_t *__restrict__ a, const bf16_t *__restrict__ b, bf16_t *__restrict__ out, size_t n) {
+__global__ void eltwise_kernel(const bf16_t *a, const bf16_t *b, bf16_t *out, size_t n) {
     PDL_ENTRY();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
@@ -153,9 +153,9 @@ __global__ void eltwise_kernel(const bf16_t *__restrict__ a, const bf16_t *__res
 // slot = block_table[seq*bpr + pos/bs]*bs + pos%bs (reference.rs:192-215).
 // DST_F32 widens exactly (kernels/src/lib.rs:620).
 template <bool DST_F32>
-__global__ void kv_scatter_kernel(const bf16_t *__restrict__ src_k, const bf16_t *__restrict__ src_v,
-                                  const uint32_t *__restrict__ block_table, const uint32_t *__restrict__ seq_ids,
-                                  const uint32_t *__restrict__ positions, void *k_dst, void *v_dst, uint32_t bpr,
+__global__ void kv_scatter_kernel(const bf16_t *src_k, const bf16_t *src_v,
+                                  const uint32_t *block_table, const uint32_t *seq_ids,
+                                  const uint32_t *positions, void *k_dst, void *v_dst, uint32_t bpr,
                                   uint32_t block_size, uint32_t head_elems, uint32_t tokens) {
     PDL_ENTRY();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -175,9 +175,9 @@ __global__ void kv_scatter_kernel(const bf16_t *__restrict__ src_k, const bf16_t
 // -------------------------------------------------------------------- conv
 // Causal depthwise conv (taps k ascending, acc = v*w + acc as two roundings),
 // rounded to bf16, then SiLU rounded again (reference.rs:476-506).
-__global__ void conv1d_dw_kernel(const bf16_t *__restrict__ x, const bf16_t *__restrict__ w,
-                                 const bf16_t *__restrict__ state_in, const uint32_t *__restrict__ tok_row,
-                                 const uint32_t *__restrict__ tok_pos, bf16_t *__restrict__ out, uint32_t conv_dim,
+__global__ void conv1d_dw_kernel(const bf16_t *x, const bf16_t *w,
+                                 const bf16_t *state_in, const uint32_t *tok_row,
+                                 const uint32_t *tok_pos, bf16_t *out, uint32_t conv_dim,
                                  uint32_t kernel, uint32_t tokens) {
     PDL_ENTRY();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -199,9 +199,9 @@ __global__ void conv1d_dw_kernel(const bf16_t *__restrict__ x, const bf16_t *__r
 // Conv-state rows (reference.rs:511-562).  One thread per (span, channel).
 // spec == 1: the window after token t goes to row row_id+t+1 (row j = state
 // after the first j tokens); spec == 0: the span's own row is rolled in place.
-__global__ void conv_state_roll_kernel(const bf16_t *__restrict__ x, bf16_t *state, const uint32_t *__restrict__ row_start,
-                                       const uint32_t *__restrict__ row_count, const uint32_t *__restrict__ row_id,
-                                       const uint32_t *__restrict__ specs, uint32_t conv_dim, uint32_t kernel, uint32_t n_rows) {
+__global__ void conv_state_roll_kernel(const bf16_t *x, bf16_t *state, const uint32_t *row_start,
+                                       const uint32_t *row_count, const uint32_t *row_id,
+                                       const uint32_t *specs, uint32_t conv_dim, uint32_t kernel, uint32_t n_rows) {
     PDL_ENTRY();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)n_rows * conv_dim) return;
@@ -231,10 +231,10 @@ __global__ void conv_state_roll_kernel(const bf16_t *__restrict__ x, bf16_t *sta
 // conv+SiLU outputs and the per-position conv-state rows.  The window after
 // token t is written to row out_base[r]+t; the span reads row in_row[r].
 // Values are bit-identical to conv1d_dw followed by conv_state_roll.
-__global__ void conv_verify_kernel(const bf16_t *__restrict__ x, uint32_t x_stride, const bf16_t *__restrict__ w,
-                                   bf16_t *state, const uint32_t *__restrict__ row_start,
-                                   const uint32_t *__restrict__ row_count, const uint32_t *__restrict__ in_row,
-                                   const uint32_t *__restrict__ out_base, bf16_t *__restrict__ out, uint32_t conv_dim,
+__global__ void conv_verify_kernel(const bf16_t *x, uint32_t x_stride, const bf16_t *w,
+                                   bf16_t *state, const uint32_t *row_start,
+                                   const uint32_t *row_count, const uint32_t *in_row,
+                                   const uint32_t *out_base, bf16_t *out, uint32_t conv_dim,
                                    uint32_t n_rows) {
     PDL_ENTRY();
     size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -281,7 +281,7 @@ __device__ __forceinline__ uint64_t warp_max_u64(uint64_t k) {
     return k;
 }
 // phase 1: grid (split, s); each block scans one slice of one row
-__global__ void argmax_p1_kernel(const bf16_t *__restrict__ x, const uint32_t *__restrict__ rows, uint64_t *__restrict__ part,
+__global__ void argmax_p1_kernel(const bf16_t *x, const uint32_t *rows, uint64_t *part,
                                  uint32_t n, uint32_t split) {
     PDL_ENTRY();
     __shared__ uint64_t sm[32];
@@ -319,7 +319,7 @@ __global__ void argmax_p1_kernel(const bf16_t *__restrict__ x, const uint32_t *_
     }
 }
 // phase 2: one warp per row merges the slices
-__global__ void argmax_p2_kernel(const uint64_t *__restrict__ part, uint32_t *__restrict__ out, uint32_t split) {
+__global__ void argmax_p2_kernel(const uint64_t *part, uint32_t *out, uint32_t split) {
     PDL_ENTRY();
     uint32_t r = blockIdx.x;
     uint64_t k = 0ull;

@@ -37,8 +37,8 @@ def load():
             _lib.wein_b200_gemm_prefetch_cap(C.c_uint64(int(os.environ["WEIN_B200_PREFETCH_MB"]) << 20))
         if os.environ.get("WEIN_B200_ABLATE"):  # profiling only: see wein_b200_engine_ablate
             _lib.wein_b200_engine_ablate(C.c_uint32(int(os.environ["WEIN_B200_ABLATE"])))
-        if os.environ.get("WEIN_B200_PDL", "1") == "0":  # A/B switch: launch every kernel fully serialised
-            _lib.wein_b200_set_pdl(C.c_uint32(0))
+        if os.environ.get("WEIN_B200_PDL", "1") != "1":  # A/B switch: 0 = every kernel fully serialised, 3 = all but the GEMMs overlap
+            _lib.wein_b200_set_pdl(C.c_uint32(int(os.environ["WEIN_B200_PDL"])))
     return _lib
 
 
