@@ -36,21 +36,30 @@ __global__ void rms_norm_zc_kernel(const bf16_t *a, const bf16_t *b, const bf16_
     size_t base = (size_t)blockIdx.x * hidden;
     float vals[CACHE], wv[CACHE];
     float acc = 0.0f;
+    // all loads first (independent, one round trip), then the arithmetic in element order
+    bf16_t av[CACHE], bv[CACHE];
 #pragma unroll
     for (int it = 0; it < CACHE; it++) {
         uint32_t i = threadIdx.x + it * blockDim.x;
-        vals[it] = 0.0f; wv[it] = 0.0f;
+        bool ok = i < hidden;
+        av[it] = ok ? a[base + i] : (bf16_t)0;
+        bv[it] = (ok && MODE == 1) ? b[base + i] : (bf16_t)0;
+        wv[it] = ok ? bf2f(w[i]) : 0.0f;
+    }
+#pragma unroll
+    for (int it = 0; it < CACHE; it++) {
+        uint32_t i = threadIdx.x + it * blockDim.x;
+        vals[it] = 0.0f;
         if (i < hidden) {
             float v;
             if (MODE == 1) {
-                bf16_t s = f2bf(bf2f(a[base + i]) + bf2f(b[base + i]));
+                bf16_t s = f2bf(bf2f(av[it]) + bf2f(bv[it]));
                 sum_out[base + i] = s;
                 v = bf2f(s);
             } else {
-                v = bf2f(a[base + i]);
+                v = bf2f(av[it]);
             }
             vals[it] = v;
-            wv[it] = bf2f(w[i]);
             acc = fmaf(v, v, acc);
         }
     }
