@@ -103,6 +103,13 @@ struct SlotState {
     bf16_t *hid;
 };
 
+// Block-wide copy of one hidden row, 16 bytes per thread and step (rows are 16-byte aligned: hidden is a multiple of 32)
+__device__ __forceinline__ void copy_row(bf16_t *dst, const bf16_t *src, uint32_t H) {
+    const uint4 *s = reinterpret_cast<const uint4 *>(src);
+    uint4 *d = reinterpret_cast<uint4 *>(dst);
+    for (uint32_t i = threadIdx.x; i < H / 8; i += blockDim.x) d[i] = s[i];
+}
+
 // Rows of a speculative round: batch row b = slot slots[b]; chain row j feeds the pending token (j = 0) or draft j-1.
 __global__ void verify_prep_kernel(const uint32_t *slots, SlotState S, const uint32_t *drafts, uint32_t k_max,
                                    uint32_t n, uint32_t P, uint32_t rows_per_slot, uint32_t bankrows, uint32_t *tok, uint32_t *pos_rows,
@@ -132,9 +139,7 @@ __global__ void commit_kernel(const uint32_t *slots, SlotState S, const uint32_t
                               uint32_t P, uint32_t k, uint32_t H) {
     PDL_ENTRY();
     uint32_t b = blockIdx.x, slot = slots[b], a = accept_len[b];
-    const bf16_t *src = x + (size_t)(b * P + a) * H;
-    bf16_t *dst = S.hid + (size_t)slot * H;
-    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+    copy_row(S.hid + (size_t)slot * H, x + (size_t)(b * P + a) * H, H);
     if (threadIdx.x == 0) {
         uint32_t oc = S.out_count[slot];
         for (uint32_t j = 0; j <= a; j++) S.ring[(size_t)slot * RING_CAP + ((oc + j) % RING_CAP)] = out_tokens[b * P + j];
@@ -176,9 +181,7 @@ __global__ void prefill_commit_kernel(const uint32_t *slots, SlotState S, const 
     PDL_ENTRY();
     uint32_t b = blockIdx.x, slot = slots[b], c = cnt[b];
     if (c == 0) return;
-    const bf16_t *src = x + (size_t)(row_start[b] + c - 1) * H;
-    bf16_t *dst = S.hid + (size_t)slot * H;
-    for (uint32_t i = threadIdx.x; i < H; i += blockDim.x) dst[i] = src[i];
+    copy_row(S.hid + (size_t)slot * H, x + (size_t)(row_start[b] + c - 1) * H, H);
     if (threadIdx.x == 0) {
         S.pos[slot] += c;
         S.state_row[slot] = out_base[b] + c - 1;

@@ -33,23 +33,31 @@ __global__ void qk_prep_kernel(const bf16_t *qgkv, uint32_t ld, const bf16_t *qn
     }
     const bf16_t *src;
     const bf16_t *w;
-    if (is_q) { src = row + (size_t)unit * 2 * hd; w = qn; gate[((size_t)t * q_heads + unit) * hd + i] = src[hd + i]; }
+    if (is_q) { src = row + (size_t)unit * 2 * hd; w = qn; }
     else { src = row + 2 * q_heads * hd + (unit - q_heads) * hd; w = kn; }
+    // every global operand is fetched before the first store (one round trip): element, norm weight, gate, rotary factors
+    const uint32_t half = rot_dim / 2;
+    const float v = bf2f(src[i]), wn = bf2f(w[i]);
+    const bf16_t gv = is_q ? src[hd + i] : (bf16_t)0;
+    float rc = 0.0f, rs = 0.0f;
+    if (i < rot_dim) {
+        uint32_t p = i < half ? i : i - half;
+        size_t ci = (size_t)rope_pos[t] * half + p;
+        rc = cosv[ci]; rs = sinv[ci];
+    }
+    if (is_q) gate[((size_t)t * q_heads + unit) * hd + i] = gv;
     // zero-centred RMSNorm over the head (reference.rs:418-430; one element per thread, block tree)
-    float v = bf2f(src[i]);
     float total = block_sum_tree(fmaf(v, v, 0.0f), red);
     float inv = 1.0f / sqrtf(total / (float)hd + eps);
-    bf16_t nb = f2bf(v * inv * (1.0f + bf2f(w[i])));
+    bf16_t nb = f2bf(v * inv * (1.0f + wn));
     nrm[i] = nb;
     __syncthreads();
     // partial RoPE on the first rot_dim dims (reference.rs:436-460), from the rounded norm output
-    const uint32_t half = rot_dim / 2;
     bf16_t o = nb;
     if (i < rot_dim) {
         uint32_t p = i < half ? i : i - half;
-        float c = cosv[(size_t)rope_pos[t] * half + p], s = sinv[(size_t)rope_pos[t] * half + p];
         float x1 = bf2f(nrm[p]), x2 = bf2f(nrm[p + half]);
-        o = i < half ? f2bf(x1 * c - x2 * s) : f2bf(x2 * c + x1 * s);
+        o = i < half ? f2bf(x1 * rc - x2 * rs) : f2bf(x2 * rc + x1 * rs);
     }
     if (is_q) qh[((size_t)t * q_heads + unit) * hd + i] = o;
     else k_pool[slot * he + (unit - q_heads) * hd + i] = o;
@@ -82,11 +90,27 @@ __global__ void mtp_cat_kernel(const uint32_t *tok, uint32_t tok_stride, const b
                                   : hid + (size_t)(hid_rows ? hid_rows[r] : r) * hidden;
     const bf16_t *w = half == 0 ? pre_e : pre_h;
     bf16_t *dst = cat + (size_t)r * 2 * hidden + (size_t)half * hidden;
-    float acc = 0.0f;
-    for (uint32_t i = threadIdx.x; i < hidden; i += blockDim.x) { float v = bf2f(src[i]); acc = fmaf(v, v, acc); }
+    // elements and weights of this thread first (independent loads), the rest of a wider row in a plain loop
+    constexpr int CACHE = 12;
+    float vals[CACHE], wv[CACHE], acc = 0.0f;
+#pragma unroll
+    for (int it = 0; it < CACHE; it++) {
+        uint32_t i = threadIdx.x + it * blockDim.x;
+        vals[it] = i < hidden ? bf2f(src[i]) : 0.0f;
+        wv[it] = i < hidden ? bf2f(w[i]) : 0.0f;
+    }
+#pragma unroll
+    for (int it = 0; it < CACHE; it++)
+        if (threadIdx.x + it * blockDim.x < hidden) acc = fmaf(vals[it], vals[it], acc);
+    for (uint32_t i = threadIdx.x + CACHE * blockDim.x; i < hidden; i += blockDim.x) { float v = bf2f(src[i]); acc = fmaf(v, v, acc); }
     float total = block_sum_tree(acc, red);
     float inv = 1.0f / sqrtf(total / (float)hidden + eps);
-    for (uint32_t i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = f2bf(bf2f(src[i]) * inv * (1.0f + bf2f(w[i])));
+#pragma unroll
+    for (int it = 0; it < CACHE; it++) {
+        uint32_t i = threadIdx.x + it * blockDim.x;
+        if (i < hidden) dst[i] = f2bf(vals[it] * inv * (1.0f + wv[it]));
+    }
+    for (uint32_t i = threadIdx.x + CACHE * blockDim.x; i < hidden; i += blockDim.x) dst[i] = f2bf(bf2f(src[i]) * inv * (1.0f + bf2f(w[i])));
 }
 int32_t wb_mtp_cat(const uint32_t *tok, uint32_t tok_stride, const void *embed, const void *hid, const uint32_t *hid_rows,
                    const void *pre_e, const void *pre_h, void *cat, uint32_t rows, uint32_t hidden, float eps, cudaStream_t st) {
