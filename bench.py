@@ -244,21 +244,40 @@ def run_ours(args, wl):
     P = k + 1
     M = B * P
     a_in = torch.randn(M, shape.hidden, device="cuda").to(torch.bfloat16)
-    c_out = torch.empty(M, 2 * shape.inter, dtype=torch.bfloat16, device="cuda")
+    fused = M <= 32   # the engine's launch for this projection: skinny GEMM with the SwiGLU epilogue, else cuBLASLt
+    c_out = torch.empty(M, shape.inter if fused else 2 * shape.inter, dtype=torch.bfloat16, device="cuda")
     scratch = torch.zeros(ops.gemm_scratch_bytes(2 * shape.inter) // 4, dtype=torch.int32, device="cuda")
     gus = [d["gu"] for d in weights.layers]
-    for g in gus[:3]:
-        ops.gemm_wt(a_in, g, c_out, M, 2 * shape.inter, shape.hidden, scratch)
+
+    def one(g):
+        if fused:
+            ops.gemm_swiglu(a_in, g, c_out, M, shape.inter, shape.hidden, scratch)
+        else:
+            ops.gemm_wt(a_in, g, c_out, M, 2 * shape.inter, shape.hidden, scratch)
+
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        for g in gus[:3]:
+            one(g)
     torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for g in gus:
-        ops.gemm_wt(a_in, g, c_out, M, 2 * shape.inter, shape.hidden, scratch)
-    e1.record()
+    graph = torch.cuda.CUDAGraph()   # replayed as a graph so the host's launch rate does not enter the kernel time
+    with torch.cuda.graph(graph, stream=side):
+        for g in gus:
+            one(g)
+    graph.replay()
     torch.cuda.synchronize()
-    gemm_ms = e0.elapsed_time(e1) / len(gus)
-    gemm_bytes = 2 * shape.inter * shape.hidden * 2 + M * shape.hidden * 2 + M * 2 * shape.inter * 2
+    gemm_ms = 1e9
+    for _ in range(3):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        graph.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        gemm_ms = min(gemm_ms, e0.elapsed_time(e1) / len(gus))
+    gemm_bytes = 2 * shape.inter * shape.hidden * 2 + M * shape.hidden * 2 + M * (shape.inter if fused else 2 * shape.inter) * 2
     achieved = gemm_bytes / (gemm_ms * 1e-3) / 1e9
+    kernel_name = (f"wgemm_kernel (gate|up + SwiGLU) m={M} n={2 * shape.inter} k={shape.hidden}" if fused
+                   else f"cuBLASLt gate|up m={M} n={2 * shape.inter} k={shape.hidden}")
 
     # ---- algorithmic bytes of one round: verify step (weights + state + conv + KV + logits) + k draft forwards
     n_full = sum(shape.is_full(l) for l in range(shape.n_layers))
@@ -292,7 +311,7 @@ def run_ours(args, wl):
                              d2h_bytes_per_step=B * (4 + 4 + 24 + 4 * (k + 1)), ms_per_step=ms_e2e_max / args.steps),
                     gpu_launches=launches,
                     roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak, traffic=None,
-                                  kernel=f"wgemm_kernel gate|up m={M} n={2 * shape.inter} k={shape.hidden}", peak_kind=peak_kind,
+                                  kernel=kernel_name, peak_kind=peak_kind,
                                   us_per_launch=gemm_ms * 1e3),
                     step_roofline=dict(verify_bytes=verify_bytes, round_bytes=round_bytes, round_us=step_s * 1e6,
                                        achieved_gbs=round_bytes / step_s / 1e9, frac_of_measured_peak=round_bytes / step_s / 1e9 / peak,
