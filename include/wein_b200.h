@@ -139,6 +139,13 @@ int32_t wein_b200_gemm_swiglu(const void *a, const void *w_gate_up, void *out, u
  * a row with no comparable element yields 0xFFFFFFFF, as the reference. */
 int32_t wein_b200_argmax_rows(const void *x, const void *rows, void *scratch, void *out, uint32_t n, uint32_t s, void *stream);
 
+/* No counterpart in the reference.  wein_b200_argmax_rows for callers that cannot allocate device memory (a plugin that only
+ * receives one call's tensors; code inside a graph-capture region or under a memory pool it does not own): the slice maxima
+ * live in a 64 KiB array built into the library (held by every GPU that loads it) instead of a caller buffer.  At most 256
+ * rows per call (WEIN_B200_ERR_CAPACITY beyond).  The first call on each device looks the array's address up on the host:
+ * make it outside any stream capture.  All calls on a device share the array: calls that may overlap on the GPU race. */
+int32_t wein_b200_argmax_rows_noalloc(const void *x, const void *rows, void *out, uint32_t n, uint32_t s, void *stream);
+
 /* ------------------------------------------------------------------------------------------------------
  * Acceptance (stands in for Qwen35Executor::spec_finish, crates/wein-exec/src/qwen.rs:2419-2502, which runs on the
  * host after a sync and a readback in the reference).

@@ -519,4 +519,52 @@ int32_t wein_b200_argmax_rows(const void *x, const void *rows, void *scratch, vo
     return WB_OK;
 }
 
+// ---------------------------------------------------------------------------------------------------------------------
+// Row argmax for callers that cannot allocate device memory.
+//
+// Some hosts of this library have no way to hand over a scratch buffer: a plugin that is only given the tensors of one call,
+// or code that runs where cudaMalloc is forbidden (inside a region being recorded into a CUDA graph, or under a memory pool the
+// embedding process owns and does not expose).  For them the per-row slice maxima of the two-phase argmax live in a fixed array
+// inside the library image instead of a caller buffer.  The array costs WEIN_B200_ARGMAX_NOALLOC_MAX_ROWS * 32 * 8 bytes = 64 KiB
+// on every GPU that loads the library, for the life of the process.
+//
+// In host code `g_argmax_static` is only a handle for the symbol, not a device address, so its address is looked up once
+// per device with cudaGetSymbolAddress (with that device current) and the looked-up pointer is what the kernels receive.
+#define WEIN_B200_ARGMAX_NOALLOC_MAX_ROWS 256
+static __device__ __align__(256) unsigned long long g_argmax_static[WEIN_B200_ARGMAX_NOALLOC_MAX_ROWS * 32];
+
+// Same result as wein_b200_argmax_rows, without a scratch argument and without any allocation.
+//  - at most WEIN_B200_ARGMAX_NOALLOC_MAX_ROWS (256) rows per call; more is rejected with WEIN_B200_ERR_CAPACITY;
+//  - the first call on each device resolves the address of the built-in array (a host-side lookup, no allocation): make
+//    that first call outside any stream capture;
+//  - every call on a device uses the same array.  Nothing in it needs clearing (each call overwrites all the words it reads
+//    back), but two calls whose kernels may run at the same time -- different streams, or different host threads -- would
+//    overwrite each other's slice maxima: serialise them on one stream.
+int32_t wein_b200_argmax_rows_noalloc(const void *x, const void *rows, void *out, uint32_t n, uint32_t s, void *stream) {
+    WB_CHECK_ARG(x && rows && out, "argmax_rows_noalloc: null pointer");
+    if (s > WEIN_B200_ARGMAX_NOALLOC_MAX_ROWS) {
+        wb_set_error("argmax_rows_noalloc: %u rows exceed the built-in scratch of %d rows; use wein_b200_argmax_rows with a caller buffer",
+                     s, WEIN_B200_ARGMAX_NOALLOC_MAX_ROWS);
+        return WB_ERR_CAPACITY;
+    }
+    if (s == 0) return WB_OK;
+    static void *scratch_of_device[64] = {nullptr};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { wb_set_error("argmax_rows_noalloc: no current CUDA device"); return WB_ERR_CUDA; }
+    if (!scratch_of_device[dev]) {
+        void *p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_argmax_static);
+        if (e != cudaSuccess || !p) { wb_set_error("argmax_rows_noalloc: cudaGetSymbolAddress failed: %s", cudaGetErrorString(e)); return WB_ERR_CUDA; }
+        scratch_of_device[dev] = p;
+    }
+    uint64_t *scratch = (uint64_t *)scratch_of_device[dev];
+    const uint32_t split = 32;
+    dim3 grid(split, s);
+    WB_LAUNCH((argmax_p1_kernel), grid, 256, 0, STREAM(stream), (const bf16_t *)x, (const uint32_t *)rows, scratch, n, split);
+    WB_LAUNCH_CHECK();
+    WB_LAUNCH((argmax_p2_kernel), s, 32, 0, STREAM(stream), (const uint64_t *)scratch, (uint32_t *)out, split);
+    WB_LAUNCH_CHECK();
+    return WB_OK;
+}
+
 }  // extern "C"

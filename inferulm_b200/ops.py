@@ -191,3 +191,11 @@ def gdn_layer(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state
     check(load().wein_b200_gdn_layer(_ptr(proj), U32(ld), _ptr(conv_w), _ptr(conv_state), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w),
                                      _ptr(state), U32(state_f32), _ptr(out), _ptr(row_start), _ptr(row_count), _ptr(in_row),
                                      _ptr(out_base), U32(n_rows), U32(k_heads), U32(v_heads), F32(l2_eps), F32(rms_eps), _stream()))
+
+
+ARGMAX_NOALLOC_MAX_ROWS = 256
+
+
+def argmax_rows_noalloc(x, rows, out, n, s):
+    """argmax_rows without a scratch argument: for callers that cannot allocate (at most ARGMAX_NOALLOC_MAX_ROWS rows)."""
+    check(load().wein_b200_argmax_rows_noalloc(_ptr(x), _ptr(rows), _ptr(out), U32(n), U32(s), _stream()))
