@@ -28,6 +28,8 @@ WORKLOADS = {
     # name: batch, k, prompt, temp, top_k, top_p
     "c2": dict(batch=1, k=3, prompt=1024, temp=0.0, top_k=0, top_p=1.0,
                desc="Qwen3.5-4B-shape hybrid decoder (24 GDN + 8 GQA, hidden 2560, FFN 9216, vocab 151936), greedy MTP k=3, batch 1, 1024-token prompt"),
+    "c4": dict(batch=8, k=4, prompt=32768, temp=0.0, top_k=0, top_p=1.0,
+               desc="same model, long context: batch 8, 32768-token prompts (paged bf16 KV, 16-token pages) + f32 recurrent state, greedy k=4"),
     "c3": dict(batch=32, k=3, prompt=2048, temp=0.7, top_k=50, top_p=0.9,
                desc="same model, batch 32, sampled acceptance T=0.7 top-k 50 top-p 0.9, k=3, 2048-token prompts"),
 }
@@ -158,9 +160,8 @@ def run_ours(args, wl):
     import torch.distributed as dist
     from inferulm_b200.engine import Engine, ModelShape, SyntheticWeights
 
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    rank = int(os.environ.get("RANK", "0"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
+    from inferulm_b200 import dist_util as du
+    rank, world, local = du.rank_world()
     torch.cuda.set_device(local)
     if world > 1:
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -170,8 +171,8 @@ def run_ours(args, wl):
     rounds_total = args.warmup + args.steps
     max_pos = prompt_len + 2 * (rounds_total + 8) * (k + 1) + 64
     eng = Engine(weights, max_seqs=B, k_max=k, max_pos=max_pos, state_f32=True)
-    rs = np.random.default_rng(1000 + rank)
-    prompts = [rs.integers(0, shape.vocab, prompt_len).astype(np.uint32) for _ in range(B)]
+    rs = np.random.default_rng(7000 + rank)
+    prompts = du.rank_prompts(rank, B, prompt_len, shape.vocab)
     slots = list(range(B))
     for s in slots:
         eng.admit(s, max_pos, temp=wl["temp"], top_k=wl["top_k"], top_p=wl["top_p"], seed=rank * 1000 + s, rng=rs)
@@ -218,22 +219,9 @@ def run_ours(args, wl):
     timed(min(args.warmup, 3), "e2e")
     ms_e2e, toks_e2e = timed(args.steps, "e2e")
 
-    def allmax(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def allsum(x):
-        if world == 1:
-            return x
-        t = torch.tensor([x], dtype=torch.float64, device="cuda")
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        return float(t.item())
-
-    ms_max, toks_all = allmax(ms), allsum(toks)
-    ms_e2e_max, toks_e2e_all = allmax(ms_e2e), allsum(toks_e2e)
+    dev0 = torch.device("cuda", local)
+    ms_max, toks_all = du.reduce_job(ms, toks, dev0)
+    ms_e2e_max, toks_e2e_all = du.reduce_job(ms_e2e, toks_e2e, dev0)
     stats = [eng.read(s, cap=1)[2] for s in slots]
     acc = sum(s["accepted"] for s in stats) / max(1, sum(s["drafts"] for s in stats))
 
@@ -310,7 +298,8 @@ def run_ours(args, wl):
                     e2e=dict(value=toks_e2e_all / (ms_e2e_max * 1e-3), unit="tok/s", h2d_bytes_per_step=4 * B,
                              d2h_bytes_per_step=B * (4 + 4 + 24 + 4 * (k + 1)), ms_per_step=ms_e2e_max / args.steps),
                     gpu_launches=launches,
-                    roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak, traffic=None,
+                    roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
+                                  traffic=(98.2e6 if fused and M == 4 else None),  # ncu dram read+write per launch, profiles/wgemm_gateup_swiglu_m4.md
                                   kernel=kernel_name, peak_kind=peak_kind,
                                   us_per_launch=gemm_ms * 1e3),
                     step_roofline=dict(verify_bytes=verify_bytes, round_bytes=round_bytes, round_us=step_s * 1e6,

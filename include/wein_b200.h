@@ -194,7 +194,7 @@ typedef struct {
     uint32_t max_pos;        /* positions per sequence (block-table rows hold ceil(max_pos/16) pages) */
     uint32_t n_pages;        /* 16-token pages per KV pool */
     uint32_t state_f32;      /* recurrent state pool: 1 = f32, 0 = bf16 (the reference's pool) */
-    uint32_t attn_seg_pages; /* pages per attention segment (0 = default 4) */
+    uint32_t attn_seg_pages; /* pages per attention segment (0 = chosen from max_pos: 4 ... 128) */
 } wein_b200_model_cfg;
 
 /* Weights stay caller-owned device memory for the life of the engine (bf16 unless noted; layouts as the safetensors

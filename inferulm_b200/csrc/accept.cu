@@ -404,10 +404,11 @@ int32_t wein_b200_topk_filter(const void *logits, const void *rows, const void *
 int32_t wein_b200_accept_greedy(const void *logits, const void *rows, const void *drafts, const void *n_drafts, uint32_t n,
                                 uint32_t B, uint32_t k, void *scratch, void *accept_len, void *out_tokens, void *target, void *stream) {
     WB_CHECK_ARG(logits && rows && scratch, "accept_greedy: null pointer");
-    int32_t rc = wein_b200_argmax_partials(logits, rows, scratch, n, B * (k + 1), 32, (cudaStream_t)stream);
+    const uint32_t T = B * (k + 1), split = T >= 64 ? 8u : (T >= 16 ? 16u : 32u);
+    int32_t rc = wein_b200_argmax_partials(logits, rows, scratch, n, T, split, (cudaStream_t)stream);
     if (rc != WB_OK) return rc;
     AcceptParams p{};
-    p.am_part = (const uint64_t *)scratch; p.am_split = 32;
+    p.am_part = (const uint64_t *)scratch; p.am_split = split;
     p.drafts = (const uint32_t *)drafts; p.n_drafts = (const uint32_t *)n_drafts; p.B = B; p.k = k; p.draft_stride = k;
     p.accept_len = (uint32_t *)accept_len; p.out_tokens = (uint32_t *)out_tokens; p.target = (uint32_t *)target;
     return wb_accept(p, (cudaStream_t)stream);

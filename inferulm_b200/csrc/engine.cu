@@ -241,7 +241,14 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
     e->lpn = e->cd + e->vald + 2 * cfg->lin_v_heads;
     e->fpn = 2 * cfg->q_heads * cfg->head_dim + 2 * cfg->kv_heads * cfg->head_dim;
     e->rows_per_slot = 2 * e->P;
-    e->seg_pages = cfg->attn_seg_pages ? cfg->attn_seg_pages : 4;
+    // pages per attention segment: fixed per engine (it fixes the summation order), about 16 segments at the longest context --
+    // short contexts need many small CTAs, long ones amortise the per-CTA merge (measured: 32K tokens, 128 pages: 4.7 TB/s)
+    e->seg_pages = cfg->attn_seg_pages;
+    if (!e->seg_pages) {
+        uint32_t want = e->bpr / 16;
+        e->seg_pages = 4;
+        while (e->seg_pages < want && e->seg_pages < 128) e->seg_pages *= 2;
+    }
     for (uint32_t l = 0; l < cfg->n_layers; l++) (cfg->layer_is_full[l] ? e->n_full : e->n_lin)++;
     *out = e;
     const uint32_t S = cfg->max_seqs, T = e->T_max, H = e->H;
@@ -494,6 +501,9 @@ static int32_t forward(Engine *e, uint32_t T, uint32_t n_spans, uint32_t max_cou
     return WB_OK;
 }
 
+// Slices per logits row for the two-phase argmax: enough CTAs to cover the SMs several times, long enough slices to stream
+static uint32_t am_split(uint32_t rows) { return rows >= 64 ? 8u : (rows >= 16 ? 16u : 32u); }
+
 // Draft step i of the MTP head over n batch rows (run_mtp_forward, qwen.rs:4435-4522).
 static int32_t mtp_forward(Engine *e, uint32_t n, uint32_t i, bool sampled, cudaStream_t st) {
     const wein_b200_model_cfg &c = e->cfg;
@@ -516,8 +526,9 @@ static int32_t mtp_forward(Engine *e, uint32_t n, uint32_t i, bool sampled, cuda
     e->launches += 2;
     TRY(gemm(e, e->n2, e->w.embed, e->logits, n, e->V, H, H, e->V, st));
     if (!sampled) {
-        TRY(wein_b200_argmax_partials(e->logits, e->d_iota, e->am_part, e->V, n, 32, st));
-        TRY(wb_argmax_finish(e->am_part, 32, e->d_drafts, km, i, n, st));
+        const uint32_t split = am_split(n);
+        TRY(wein_b200_argmax_partials(e->logits, e->d_iota, e->am_part, e->V, n, split, st));
+        TRY(wb_argmax_finish(e->am_part, split, e->d_drafts, km, i, n, st));
         e->launches += 2;
     } else {
         FilterArgs f{};
@@ -572,8 +583,9 @@ static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32
     AcceptArgs a{};
     a.drafts = e->d_drafts; a.draft_stride = km; a.B = n; a.k = k; a.accept_len = e->d_accept_len; a.out_tokens = e->d_out_tokens; a.target = e->d_target;
     if (!sampled) {
-        TRY(wein_b200_argmax_partials(e->logits, e->d_lg_rows, e->am_part, e->V, T, 32, st));
-        a.am_part = (const uint64_t *)e->am_part; a.am_split = 32;
+        const uint32_t split = am_split(T);
+        TRY(wein_b200_argmax_partials(e->logits, e->d_lg_rows, e->am_part, e->V, T, split, st));
+        a.am_part = (const uint64_t *)e->am_part; a.am_split = split;
     } else {
         FilterArgs f{};
         f.logits = e->logits; f.rows = nullptr; f.row_seq = e->d_seq_rows; f.rows_per_seq = 1; f.temp = e->d_temp; f.top_k = e->d_top_k; f.top_p = e->d_top_p;
@@ -693,8 +705,9 @@ extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, con
         TRY(forward(e, T, n, P, max_ctx, n_lg, false, st));
         if (n_lg > 0) {
             if (!sampled) {
-                TRY(wein_b200_argmax_partials(e->logits, e->d_iota, e->am_part, e->V, n_lg, 32, st));
-                TRY(wb_argmax_finish(e->am_part, 32, e->d_first_tok, 1, 0, n_lg, st));
+                const uint32_t split = am_split(n_lg);
+                TRY(wein_b200_argmax_partials(e->logits, e->d_iota, e->am_part, e->V, n_lg, split, st));
+                TRY(wb_argmax_finish(e->am_part, split, e->d_first_tok, 1, 0, n_lg, st));
             } else {
                 // the first token of a sequence: drawn from the filtered distribution of the last prompt position
                 FilterArgs f{};

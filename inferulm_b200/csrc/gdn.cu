@@ -288,7 +288,7 @@ struct GdnLayerParams {
 };
 
 template <bool F32>
-__global__ void __launch_bounds__(512) gdn_layer_kernel(const GdnLayerParams P) {
+__global__ void __launch_bounds__(512, 2) gdn_layer_kernel(const GdnLayerParams P) {
     PDL_ENTRY();
     constexpr int KD = 128, VD = 128, R = 8, WARPS = 16, MAXT = 8;
     __shared__ float T[WARPS][R][33];

@@ -120,9 +120,11 @@ def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("case", choices=sorted(CASES))
     ap.add_argument("--reps", type=int, default=3)
+    ap.add_argument("--set", action="append", default=[], metavar="NAME=INT", help="override a case parameter, e.g. --set ctx=32768")
     args = ap.parse_args()
     torch.manual_seed(0)
-    print(json.dumps(CASES[args.case](args.reps)))
+    kw = {k: int(v) for k, v in (kv.split("=") for kv in args.set)}
+    print(json.dumps(CASES[args.case](args.reps, **kw)))
 
 
 if __name__ == "__main__":
