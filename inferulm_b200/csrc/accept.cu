@@ -93,7 +93,7 @@ __device__ __forceinline__ void scan_row(const bf16_t *row, uint32_t n, F fn) {
 // One CTA of 1024 threads per row.
 __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P) {
     PDL_ENTRY();
-    __shared__ uint32_t lm[1024];
+    __shared__ __align__(16) uint32_t lm[1024];
     __shared__ uint32_t hist[256];
     __shared__ uint32_t warp_cnt[32];
     __shared__ uint32_t sh[8];        // 0: bound key, 1: bin hi, 2: k left inside bin, 3: tau, 4: need, 5: count_eq, 6: list length, 7: ties emitted
@@ -124,7 +124,14 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
     __syncthreads();
     {
         uint32_t rank = 0;
-        for (uint32_t u = 0; u < 1024; u++) { uint32_t o = lm[u]; rank += (o > best) || (o == best && u < tid); }
+#pragma unroll 4
+        for (uint32_t u = 0; u < 1024; u += 4) {   // vector reads: four candidates per shared-memory round trip
+            const uint4 o4 = *reinterpret_cast<const uint4 *>(&lm[u]);
+            rank += (o4.x > best) || (o4.x == best && u < tid);
+            rank += (o4.y > best) || (o4.y == best && u + 1 < tid);
+            rank += (o4.z > best) || (o4.z == best && u + 2 < tid);
+            rank += (o4.w > best) || (o4.w == best && u + 3 < tid);
+        }
         if (rank == k - 1) sh[0] = best;
     }
     __syncthreads();

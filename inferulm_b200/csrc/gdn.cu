@@ -287,12 +287,14 @@ struct GdnLayerParams {
     float l2_eps, rms_eps;
 };
 
-template <bool F32>
-__global__ void __launch_bounds__(512, 2) gdn_layer_kernel(const GdnLayerParams P) {
+// MINB = CTAs per SM the register budget is planned for: 2 for large grids (bandwidth: more bytes in flight per SM),
+// 1 for small ones (latency: no spills in the token loop)
+template <bool F32, int MINB>
+__global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerParams P) {
     PDL_ENTRY();
     constexpr int KD = 128, VD = 128, R = 8, WARPS = 16, MAXT = 8;
-    __shared__ float T[WARPS][R][33];
-    __shared__ bf16_t qc[MAXT][KD], kc[MAXT][KD], vc[MAXT][VD];
+    __shared__ __align__(16) float T[WARPS][R][36];   // row stride 36 words: float4 reads by lanes 0..7 hit disjoint banks
+    __shared__ __align__(16) bf16_t qc[MAXT][KD], kc[MAXT][KD], vc[MAXT][VD];
     __shared__ float o_s[MAXT][VD];
     __shared__ float inv_s[MAXT][2], gate_s[MAXT][2], red_s[4][4];
     __shared__ __align__(16) float kk_s[MAXT][KD], qq_s[MAXT][KD];
@@ -367,7 +369,19 @@ __global__ void __launch_bounds__(512, 2) gdn_layer_kernel(const GdnLayerParams 
     if (tid < 2 * (int)cnt) {
         const bf16_t *src = (tid & 1) ? kc[tid >> 1] : qc[tid >> 1];
         float s = 0.0f;
-        for (int j = 0; j < KD; j++) { float x = bf2f(src[j]); s = __fadd_rn(__fmul_rn(x, x), s); }
+        uint4 raw[KD / 8];   // the whole row first (16 vector loads), then the ordered sum
+#pragma unroll
+        for (int v8 = 0; v8 < KD / 8; v8++) raw[v8] = *reinterpret_cast<const uint4 *>(src + v8 * 8);
+#pragma unroll
+        for (int v8 = 0; v8 < KD / 8; v8++) {
+            const uint32_t wv[4] = {raw[v8].x, raw[v8].y, raw[v8].z, raw[v8].w};
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                float x0 = __uint_as_float(wv[u] << 16), x1 = __uint_as_float(wv[u] & 0xffff0000u);
+                s = __fadd_rn(__fmul_rn(x0, x0), s);
+                s = __fadd_rn(__fmul_rn(x1, x1), s);
+            }
+        }
         inv_s[tid >> 1][tid & 1] = __fdiv_rn(1.0f, sqrtf(__fadd_rn(s, P.l2_eps)));
     }
     __syncthreads();
@@ -404,9 +418,15 @@ __global__ void __launch_bounds__(512, 2) gdn_layer_kernel(const GdnLayerParams 
         __syncwarp();
         float delta = 0.0f;
         if (lane < R) {
+            float tv[32];   // all 32 slice partials first (8 vector loads in flight), then the ordered fold
+#pragma unroll
+            for (int v4 = 0; v4 < 8; v4++) {
+                const float4 t4 = *reinterpret_cast<const float4 *>(&T[w][lane][v4 * 4]);
+                tv[v4 * 4] = t4.x; tv[v4 * 4 + 1] = t4.y; tv[v4 * 4 + 2] = t4.z; tv[v4 * 4 + 3] = t4.w;
+            }
             float kvm = 0.0f;
-#pragma unroll 8
-            for (int sl = 0; sl < 32; sl++) kvm = __fadd_rn(T[w][lane][sl], kvm);
+#pragma unroll
+            for (int sl = 0; sl < 32; sl++) kvm = __fadd_rn(tv[sl], kvm);
             delta = __fmul_rn(__fsub_rn(vin, kvm), beta);
         }
         __syncwarp();
@@ -425,9 +445,15 @@ __global__ void __launch_bounds__(512, 2) gdn_layer_kernel(const GdnLayerParams 
         }
         __syncwarp();
         if (lane < R) {
+            float tv[32];
+#pragma unroll
+            for (int v4 = 0; v4 < 8; v4++) {
+                const float4 t4 = *reinterpret_cast<const float4 *>(&T[w][lane][v4 * 4]);
+                tv[v4 * 4] = t4.x; tv[v4 * 4 + 1] = t4.y; tv[v4 * 4 + 2] = t4.z; tv[v4 * 4 + 3] = t4.w;
+            }
             float o = 0.0f;
-#pragma unroll 8
-            for (int sl = 0; sl < 32; sl++) o = __fadd_rn(T[w][lane][sl], o);
+#pragma unroll
+            for (int sl = 0; sl < 32; sl++) o = __fadd_rn(tv[sl], o);
             o_s[i][row0 + lane] = rbf(o);   // the core output is stored as bf16 by the reference before the norm reads it
         }
         __syncwarp();
@@ -478,8 +504,14 @@ int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *co
     p.out = (bf16_t *)out; p.row_start = (const uint32_t *)row_start; p.row_count = (const uint32_t *)row_count;
     p.in_row = (const uint32_t *)in_row; p.out_base = (const uint32_t *)out_base;
     p.n_rows = n_rows; p.k_heads = k_heads; p.v_heads = v_heads; p.l2_eps = l2_eps; p.rms_eps = rms_eps;
-    if (state_f32) WB_LAUNCH((gdn_layer_kernel<true>), n_rows * v_heads, 512, 0, st, p);
-    else WB_LAUNCH((gdn_layer_kernel<false>), n_rows * v_heads, 512, 0, st, p);
+    const bool big = (uint64_t)n_rows * v_heads >= 296;
+    if (state_f32) {
+        if (big) WB_LAUNCH((gdn_layer_kernel<true, 2>), n_rows * v_heads, 512, 0, st, p);
+        else WB_LAUNCH((gdn_layer_kernel<true, 1>), n_rows * v_heads, 512, 0, st, p);
+    } else {
+        if (big) WB_LAUNCH((gdn_layer_kernel<false, 2>), n_rows * v_heads, 512, 0, st, p);
+        else WB_LAUNCH((gdn_layer_kernel<false, 1>), n_rows * v_heads, 512, 0, st, p);
+    }
     WB_LAUNCH_CHECK();
     return WB_OK;
 }
