@@ -216,12 +216,20 @@ def run_ours(args, wl):
     sampler.stop_flag = True
     launches = eng.last_launches() * args.steps
     ctx_now = max(p for _, p in eng.counts(slots))
+    # the verify step alone (verify forward over k+1 rows + acceptance + commit): the same round with the draft forwards
+    # skipped through the library's measurement hook (the verify rows then carry stale draft tokens: timing only)
+    import ctypes as C
+    eng.lib.wein_b200_engine_ablate(C.c_uint32(16))
+    timed(min(args.warmup, 3), "graph")
+    ms_verify, _ = timed(args.steps, "graph")
+    eng.lib.wein_b200_engine_ablate(C.c_uint32(int(os.environ.get("WEIN_B200_ABLATE", "0"))))
     timed(min(args.warmup, 3), "e2e")
     ms_e2e, toks_e2e = timed(args.steps, "e2e")
 
     dev0 = torch.device("cuda", local)
     ms_max, toks_all = du.reduce_job(ms, toks, dev0)
     ms_e2e_max, toks_e2e_all = du.reduce_job(ms_e2e, toks_e2e, dev0)
+    ms_verify_max, _ = du.reduce_job(ms_verify, 0, dev0)
     stats = [eng.read(s, cap=1)[2] for s in slots]
     acc = sum(s["accepted"] for s in stats) / max(1, sum(s["drafts"] for s in stats))
 
@@ -302,6 +310,10 @@ def run_ours(args, wl):
                                   traffic=(98.2e6 if fused and M == 4 else None),  # ncu dram read+write per launch, profiles/wgemm_gateup_swiglu_m4.md
                                   kernel=kernel_name, peak_kind=peak_kind,
                                   us_per_launch=gemm_ms * 1e3),
+                    verify_step=dict(us=ms_verify_max / args.steps * 1e3, bytes=verify_bytes,
+                                     achieved_gbs=verify_bytes / (ms_verify_max / args.steps * 1e-3) / 1e9,
+                                     frac_of_measured_peak=verify_bytes / (ms_verify_max / args.steps * 1e-3) / 1e9 / peak,
+                                     frac_of_8tbs=verify_bytes / (ms_verify_max / args.steps * 1e-3) / 8e12),
                     step_roofline=dict(verify_bytes=verify_bytes, round_bytes=round_bytes, round_us=step_s * 1e6,
                                        achieved_gbs=round_bytes / step_s / 1e9, frac_of_measured_peak=round_bytes / step_s / 1e9 / peak,
                                        frac_of_8tbs=round_bytes / step_s / 8e12),

@@ -72,7 +72,7 @@ struct wein_b200_engine {
     std::vector<uint32_t> h_slots_cached;
     uint32_t *h_stage = nullptr;  // pinned
     size_t h_stage_words = 0;
-    std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint32_t>, cudaGraphExec_t> graphs;
+    std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint32_t, uint32_t>, cudaGraphExec_t> graphs;
     uint32_t launches = 0, last_launches = 0;
     // weight matrices in the order a round multiplies them (for the next-weights L2 prefetch); empty = no prefetch
     std::vector<std::pair<const void *, uint64_t>> chain;
@@ -382,8 +382,9 @@ extern "C" int32_t wein_b200_engine_admit(wein_b200_engine *e, uint32_t slot, co
 
 // ------------------------------------------------------------------------------------------------ forward passes
 // Profiling hook (ablation, as the reference's WEIN_ABLATE): bit 0 skips every GEMM launch, bit 1 the residual-add+norm
-// kernels, bit 2 the DeltaNet layer kernel, bit 3 the attention kernels (q/k prep, attention, combine), so timed rounds
-// attribute the in-graph cost of each class; results are then meaningless.  Never set outside measurements.
+// kernels, bit 2 the DeltaNet layer kernel, bit 3 the attention kernels (q/k prep, attention, combine), bit 4 the draft
+// forwards (the verify forward then runs on stale draft tokens: this is how the verify step is timed alone), so timed
+// rounds attribute the in-graph cost of each class; results are then meaningless.  Never set outside measurements.
 static uint32_t g_ablate = 0;
 extern "C" void wein_b200_engine_ablate(uint32_t mask) { g_ablate = mask; }
 
@@ -573,7 +574,8 @@ static void build_chain(Engine *e, uint32_t k, uint32_t T) {
 static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32_t max_ctx, cudaStream_t st) {
     const uint32_t P = k + 1, T = n * P, km = e->cfg.k_max ? e->cfg.k_max : 1;
     build_chain(e, k, T);
-    for (uint32_t i = 0; i < k; i++) TRY(mtp_forward(e, n, i, sampled, st));
+    if (!(g_ablate & 16u))
+        for (uint32_t i = 0; i < k; i++) TRY(mtp_forward(e, n, i, sampled, st));
     WB_LAUNCH((verify_prep_kernel), (n + 127) / 128, 128, 0, st, e->d_slots, slot_state(e), e->d_drafts, km, n, P, e->rows_per_slot, e->P, e->d_tok,
                                                       e->d_pos_rows, e->d_seq_rows, e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base,
                                                       e->d_lg_rows);
@@ -638,7 +640,9 @@ extern "C" int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, c
         e->last_launches = e->launches;
         return WB_OK;
     }
-    auto key = std::make_tuple(n, k, (uint32_t)sampled, bucket);
+    auto key = std::make_tuple(n, k, (uint32_t)sampled, bucket, g_ablate);
+    const std::string gname = "graph_launches:" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string((int)sampled) + ":" +
+                              std::to_string(bucket) + ":" + std::to_string(g_ablate);
     auto it = e->graphs.find(key);
     if (it == e->graphs.end()) {
         cudaGraph_t g = nullptr;
@@ -653,10 +657,9 @@ extern "C" int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, c
         cudaGraphDestroy(g);
         if (ce != cudaSuccess) { wb_set_error("spec_step: graph instantiation failed: %s", cudaGetErrorString(ce)); return WB_ERR_CUDA; }
         it = e->graphs.emplace(key, ge).first;
-        e->named["graph_launches:" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string((int)sampled) + ":" + std::to_string(bucket)] =
-            {nullptr, e->launches};
+        e->named[gname] = {nullptr, e->launches};
     }
-    e->last_launches = (uint32_t)e->named["graph_launches:" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string((int)sampled) + ":" + std::to_string(bucket)].second;
+    e->last_launches = (uint32_t)e->named[gname].second;
     CUDA_TRY(cudaGraphLaunch(it->second, st));
     return WB_OK;
 }
