@@ -33,6 +33,9 @@ def load():
         _lib = C.CDLL(LIB_PATH)
         _lib.wein_b200_last_error.restype = C.c_char_p
         _lib.wein_b200_abi_version.restype = C.c_uint32
+        if os.environ.get("WEIN_B200_GEMM_TUNE"):  # A/B switch "kw,ksplit,depth" (0 = automatic), see wein_b200_gemm_tune
+            kw, ks, unr = (int(v) for v in os.environ["WEIN_B200_GEMM_TUNE"].split(","))
+            _lib.wein_b200_gemm_tune(C.c_uint32(kw), C.c_uint32(ks), C.c_uint32(unr))
         if os.environ.get("WEIN_B200_PREFETCH_MB"):  # A/B switch: cap of the next-weights L2 prefetch (0 = off)
             _lib.wein_b200_gemm_prefetch_cap(C.c_uint64(int(os.environ["WEIN_B200_PREFETCH_MB"]) << 20))
         if os.environ.get("WEIN_B200_ABLATE"):  # profiling only: see wein_b200_engine_ablate

@@ -141,3 +141,33 @@ def test_gemm_wt_small_oracle_and_batch_invariance(ops):
         c = torch.zeros(mm * n, dtype=torch.int16, device="cuda")
         ops.gemm_wt(dev(rows), dev(w), c, mm, n, k)
         assert np.array_equal(u16(c)[:n], u16(c4)[:n]), mm
+
+
+def test_attn_verify_long_context_full_size(ops):
+    """BASELINE long-context shape: one chain of k+1 = 5 rows against a 32,768-token paged KV.  Checked against the oracle
+    (tolerance class) and through the size-independent property that a chain row equals the same row verified alone."""
+    rs = np.random.default_rng(4)
+    ctx, cnt = 32763, 5
+    c = _attn_case(rs, [ctx], cnt)
+    want = orc.paged_attn(c["q"], c["k"], c["v"], c["bt"], c["seq_ids"], c["positions"], 1.0 / 16.0, c["bpr"], 16, 16, 4, 256, threads=8)
+    full = _run_attn(ops, c, 1, cnt, ctx + cnt, 128)
+    rel2, peak = norm_err(orc.bf16_to_f32(full), orc.bf16_to_f32(want))
+    assert rel2 <= 3e-3 and peak <= 1.5e-2, (rel2, peak)
+    single = _run_attn(ops, c, cnt, 1, c["bpr"] * 16, 128, spans=(np.arange(cnt, dtype=np.uint32), np.ones(cnt, np.uint32)))
+    assert np.array_equal(full, single)
+
+
+def test_zero_sized_calls_are_accepted(ops):
+    """Empty inputs (no rows / no tokens) return success without launching, like the reference's launch wrappers."""
+    z16 = torch.zeros(64, dtype=torch.int16, device="cuda")
+    z32 = torch.zeros(64, dtype=torch.int32, device="cuda")
+    zf = torch.zeros(64, dtype=torch.float32, device="cuda")
+    ops.gemm_wt(z16, z16, z16, 0, 32, 32)
+    ops.embed(z32, z16, z16, 32, 0)
+    ops.rms_norm_zc(z16, z16, z16, 0, 32, 1e-6)
+    ops.add(z16, z16, z16, 0)
+    ops.kv_scatter(z16, z16, z32, z32, z32, z16, z16, 1, 16, 32, 0)
+    ops.deltanet(z16, z16, z16, z16, z16, zf, z16, z16, z16, z32, z32, z32, 0, 1, 1, 128, 128, 0, 1e-6, z32, 1)
+    ops.attn_verify(z16, z16, z16, z32, z32, z32, z32, z32, None, z16, 1.0, 4, 16, 4, 1, 64, 0, 1, 16, 4, zf)
+    ops.argmax_rows(z16, z32, torch.zeros(64, dtype=torch.int64, device="cuda"), z32, 8, 0)
+    torch.cuda.synchronize()

@@ -211,3 +211,19 @@ def test_engine_rejects_bad_arguments(small_weights):
     with pytest.raises(WeinB200Error):
         eng.prefill([0], [np.array([99999999], np.uint32)])  # token outside the vocabulary
     eng.close()
+
+
+def test_max_draft_length_k7(small_weights):
+    """The longest supported chain (k = 7, 8 verify rows, two attention m-tiles): speculative == plain greedy."""
+    from inferulm_b200.engine import Engine
+    w = small_weights
+    prompt = _prompt(29, w.shape.vocab, 8)
+    outs = []
+    for k in (0, 7):
+        eng = Engine(w, max_seqs=1, k_max=7, max_pos=512)
+        eng.admit(0, 400)
+        eng.prefill([0], [prompt])
+        eng.generate([0], 30, k)
+        outs.append(eng.read(0)[0][:30])
+        eng.close()
+    assert np.array_equal(outs[0], outs[1])
