@@ -146,6 +146,11 @@ int32_t wein_b200_argmax_rows(const void *x, const void *rows, void *scratch, vo
  * make it outside any stream capture.  All calls on a device share the array: calls that may overlap on the GPU race. */
 int32_t wein_b200_argmax_rows_noalloc(const void *x, const void *rows, void *out, uint32_t n, uint32_t s, void *stream);
 
+/* SampleRowsOp::run (ops/mod.rs:1379-1393): temperature / top-k (<= 64) / top-p sampler with one PCG-XSH-RR state per slot in
+ * `rng` (0 = derive from the row's seed), per-row parameters; temp <= 0 -> argmax; top_k == 0 -> 0xFFFFFFFF (in-band). */
+int32_t wein_b200_sample_rows(const void *x, const void *rows, const void *slots, const void *temp, const void *top_k, const void *top_p,
+                              const void *seed, void *rng, void *out, uint32_t n, uint32_t s, void *stream);
+
 /* ------------------------------------------------------------------------------------------------------
  * Acceptance (stands in for Qwen35Executor::spec_finish, crates/wein-exec/src/qwen.rs:2419-2502, which runs on the
  * host after a sync and a readback in the reference).

@@ -71,6 +71,12 @@ struct FilterParams {
     uint32_t sample_mul, sample_off;
     const uint64_t *seed, *round;  // per sequence
     uint32_t position;
+    // optional: the reference's plain sampler (SampleRowsOp, reference.rs:787-877): PCG-XSH-RR state per slot in `pcg_rng`
+    // (0 = not yet seeded: derived from pcg_seed[row]), one uniform per row, pick over e_j/denom (not renormalised)
+    uint64_t *pcg_rng;
+    const uint32_t *pcg_slots;
+    const uint64_t *pcg_seed;
+    uint32_t *pcg_out;         // [s]; the compact-distribution outputs may then be null
 };
 
 // Applies fn(key, index) to every element of the row, 8 elements per 16-byte load when aligned.
@@ -107,11 +113,15 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
     const bool greedy = !(temp > 0.0f);
     uint32_t k = greedy ? 1u : min(P.top_k[seq], (uint32_t)DIST_CAP);
     const size_t oslot = (size_t)r * P.out_mul + P.out_off, sslot = (size_t)r * P.sample_mul + P.sample_off;
-    uint32_t *ids = P.out_ids + oslot * DIST_CAP;
-    float *probs = P.out_probs + oslot * DIST_CAP;
+    uint32_t *ids = P.out_ids ? P.out_ids + oslot * DIST_CAP : nullptr;
+    float *probs = P.out_probs ? P.out_probs + oslot * DIST_CAP : nullptr;
     if (k == 0 || P.n == 0) {  // top_k = 0 (whole vocabulary) is not supported on the device: in-band error, as the reference
-        if (tid < DIST_CAP) { ids[tid] = 0xffffffffu; probs[tid] = 0.0f; }
-        if (tid == 0) { P.out_n[oslot] = 0; if (P.sample_out) P.sample_out[sslot] = 0xffffffffu; }
+        if (tid < DIST_CAP && ids) { ids[tid] = 0xffffffffu; probs[tid] = 0.0f; }
+        if (tid == 0) {
+            if (P.out_n) P.out_n[oslot] = 0;
+            if (P.sample_out) P.sample_out[sslot] = 0xffffffffu;
+            if (P.pcg_out) P.pcg_out[r] = 0xffffffffu;
+        }
         return;
     }
     if (k > P.n) k = P.n;
@@ -212,12 +222,36 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
                 keep = j + 1;
                 if (cacc >= pp) break;
             }
+            if (P.pcg_out) {   // reference.rs:857-874, PCG of reference.rs:756-775
+                uint64_t st = P.pcg_rng[P.pcg_slots[r]];
+                if (st == 0) {
+                    uint64_t x = P.pcg_seed[r] + 0x9e3779b97f4a7c15ull;
+                    x = (x ^ (x >> 30)) * 0xbf58476d1ce4e5b9ull;
+                    x = (x ^ (x >> 27)) * 0x94d049bb133111ebull;
+                    st = (x ^ (x >> 31)) | 1ull;
+                }
+                const uint64_t old = st;
+                st = old * 6364136223846793005ull + 1442695040888963407ull;
+                const uint32_t xs = (uint32_t)(((old >> 18) ^ old) >> 27), rot = (uint32_t)(old >> 59);
+                const uint32_t rnd = (xs >> rot) | (xs << ((32 - rot) & 31));
+                P.pcg_rng[P.pcg_slots[r]] = st;
+                const float u = __fmul_rn((float)(rnd >> 8), 1.0f / 16777216.0f);
+                float acc = 0.0f;
+                uint32_t pick = keep - 1;
+                for (uint32_t j = 0; j < keep; j++) {
+                    acc = __fadd_rn(__fdiv_rn(e_s[j], denom), acc);
+                    if (u < acc) { pick = j; break; }
+                }
+                P.pcg_out[r] = srt_idx[pick];
+            }
+        } else if (P.pcg_out) {
+            P.pcg_out[r] = srt_idx[0];   // temp <= 0: argmax, the RNG is not advanced (reference.rs:798-801)
         }
         float z = 0.0f;
         for (uint32_t j = 0; j < keep; j++) z = __fadd_rn(e_s[j], z);
         for (uint32_t j = 0; j < keep; j++) e_s[j] = __fdiv_rn(e_s[j], z);
         sh[6] = keep;
-        P.out_n[oslot] = keep;
+        if (P.out_n) P.out_n[oslot] = keep;
         if (P.sample_out) {
             uint32_t tok = srt_idx[0];
             if (!greedy) {
@@ -229,7 +263,7 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
         }
     }
     __syncthreads();
-    if (tid < DIST_CAP) {
+    if (tid < DIST_CAP && ids) {
         bool live = tid < sh[6];
         ids[tid] = live ? srt_idx[tid] : 0xffffffffu;
         probs[tid] = live ? e_s[tid] : 0.0f;
@@ -354,7 +388,8 @@ __global__ void __launch_bounds__(32) accept_kernel(const AcceptParams P) {
 
 
 int32_t wb_topk_filter(const FilterParams &p, cudaStream_t st) {
-    WB_CHECK_ARG(p.x && p.temp && p.top_k && p.top_p && p.out_ids && p.out_probs && p.out_n, "topk_filter: null pointer");
+    WB_CHECK_ARG(p.x && p.temp && p.top_k && p.top_p && ((p.out_ids && p.out_probs && p.out_n) || p.pcg_out), "topk_filter: null pointer");
+    WB_CHECK_ARG(!p.pcg_out || (p.pcg_rng && p.pcg_slots && p.pcg_seed), "sample_rows: rng, slots and seed are required");
     WB_CHECK_ARG(p.row_seq || p.rows_per_seq > 0, "topk_filter: rows_per_seq must be positive");
     WB_CHECK_ARG(!p.sample_out || (p.seed && p.round), "topk_filter: sampling needs seed and round");
     if (p.s == 0) return WB_OK;
@@ -403,6 +438,21 @@ int32_t wein_b200_topk_filter(const void *logits, const void *rows, const void *
     p.out_ids = (uint32_t *)out_ids; p.out_probs = (float *)out_probs; p.out_n = (uint32_t *)out_n;
     p.sample_out = (uint32_t *)sample_out; p.seed = (const uint64_t *)seed; p.round = (const uint64_t *)round; p.position = position;
     p.out_mul = 1; p.out_off = 0; p.sample_mul = 1; p.sample_off = 0;
+    return wb_topk_filter(p, (cudaStream_t)stream);
+}
+
+// SampleRowsOp::run (crates/wein-kernel/src/ops/mod.rs:1379-1393): x [*, n] bf16, rows [s] sampled row ids, slots [s] RNG slot
+// of each row, temp / top_k / top_p / seed [s] per row, rng [slots] u64 PCG states (0 = derive from the seed), out [s]
+// (0xFFFFFFFF = top_k 0 with temp > 0).  Bit-identical to the reference sampler for rows whose top-k lies within the
+// reference kernel's per-lane ladder (always, for distinct-enough logits; reference.rs:783-786).
+int32_t wein_b200_sample_rows(const void *x, const void *rows, const void *slots, const void *temp, const void *top_k, const void *top_p,
+                              const void *seed, void *rng, void *out, uint32_t n, uint32_t s, void *stream) {
+    WB_CHECK_ARG(rows && slots && seed && rng && out, "sample_rows: null pointer");
+    FilterParams p{};
+    p.x = (const bf16_t *)x; p.rows = (const uint32_t *)rows; p.rows_per_seq = 1;
+    p.temp = (const float *)temp; p.top_k = (const uint32_t *)top_k; p.top_p = (const float *)top_p; p.n = n; p.s = s;
+    p.out_mul = 1; p.sample_mul = 1;
+    p.pcg_rng = (uint64_t *)rng; p.pcg_slots = (const uint32_t *)slots; p.pcg_seed = (const uint64_t *)seed; p.pcg_out = (uint32_t *)out;
     return wb_topk_filter(p, (cudaStream_t)stream);
 }
 

@@ -199,3 +199,9 @@ ARGMAX_NOALLOC_MAX_ROWS = 256
 def argmax_rows_noalloc(x, rows, out, n, s):
     """argmax_rows without a scratch argument: for callers that cannot allocate (at most ARGMAX_NOALLOC_MAX_ROWS rows)."""
     check(load().wein_b200_argmax_rows_noalloc(_ptr(x), _ptr(rows), _ptr(out), U32(n), U32(s), _stream()))
+
+
+def sample_rows(x, rows, slots, temp, top_k, top_p, seed, rng, out, n, s):
+    """SampleRowsOp::run: per-row temperature / top-k / top-p sampling with PCG state in `rng` (int64 tensor, advanced in place)."""
+    check(load().wein_b200_sample_rows(_ptr(x), _ptr(rows), _ptr(slots), _ptr(temp), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(rng),
+                                       _ptr(out), U32(n), U32(s), _stream()))

@@ -163,3 +163,47 @@ def test_rejection_sampling_chi_square_on_device(ops):
     assert chi < chi2.ppf(1 - 1e-4, sup.sum() - 1), chi
     qfull = np.zeros(n); qfull[qi1[0][:qn1[0]]] = qp1[0][:qn1[0]]
     assert abs(host(al, np.uint32).mean() - np.minimum(expect, qfull).sum()) < 0.01
+
+
+def _sample(ops, x, n, s, temp, top_k, top_p, seed, rng_dev):
+    out = torch.zeros(s, dtype=torch.int32, device="cuda")
+    ops.sample_rows(dev(x), dev(np.arange(s, dtype=np.uint32)), dev(np.arange(s, dtype=np.uint32)), dev(np.asarray(temp, np.float32)),
+                    dev(np.asarray(top_k, np.uint32)), dev(np.asarray(top_p, np.float32)), dev(np.asarray(seed, np.uint64)), rng_dev, out, n, s)
+    return host(out, np.uint32)
+
+
+def test_sample_rows_matches_reference_sampler_bitwise(ops):
+    """k10 of crates/wein-kernel/tests/ops_sample.rs:392-417 (kernel == reference, random logits / parameters / seeds), run
+    over several consecutive calls so the PCG state carried in the device buffer is exercised, plus k1 (temp = 0 == argmax)."""
+    for (s, n, tk, tp, temp) in [(6, 33, 4, 0.9, 1.0), (5, 257, 64, 1.0, 0.7), (4, 1000, 8, 0.5, 1.3), (3, 513, 1, 1.0, 1.0), (4, V, 50, 0.9, 0.7)]:
+        x = orc.vec_bf16(0xD4, s * n, 5.0)
+        seeds = np.array([0x7000 + j * 977 for j in range(s)], np.uint64)
+        rng_dev = torch.zeros(s, dtype=torch.int64, device="cuda")
+        rng_ref = np.zeros(s, np.uint64)
+        for call in range(4):
+            got = _sample(ops, x, n, s, [temp] * s, [tk] * s, [tp] * s, seeds, rng_dev)
+            want = orc.sample_rows(x, np.arange(s), n, [temp] * s, [tk] * s, [tp] * s, seeds, np.arange(s), rng_ref)
+            assert np.array_equal(got, want), (s, n, tk, tp, temp, call)
+        assert np.array_equal(host(rng_dev, np.uint64), rng_ref)
+    x = orc.vec_bf16(0x51, 3 * 1024, 4.0)
+    rng_dev = torch.zeros(3, dtype=torch.int64, device="cuda")
+    got = _sample(ops, x, 1024, 3, [0.0] * 3, [0] * 3, [1.0] * 3, [1] * 3, rng_dev)
+    assert np.array_equal(got, orc.argmax_rows(x, np.arange(3), 1024))
+    assert int(rng_dev.abs().sum()) == 0                      # greedy rows do not advance the RNG
+    bad = _sample(ops, x, 1024, 3, [1.0] * 3, [0] * 3, [1.0] * 3, [1] * 3, rng_dev)
+    assert (bad == 0xFFFFFFFF).all()
+
+
+def test_sample_rows_chi_square(ops):
+    """k8 of ops_sample.rs:350-387 on the device: 0.5/0.3/0.15/0.05, 200k draws, chi-square below 21.108 (dof 3, alpha 1e-4)."""
+    s, n = 512, 4
+    logits = orc.f32_to_bf16(np.log(np.array([0.5, 0.3, 0.15, 0.05], np.float32)))
+    x = np.tile(logits, s)
+    rng_dev = torch.zeros(s, dtype=torch.int64, device="cuda")
+    seeds = 0xABC000 + np.arange(s, dtype=np.uint64)
+    cnt = np.zeros(n)
+    for _ in range(391):
+        cnt += np.bincount(_sample(ops, x, n, s, [1.0] * s, [64] * s, [1.0] * s, seeds, rng_dev), minlength=n)
+    p = np.exp(orc.bf16_to_f32(logits).astype(np.float64)); p /= p.sum()
+    chi = ((cnt - cnt.sum() * p) ** 2 / (cnt.sum() * p)).sum()
+    assert chi < 21.108, chi
