@@ -24,6 +24,7 @@ SOURCES = [
     ("fused_glue.cu", ["-fmad=false"]),
     ("attn.cu", []),
     ("gemm.cu", []),
+    ("gemm_stream.cu", []),
     ("engine.cu", []),
 ]
 

@@ -128,8 +128,10 @@ __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;"
 
 // Host-side launch helper: every kernel goes through cudaLaunchKernelEx so the attribute can be switched globally.
 extern bool g_wb_pdl;
+void wb_prepare_kernel(const void *kern);  // once per kernel: the same shared-memory carve-out preference for every kernel of the library
 template <typename... KArgs, typename... Args>
 static inline cudaError_t wb_launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
+    wb_prepare_kernel(reinterpret_cast<const void *>(kern));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute at[1];

@@ -17,6 +17,7 @@
 #include <stdio.h>
 #include <string.h>
 #include <map>
+#include <set>
 #include <string>
 #include <tuple>
 #include <vector>
@@ -78,6 +79,7 @@ struct wein_b200_engine {
     std::vector<std::pair<const void *, uint64_t>> chain;
     size_t chain_pos = 0;
     std::map<std::string, std::pair<void *, uint64_t>> named;
+    std::set<uint32_t> lt_tuned;   // row counts m > 32 whose library GEMM algorithms have been chosen by timing
 };
 typedef wein_b200_engine Engine;
 
@@ -571,6 +573,43 @@ static void build_chain(Engine *e, uint32_t k, uint32_t T) {
     e->chain.push_back({e->w.embed, (uint64_t)e->V * H * 2});
 }
 
+// Forwards of more than 32 rows multiply through cuBLASLt.  Its first heuristic answer is rarely the fastest for these
+// skinny weight-streaming shapes, so the first time a row count is seen every product shape of the forward is timed once
+// on the engine's own buffers (activations are scratch between rounds) and the winner is kept.  Not capturable: called
+// before a round is captured or run.
+static int32_t tune_rows(Engine *e, uint32_t m, bool mtp, cudaStream_t st) {
+    if (m <= 32 || e->lt_tuned.count(m | (mtp ? 0x80000000u : 0u))) return WB_OK;
+    const wein_b200_model_cfg &c = e->cfg;
+    const uint32_t H = e->H, II = e->II, qd = c.q_heads * c.head_dim;
+    auto tune_layer = [&](const wein_b200_layer_weights &w, bool full) -> int32_t {
+        if (full) {
+            TRY(wb_gemm_lt_autotune(e->n1, w.qg, e->proj, m, e->fpn, H, H, e->fpn, st));
+            TRY(wb_gemm_lt_autotune(e->attn, w.o, e->o, m, H, qd, qd, H, st));
+        } else {
+            TRY(wb_gemm_lt_autotune(e->n1, w.qkv, e->proj, m, e->lpn, H, H, e->lpn, st));
+            TRY(wb_gemm_lt_autotune(e->normed, w.out, e->o, m, H, e->vald, e->vald, H, st));
+        }
+        TRY(wb_gemm_lt_autotune(e->n2, w.wg, e->gu, m, 2 * II, H, H, 2 * II, st));
+        TRY(wb_gemm_lt_autotune(e->m, w.wd, e->d, m, H, II, II, H, st));
+        return WB_OK;
+    };
+    if (mtp) {
+        TRY(wb_gemm_lt_autotune(e->cat, e->w.mtp_fc, e->x, m, H, 2 * H, 2 * H, H, st));
+        TRY(tune_layer(e->w.mtp_layer, true));
+    } else {
+        bool seen_full = false, seen_lin = false;
+        for (uint32_t l = 0; l < c.n_layers; l++) {
+            const bool full = c.layer_is_full[l] != 0;
+            if (full ? seen_full : seen_lin) continue;
+            (full ? seen_full : seen_lin) = true;
+            TRY(tune_layer(e->w.layers[l], full));
+        }
+    }
+    TRY(wb_gemm_lt_autotune(e->n2, e->w.embed, e->logits, m, e->V, H, H, e->V, st));
+    e->lt_tuned.insert(m | (mtp ? 0x80000000u : 0u));
+    return WB_OK;
+}
+
 static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32_t max_ctx, cudaStream_t st) {
     const uint32_t P = k + 1, T = n * P, km = e->cfg.k_max ? e->cfg.k_max : 1;
     build_chain(e, k, T);
@@ -634,6 +673,8 @@ extern "C" int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, c
     uint32_t bucket = 256;
     while (bucket < ctx_bound) bucket *= 2;
     if (bucket > e->bpr * 16) bucket = e->bpr * 16;
+    TRY(tune_rows(e, n * (k + 1), false, st));
+    if (k) TRY(tune_rows(e, n, true, st));
     if (!use_graph) {
         e->launches = 0;
         TRY(run_round(e, n, k, sampled, bucket, st));

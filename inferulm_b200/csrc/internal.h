@@ -8,6 +8,12 @@ int32_t wb_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n
 int32_t wb_gemm_swiglu(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k, uint32_t lda,
                        uint32_t ldc, void *scratch, uint64_t scratch_bytes, cudaStream_t st);
 void wb_gemm_set_next(const void *w, uint64_t bytes);  // hint for the next skinny GEMM launch: what the stream multiplies after it
+int32_t wb_tgemm(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, bool swiglu,
+                 cudaStream_t st);  // bulk-copy staged skinny GEMM (m <= 32), arguments already validated
+bool wb_tgemm_supports(uint32_t n, uint32_t k, bool swiglu);
+int32_t wb_tgemm_init();  // its one-time shared-memory opt-in, outside any stream capture
+int32_t wb_gemm_lt_autotune(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc,
+                            cudaStream_t st);  // picks the fastest library algorithm for a shape with m > 32; synchronises, not capturable
 int32_t wb_gemm_warmup();  // creates the cuBLASLt handle and workspace outside any stream capture
 int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, const void *block_table, const void *seq_ids,
                        const void *positions, const void *row_start, const void *row_count, const void *gate, void *out,

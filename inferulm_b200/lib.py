@@ -38,6 +38,12 @@ def load():
             _lib.wein_b200_gemm_tune(C.c_uint32(kw), C.c_uint32(ks), C.c_uint32(unr))
         if os.environ.get("WEIN_B200_PREFETCH_MB"):  # A/B switch: cap of the next-weights L2 prefetch (0 = off)
             _lib.wein_b200_gemm_prefetch_cap(C.c_uint64(int(os.environ["WEIN_B200_PREFETCH_MB"]) << 20))
+        if os.environ.get("WEIN_B200_GEMM_IMPL"):  # A/B switch: 0 register-streaming, 1 bulk-copy staged skinny GEMM
+            _lib.wein_b200_gemm_impl(C.c_uint32(int(os.environ["WEIN_B200_GEMM_IMPL"])))
+        if os.environ.get("WEIN_B200_CARVEOUT"):  # A/B switch: shared-memory carve-out preference (percent, -1 = driver default)
+            _lib.wein_b200_set_carveout(C.c_int32(int(os.environ["WEIN_B200_CARVEOUT"])))
+        if os.environ.get("WEIN_B200_LT_TUNE"):  # A/B switch: 0 = keep cuBLASLt's first heuristic answer for forwards of > 32 rows
+            _lib.wein_b200_gemm_lt_tune(C.c_uint32(int(os.environ["WEIN_B200_LT_TUNE"])))
         if os.environ.get("WEIN_B200_ABLATE"):  # profiling only: see wein_b200_engine_ablate
             _lib.wein_b200_engine_ablate(C.c_uint32(int(os.environ["WEIN_B200_ABLATE"])))
         if os.environ.get("WEIN_B200_PDL", "1") != "1":  # A/B switch: 0 = every kernel fully serialised, 3 = all but the GEMMs overlap

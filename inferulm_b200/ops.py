@@ -186,6 +186,18 @@ def gemm_tune(kw=0, ksplit=0, unr=0):
     load().wein_b200_gemm_tune(U32(kw), U32(ksplit), U32(unr))
 
 
+def gemm_impl(impl=0):
+    """A/B hook: 0 = register-streaming skinny GEMM (default), 1 = TMA-staged skinny GEMM (k % 64 == 0; other shapes keep 0)."""
+    load().wein_b200_gemm_impl(U32(impl))
+
+
+def gemm_stream_timeouts():
+    """Barrier waits of the TMA-staged GEMM that gave up since the library was loaded (0 in a healthy run); synchronises."""
+    v = C.c_uint32(0)
+    check(load().wein_b200_gemm_stream_timeouts(C.byref(v)))
+    return v.value
+
+
 def gdn_layer(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state_f32, out, row_start, row_count, in_row, out_base,
               n_rows, k_heads, v_heads, l2_eps, rms_eps):
     check(load().wein_b200_gdn_layer(_ptr(proj), U32(ld), _ptr(conv_w), _ptr(conv_state), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w),
