@@ -106,6 +106,24 @@ int32_t wein_b200_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, v
                             const void *row_start, const void *row_count, const void *in_row, const void *out_base,
                             uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps, float rms_eps, void *stream);
 
+/* Snapshot-lite pair.  No counterpart in the reference's operator set: the reference writes a full state row per verify
+ * position (DeltanetOp::run with per-position rows, ops/mod.rs:886-1050) and names this scheme as the next step for its
+ * speculative commit (crates/wein-exec/src/qwen.rs:5480-5624).
+ * gdn_layer_lite: as gdn_layer, but the recurrent state pool is only READ (row in_row[r]); instead of state rows it writes one
+ *   record per (token, v-head) to log [tokens, v_heads, 264] f32 (16-byte aligned): delta[128] | k-hat[128] | decay | pad.  Conv
+ *   state rows and `out` are written exactly as by gdn_layer.
+ * gdn_commit: for every span r and every head of n_layers layers, replays records 0..a (a = min(accept_len[r], row_count[r]-1))
+ *   on state row in_row[r] and stores row out_base[r] + a: bit for bit the row gdn_layer would have written there.  `states`
+ *   and `logs` are DEVICE arrays of n_layers device pointers (state pools / logs of the layers). */
+int32_t wein_b200_gdn_layer_lite(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log,
+                                 const void *dt_bias, const void *norm_w, const void *state, uint32_t state_f32, void *out,
+                                 const void *row_start, const void *row_count, const void *in_row, const void *out_base,
+                                 uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps, float rms_eps, void *log,
+                                 void *stream);
+int32_t wein_b200_gdn_commit(const void *states, const void *logs, uint32_t n_layers, uint32_t state_f32, const void *row_start,
+                             const void *row_count, const void *in_row, const void *out_base, const void *accept_len,
+                             uint32_t n_rows, uint32_t v_heads, void *stream);
+
 /* PagedAttnOp::run (ops/mod.rs:1687-1704) plus the scratch buffer that the reference's op object owns privately
  * (wein_b200_attn_scratch_bytes(tokens, kv_heads, head_dim, 16) bytes).  16-token pages; head_dim 64 / 128 / 256. */
 uint64_t wein_b200_attn_scratch_bytes(uint32_t n_spans, uint32_t kv_heads, uint32_t head_dim, uint32_t max_segs);

@@ -51,6 +51,9 @@ struct wein_b200_engine {
     std::vector<void *> allocs;
     uint64_t bytes = 0;
     std::vector<void *> lin_state, conv_state, k_pool, v_pool;  // k/v pools: full layers then the MTP layer
+    std::vector<float *> lin_log;      // per DeltaNet layer: update records of a round's positions (snapshot-lite verification)
+    void **d_state_ptrs = nullptr;     // device copies of lin_state / lin_log for the one-launch commit
+    float **d_log_ptrs = nullptr;
     // per-slot device state
     uint32_t *d_pos, *d_pending, *d_state_row, *d_bank, *d_out_count, *d_top_k, *d_ring, *d_block_table;
     uint64_t *d_round, *d_seed, *d_stats;
@@ -265,6 +268,17 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
         TRY(dalloc(e, &c, (size_t)S * e->rows_per_slot * conv_row, ("conv_state:" + std::to_string(i)).c_str(), false));
         e->lin_state.push_back(p); e->conv_state.push_back(c);
     }
+    if (e->P >= 3 && e->n_lin) {
+        // from three positions per round on, a round logs its state updates instead of writing a snapshot per position
+        for (uint32_t i = 0; i < e->n_lin; i++) {
+            float *lg;
+            TRY(dalloc(e, &lg, (size_t)T * cfg->lin_v_heads * 264, ("lin_log:" + std::to_string(i)).c_str(), false));
+            e->lin_log.push_back(lg);
+        }
+        TRY(dalloc(e, &e->d_state_ptrs, e->n_lin, "state_ptrs")); TRY(dalloc(e, &e->d_log_ptrs, e->n_lin, "log_ptrs"));
+        CUDA_TRY(cudaMemcpy(e->d_state_ptrs, e->lin_state.data(), e->n_lin * sizeof(void *), cudaMemcpyHostToDevice));
+        CUDA_TRY(cudaMemcpy(e->d_log_ptrs, e->lin_log.data(), e->n_lin * sizeof(float *), cudaMemcpyHostToDevice));
+    }
     size_t he = (size_t)cfg->kv_heads * cfg->head_dim;
     for (uint32_t i = 0; i < e->n_full; i++) {
         bf16_t *k, *v;
@@ -388,6 +402,8 @@ extern "C" int32_t wein_b200_engine_admit(wein_b200_engine *e, uint32_t slot, co
 // forwards (the verify forward then runs on stale draft tokens: this is how the verify step is timed alone), so timed
 // rounds attribute the in-graph cost of each class; results are then meaningless.  Never set outside measurements.
 static uint32_t g_ablate = 0;
+static bool g_lite = true;   // A/B switch: false writes a state snapshot per position in every round
+extern "C" void wein_b200_engine_lite(uint32_t on) { g_lite = on != 0; }
 extern "C" void wein_b200_engine_ablate(uint32_t mask) { g_ablate = mask; }
 
 // Tells the GEMM about to be launched which weights come after it in the round, if this launch is where the chain expects it.
@@ -457,7 +473,7 @@ static int32_t mlp_block(Engine *e, const wein_b200_layer_weights &w, uint32_t T
 
 // The verify forward (run_forward, qwen.rs:3843-4153) over the T rows described by the step tables.  n_lg rows of
 // lg_rows get logits (all T when lg_all).
-static int32_t forward(Engine *e, uint32_t T, uint32_t n_spans, uint32_t max_count, uint32_t max_ctx, uint32_t n_lg, bool lg_all, cudaStream_t st) {
+static int32_t forward(Engine *e, uint32_t T, uint32_t n_spans, uint32_t max_count, uint32_t max_ctx, uint32_t n_lg, bool lg_all, bool lite, cudaStream_t st) {
     const wein_b200_model_cfg &c = e->cfg;
     uint32_t H = e->H;
     TRY(wein_b200_embed(e->d_tok, e->w.embed, e->x, H, T, st));
@@ -482,7 +498,8 @@ static int32_t forward(Engine *e, uint32_t T, uint32_t n_spans, uint32_t max_cou
             }
             // conv + SiLU + conv rows + l2 norms + gates + chain recurrence + gated norm: one launch per layer
             if (!(g_ablate & 4u)) TRY(wb_gdn_layer(e->proj, e->lpn, w.conv, e->conv_state[li], w.a_log, w.dt_bias, w.norm, e->lin_state[li], c.state_f32, e->normed,
-                             e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base, n_spans, c.lin_k_heads, vh, c.l2_eps, c.rms_eps, st));
+                             e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base, n_spans, c.lin_k_heads, vh, c.l2_eps, c.rms_eps,
+                             lite ? e->lin_log[li] : nullptr, st));
             e->launches += 1;
             TRY(gemm(e, e->normed, w.out, e->o, T, H, e->vald, e->vald, H, st));
             li++;
@@ -620,7 +637,9 @@ static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32
                                                       e->d_lg_rows);
     WB_LAUNCH_CHECK();
     e->launches += 1 + k;
-    TRY(forward(e, T, n, P, max_ctx, T, true, st));
+    // three positions or more: log the state updates, materialise the accepted state once after acceptance (below)
+    const bool lite = g_lite && P >= 3 && !e->lin_log.empty();
+    TRY(forward(e, T, n, P, max_ctx, T, true, lite, st));
     AcceptArgs a{};
     a.drafts = e->d_drafts; a.draft_stride = km; a.B = n; a.k = k; a.accept_len = e->d_accept_len; a.out_tokens = e->d_out_tokens; a.target = e->d_target;
     if (!sampled) {
@@ -636,6 +655,11 @@ static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32
         a.temp = e->d_temp; a.seed = e->d_seed; a.round = e->d_round; a.slot_of = e->d_slots;
     }
     TRY(wb_accept_args(a, st));
+    if (lite && !(g_ablate & 4u)) {
+        TRY(wb_gdn_commit(e->d_state_ptrs, e->d_log_ptrs, e->n_lin, e->cfg.state_f32, e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base,
+                          e->d_accept_len, n, e->cfg.lin_v_heads, st));
+        e->launches++;
+    }
     WB_LAUNCH((commit_kernel), n, 128, 0, st, e->d_slots, slot_state(e), e->d_accept_len, e->d_out_tokens, e->d_out_base, e->x, P, k, e->H);
     WB_LAUNCH_CHECK();
     e->launches += 3;
@@ -681,7 +705,7 @@ extern "C" int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, c
         e->last_launches = e->launches;
         return WB_OK;
     }
-    auto key = std::make_tuple(n, k, (uint32_t)sampled, bucket, g_ablate);
+    auto key = std::make_tuple(n, k, (uint32_t)sampled, bucket, g_ablate | (g_lite ? 0u : 0x8000u));
     const std::string gname = "graph_launches:" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string((int)sampled) + ":" +
                               std::to_string(bucket) + ":" + std::to_string(g_ablate);
     auto it = e->graphs.find(key);
@@ -746,7 +770,7 @@ extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, con
         WB_LAUNCH_CHECK();
         uint32_t max_ctx = base + P < e->bpr * 16 ? base + P : e->bpr * 16;
         e->chain.clear();
-        TRY(forward(e, T, n, P, max_ctx, n_lg, false, st));
+        TRY(forward(e, T, n, P, max_ctx, n_lg, false, false, st));
         if (n_lg > 0) {
             if (!sampled) {
                 const uint32_t split = am_split(n_lg);

@@ -285,7 +285,10 @@ struct GdnLayerParams {
     const uint32_t *row_start, *row_count, *in_row, *out_base;
     uint32_t n_rows, k_heads, v_heads;
     float l2_eps, rms_eps;
+    float *log;                // null: write a state snapshot per position.  Else [tokens, v_heads, GDN_LOG_W]: write only what a
+                               // position did to the state (delta[128], k-hat[128], decay) and no state at all
 };
+#define GDN_LOG_W 264          // floats per (token, v-head) record: delta at 0, k-hat at 128, decay at 256; 1056 bytes, 16-byte aligned
 
 // MINB = CTAs per SM the register budget is planned for: 2 for large grids (bandwidth: more bytes in flight per SM),
 // 1 for small ones (latency: no spills in the token loop)
@@ -457,9 +460,18 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
             o_s[i][row0 + lane] = rbf(o);   // the core output is stored as bf16 by the reference before the norm reads it
         }
         __syncwarp();
-        size_t e0 = (base + i) * row_elems + (size_t)h * head_elems + (size_t)row0 * KD + lane * 4;
+        if (P.log) {
+            float *lg = P.log + ((size_t)(t0 + i) * P.v_heads + h) * GDN_LOG_W;
+            if (lane < R) lg[row0 + lane] = delta;
+            if (w == 0) {
+                *reinterpret_cast<float4 *>(&lg[128 + lane * 4]) = make_float4(kk[0], kk[1], kk[2], kk[3]);
+                if (lane == 0) lg[256] = decay;
+            }
+        } else {
+            size_t e0 = (base + i) * row_elems + (size_t)h * head_elems + (size_t)row0 * KD + lane * 4;
 #pragma unroll
-        for (int rr = 0; rr < R; rr++) StateIO<F32>::store(P.state, e0 + (size_t)rr * KD, S[rr]);
+            for (int rr = 0; rr < R; rr++) StateIO<F32>::store(P.state, e0 + (size_t)rr * KD, S[rr]);
+        }
     }
     __syncthreads();
     // ---- gated RMSNorm over the head (reference.rs:699-713): warp-group g = tid / 128 takes tokens g, g+4
@@ -493,7 +505,7 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
 int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log, const void *dt_bias,
                      const void *norm_w, void *state, uint32_t state_f32, void *out, const void *row_start, const void *row_count,
                      const void *in_row, const void *out_base, uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps,
-                     float rms_eps, cudaStream_t st) {
+                     float rms_eps, void *log, cudaStream_t st) {
     WB_CHECK_ARG(proj && conv_w && conv_state && a_log && dt_bias && norm_w && state && out && row_start && row_count && in_row && out_base,
                  "gdn_layer: null pointer");
     WB_CHECK_ARG(k_heads > 0 && v_heads % k_heads == 0, "gdn_layer: v_heads %u must be a multiple of k_heads %u", v_heads, k_heads);
@@ -503,7 +515,8 @@ int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *co
     p.a_log = (const float *)a_log; p.dt_bias = (const bf16_t *)dt_bias; p.norm_w = (const float *)norm_w; p.state = state;
     p.out = (bf16_t *)out; p.row_start = (const uint32_t *)row_start; p.row_count = (const uint32_t *)row_count;
     p.in_row = (const uint32_t *)in_row; p.out_base = (const uint32_t *)out_base;
-    p.n_rows = n_rows; p.k_heads = k_heads; p.v_heads = v_heads; p.l2_eps = l2_eps; p.rms_eps = rms_eps;
+    p.n_rows = n_rows; p.k_heads = k_heads; p.v_heads = v_heads; p.l2_eps = l2_eps; p.rms_eps = rms_eps; p.log = (float *)log;
+    WB_CHECK_ARG(((uintptr_t)log & 15u) == 0, "gdn_layer: the update log must be 16-byte aligned");
     const bool big = (uint64_t)n_rows * v_heads >= 296;
     if (state_f32) {
         if (big) WB_LAUNCH((gdn_layer_kernel<true, 2>), n_rows * v_heads, 512, 0, st, p);
@@ -522,5 +535,98 @@ extern "C" int32_t wein_b200_gdn_layer(const void *proj, uint32_t ld, const void
                                        const void *row_start, const void *row_count, const void *in_row, const void *out_base,
                                        uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps, float rms_eps, void *stream) {
     return wb_gdn_layer(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state_f32, out, row_start, row_count, in_row, out_base,
-                        n_rows, k_heads, v_heads, l2_eps, rms_eps, (cudaStream_t)stream);
+                        n_rows, k_heads, v_heads, l2_eps, rms_eps, nullptr, (cudaStream_t)stream);
+}
+
+// ---------------------------------------------------------------------------------------------------------------------
+// Snapshot-lite verification.  A state snapshot per position costs (1 + P) x 64 KiB (f32) of HBM traffic per head and
+// layer, although only one of the P snapshots survives acceptance.  With a log the layer kernel above writes no state: per
+// position it records what that position did to the state -- S <- decay * S, then S[r][c] <- fma(k-hat[c], delta[r], S[r][c])
+// -- in 1 KiB, and once the accept length a is known gdn_commit_kernel replays records 0..a on the input state, element by
+// element with the very operations of the layer kernel, and stores the one state that is kept: (1 + 1 + 1) x 64 KiB
+// instead of (1 + P).  The stored row is out_base + a, i.e. the row the snapshot of position a would occupy, so the
+// result is bit-identical to the snapshot path and nothing around it changes.
+struct GdnCommitParams {
+    void *const *states;        // [layers] state pools [rows, v_heads, 128, 128]
+    const float *const *logs;   // [layers] logs [tokens, v_heads, GDN_LOG_W]
+    const uint32_t *row_start, *row_count, *in_row, *out_base, *accept_len;
+    uint32_t v_heads;
+};
+
+template <bool F32>
+__global__ void __launch_bounds__(512) gdn_commit_kernel(const GdnCommitParams P) {
+    PDL_ENTRY();
+    constexpr int KD = 128, VD = 128, R = 8;
+    const int lane = threadIdx.x & 31, w = threadIdx.x >> 5;
+    const uint32_t r = blockIdx.x / P.v_heads, h = blockIdx.x % P.v_heads, layer = blockIdx.y;
+    const uint32_t cnt = P.row_count[r];
+    if (cnt == 0) return;
+    const uint32_t a = min(P.accept_len[r], cnt - 1), t0 = P.row_start[r];
+    const size_t head_elems = (size_t)VD * KD, row_elems = (size_t)P.v_heads * head_elems;
+    const uint32_t row0 = w * R;
+    void *state = P.states[layer];
+    const float *log = P.logs[layer];
+    float S[R][4];
+    {
+        size_t e0 = (size_t)P.in_row[r] * row_elems + (size_t)h * head_elems + (size_t)row0 * KD + lane * 4;
+#pragma unroll
+        for (int i = 0; i < R; i++) StateIO<F32>::load(state, e0 + (size_t)i * KD, S[i]);
+    }
+    for (uint32_t i = 0; i <= a; i++) {
+        const float *lg = log + ((size_t)(t0 + i) * P.v_heads + h) * GDN_LOG_W;
+        const float decay = lg[256];
+        const float4 k4 = *reinterpret_cast<const float4 *>(&lg[128 + lane * 4]);
+        const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+        float d[R];
+#pragma unroll
+        for (int rr = 0; rr < R; rr++) d[rr] = lg[row0 + rr];
+#pragma unroll
+        for (int rr = 0; rr < R; rr++)
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                float s = fmaf(kk[u], d[rr], __fmul_rn(S[rr][u], decay));
+                if (!F32) s = rbf(s);
+                S[rr][u] = s;
+            }
+    }
+    size_t e1 = ((size_t)P.out_base[r] + a) * row_elems + (size_t)h * head_elems + (size_t)row0 * KD + lane * 4;
+#pragma unroll
+    for (int rr = 0; rr < R; rr++) StateIO<F32>::store(state, e1 + (size_t)rr * KD, S[rr]);
+}
+
+int32_t wb_gdn_commit(void *const *states, const float *const *logs, uint32_t n_layers, uint32_t state_f32, const void *row_start,
+                      const void *row_count, const void *in_row, const void *out_base, const void *accept_len, uint32_t n_rows,
+                      uint32_t v_heads, cudaStream_t st) {
+    WB_CHECK_ARG(states && logs && row_start && row_count && in_row && out_base && accept_len, "gdn_commit: null pointer");
+    if (n_rows == 0 || n_layers == 0) return WB_OK;
+    GdnCommitParams p{};
+    p.states = states; p.logs = logs; p.row_start = (const uint32_t *)row_start; p.row_count = (const uint32_t *)row_count;
+    p.in_row = (const uint32_t *)in_row; p.out_base = (const uint32_t *)out_base; p.accept_len = (const uint32_t *)accept_len; p.v_heads = v_heads;
+    dim3 grid(n_rows * v_heads, n_layers);
+    if (state_f32) WB_LAUNCH((gdn_commit_kernel<true>), grid, 512, 0, st, p);
+    else WB_LAUNCH((gdn_commit_kernel<false>), grid, 512, 0, st, p);
+    WB_LAUNCH_CHECK();
+    return WB_OK;
+}
+
+// The layer kernel in log mode: as wein_b200_gdn_layer, but the state pool is only read (row in_row) and `log`
+// ([tokens, v_heads, 264] f32) receives one record per position and head.  No counterpart in the reference's operator set:
+// it implements what the reference lists as its next step for the speculative commit.
+extern "C" int32_t wein_b200_gdn_layer_lite(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log,
+                                            const void *dt_bias, const void *norm_w, const void *state, uint32_t state_f32, void *out,
+                                            const void *row_start, const void *row_count, const void *in_row, const void *out_base,
+                                            uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps, float rms_eps, void *log,
+                                            void *stream) {
+    WB_CHECK_ARG(log != nullptr, "gdn_layer_lite: the update log is required");
+    return wb_gdn_layer(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, const_cast<void *>(state), state_f32, out, row_start, row_count,
+                        in_row, out_base, n_rows, k_heads, v_heads, l2_eps, rms_eps, log, (cudaStream_t)stream);
+}
+
+// Replays the records 0..accept_len[r] of span r on state row in_row[r] and stores row out_base[r] + accept_len[r], for
+// every head of `n_layers` layers in one launch.  `states` and `logs` are DEVICE arrays of n_layers device pointers.
+extern "C" int32_t wein_b200_gdn_commit(const void *states, const void *logs, uint32_t n_layers, uint32_t state_f32, const void *row_start,
+                                        const void *row_count, const void *in_row, const void *out_base, const void *accept_len,
+                                        uint32_t n_rows, uint32_t v_heads, void *stream) {
+    return wb_gdn_commit((void *const *)states, (const float *const *)logs, n_layers, state_f32, row_start, row_count, in_row, out_base,
+                         accept_len, n_rows, v_heads, (cudaStream_t)stream);
 }

@@ -44,6 +44,8 @@ def load():
             _lib.wein_b200_set_carveout(C.c_int32(int(os.environ["WEIN_B200_CARVEOUT"])))
         if os.environ.get("WEIN_B200_LT_TUNE"):  # A/B switch: 0 = keep cuBLASLt's first heuristic answer for forwards of > 32 rows
             _lib.wein_b200_gemm_lt_tune(C.c_uint32(int(os.environ["WEIN_B200_LT_TUNE"])))
+        if os.environ.get("WEIN_B200_LITE"):  # A/B switch: 0 = a DeltaNet state snapshot per verify position instead of update records
+            _lib.wein_b200_engine_lite(C.c_uint32(int(os.environ["WEIN_B200_LITE"])))
         if os.environ.get("WEIN_B200_ABLATE"):  # profiling only: see wein_b200_engine_ablate
             _lib.wein_b200_engine_ablate(C.c_uint32(int(os.environ["WEIN_B200_ABLATE"])))
         if os.environ.get("WEIN_B200_PDL", "1") != "1":  # A/B switch: 0 = every kernel fully serialised, 3 = all but the GEMMs overlap

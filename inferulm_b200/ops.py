@@ -186,6 +186,25 @@ def gemm_tune(kw=0, ksplit=0, unr=0):
     load().wein_b200_gemm_tune(U32(kw), U32(ksplit), U32(unr))
 
 
+def gdn_layer_lite(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state_f32, out, row_start, row_count, in_row, out_base,
+                   n_rows, k_heads, v_heads, l2_eps, rms_eps, log):
+    """gdn_layer without state snapshots: one update record per (token, v-head) into log [tokens, v_heads, 264] f32."""
+    check(load().wein_b200_gdn_layer_lite(_ptr(proj), U32(ld), _ptr(conv_w), _ptr(conv_state), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w),
+                                          _ptr(state), U32(state_f32), _ptr(out), _ptr(row_start), _ptr(row_count), _ptr(in_row),
+                                          _ptr(out_base), U32(n_rows), U32(k_heads), U32(v_heads), F32(l2_eps), F32(rms_eps), _ptr(log),
+                                          _stream()))
+
+
+def gdn_commit(states, logs, state_f32, row_start, row_count, in_row, out_base, accept_len, n_rows, v_heads):
+    """Replays records 0..accept_len[r] on row in_row[r] of every layer's pool and stores row out_base[r] + accept_len[r].
+    states / logs: lists of device tensors (one per layer)."""
+    sp = torch.tensor([t.data_ptr() for t in states], dtype=torch.int64, device="cuda")
+    lp = torch.tensor([t.data_ptr() for t in logs], dtype=torch.int64, device="cuda")
+    check(load().wein_b200_gdn_commit(_ptr(sp), _ptr(lp), U32(len(states)), U32(state_f32), _ptr(row_start), _ptr(row_count), _ptr(in_row),
+                                      _ptr(out_base), _ptr(accept_len), U32(n_rows), U32(v_heads), _stream()))
+    torch.cuda.current_stream().synchronize()   # the pointer arrays above are temporaries
+
+
 def gemm_impl(impl=0):
     """A/B hook: 0 = register-streaming skinny GEMM (default), 1 = TMA-staged skinny GEMM (k % 64 == 0; other shapes keep 0)."""
     load().wein_b200_gemm_impl(U32(impl))

@@ -282,3 +282,57 @@ def test_gdn_layer_fusion_equals_operator_chain(ops, state_f32):
     assert np.array_equal(u16(cs_d), want_conv.reshape(-1))
     got_state = host(st_d, np.float32 if state_f32 else np.uint16)
     assert np.array_equal(got_state.view(np.uint32 if state_f32 else np.uint16), want_state.reshape(-1).view(np.uint32 if state_f32 else np.uint16))
+
+
+@pytest.mark.parametrize("state_f32", [1, 0])
+def test_gdn_lite_commit_equals_snapshot(ops, state_f32):
+    """Snapshot-lite: the layer kernel in log mode followed by gdn_commit leaves, for every accept length a, bit for bit the
+    state row that the snapshot path writes at out_base + a; outputs and conv-state rows do not depend on the mode, and the
+    log mode writes no state row at all."""
+    rs = np.random.default_rng(33)
+    kh, vh = 16, 32
+    keyd, vald = kh * 128, vh * 128
+    cd = 2 * keyd + vald
+    ld = cd + vald + 2 * vh
+    counts = [4, 1, 8, 3, 5]
+    n = len(counts)
+    T = sum(counts)
+    row_start = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.uint32)
+    row_count = np.array(counts, np.uint32)
+    pool_rows = n * 16
+    in_row = (np.arange(n) * 16 + 2).astype(np.uint32)
+    out_base = (np.arange(n) * 16 + 8).astype(np.uint32)
+    proj = rand_bf16(rs, T * ld, 1.0)
+    conv_w = rand_bf16(rs, cd * 4, 0.5)
+    conv_state = rand_bf16(rs, pool_rows * cd * 3, 1.0)
+    a_log = (rs.standard_normal(vh) * 0.5).astype(np.float32)
+    dtb = rand_bf16(rs, vh, 0.5)
+    norm_w = (1 + 0.1 * rs.standard_normal(128)).astype(np.float32)
+    st16 = rand_bf16(rs, pool_rows * vh * 128 * 128, 0.3)
+    state = orc.bf16_to_f32(st16).copy() if state_f32 else st16
+    sdt = np.float32 if state_f32 else np.uint16
+    bits = np.uint32 if state_f32 else np.uint16
+    args = (dev(proj), ld, dev(conv_w))
+    tabs = (dev(row_start), dev(row_count), dev(in_row), dev(out_base))
+    # snapshot path
+    cs_a, st_a = dev(conv_state), dev(state)
+    out_a = torch.zeros(T * vald, dtype=torch.int16, device="cuda")
+    ops.gdn_layer(*args, cs_a, dev(a_log), dev(dtb), dev(norm_w), st_a, state_f32, out_a, *tabs, n, kh, vh, 1e-6, 1e-6)
+    snap = host(st_a, sdt).view(bits).reshape(pool_rows, -1)
+    # log path
+    cs_b, st_b = dev(conv_state), dev(state)
+    out_b = torch.zeros(T * vald, dtype=torch.int16, device="cuda")
+    log = torch.zeros(T * vh * 264, dtype=torch.float32, device="cuda")
+    ops.gdn_layer_lite(*args, cs_b, dev(a_log), dev(dtb), dev(norm_w), st_b, state_f32, out_b, *tabs, n, kh, vh, 1e-6, 1e-6, log)
+    assert np.array_equal(u16(out_a), u16(out_b))
+    assert np.array_equal(u16(cs_a), u16(cs_b))
+    assert np.array_equal(host(st_b, sdt).view(bits), state.view(bits))   # untouched
+    for trial, acc in enumerate(([3, 0, 7, 1, 2], [0, 0, 0, 0, 0], [3, 0, 7, 2, 4], [9, 9, 9, 9, 9])):
+        st_c = dev(state)
+        ops.gdn_commit([st_c], [log], state_f32, tabs[0], tabs[1], tabs[2], tabs[3], dev(np.array(acc, np.uint32)), n, vh)
+        got = host(st_c, sdt).view(bits).reshape(pool_rows, -1)
+        want = state.view(bits).reshape(pool_rows, -1).copy()
+        for s_ in range(n):
+            a = min(acc[s_], counts[s_] - 1)
+            want[out_base[s_] + a] = snap[out_base[s_] + a]
+        assert np.array_equal(got, want), trial
