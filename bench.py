@@ -281,7 +281,12 @@ def run_ours(args, wl):
     st_row = shape.lin_v_heads * 128 * 128 * 4
     conv_row = (2 * shape.lin_k_heads * 128 + shape.lin_v_heads * 128) * 3 * 2
     kv_tok = 2 * shape.kv_heads * shape.head_dim * 2
-    verify_bytes = (shape.weight_bytes() + B * n_lin * (1 + P) * (st_row + conv_row) + B * n_full * kv_tok * (ctx_now + P)
+    # DeltaNet state: with three or more positions the engine logs per-position updates and materialises one state per chain
+    # (read by the layer, read + written by the commit: 3 rows, plus the 1056-byte records written and read back); below
+    # that, and with WEIN_B200_LITE=0, one row is read and a snapshot per position written (1 + P rows)
+    lite = P >= 3 and os.environ.get("WEIN_B200_LITE", "1") != "0"
+    state_bytes = (3 * st_row + 2 * P * shape.lin_v_heads * 1056) if lite else (1 + P) * st_row
+    verify_bytes = (shape.weight_bytes() + B * n_lin * (state_bytes + (1 + P) * conv_row) + B * n_full * kv_tok * (ctx_now + P)
                     + 2 * B * P * shape.vocab * 2)
     round_bytes = verify_bytes + k * shape.mtp_bytes()
     step_s = ms_max * 1e-3 / args.steps
@@ -314,6 +319,8 @@ def run_ours(args, wl):
                                      achieved_gbs=verify_bytes / (ms_verify_max / args.steps * 1e-3) / 1e9,
                                      frac_of_measured_peak=verify_bytes / (ms_verify_max / args.steps * 1e-3) / 1e9 / peak,
                                      frac_of_8tbs=verify_bytes / (ms_verify_max / args.steps * 1e-3) / 8e12),
+                    state_traffic=("update records + one committed state per chain (3 state rows per layer)" if lite
+                                   else "one state snapshot per position (1 + P state rows per layer)"),
                     step_roofline=dict(verify_bytes=verify_bytes, round_bytes=round_bytes, round_us=step_s * 1e6,
                                        achieved_gbs=round_bytes / step_s / 1e9, frac_of_measured_peak=round_bytes / step_s / 1e9 / peak,
                                        frac_of_8tbs=round_bytes / step_s / 8e12),

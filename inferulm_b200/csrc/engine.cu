@@ -402,6 +402,8 @@ extern "C" int32_t wein_b200_engine_admit(wein_b200_engine *e, uint32_t slot, co
 // forwards (the verify forward then runs on stale draft tokens: this is how the verify step is timed alone), so timed
 // rounds attribute the in-graph cost of each class; results are then meaningless.  Never set outside measurements.
 static uint32_t g_ablate = 0;
+static bool g_fast_sampled = true;   // A/B switch, see spec_step
+extern "C" void wein_b200_engine_fast_sampled(uint32_t on) { g_fast_sampled = on != 0; }
 static bool g_lite = true;   // A/B switch: false writes a state snapshot per position in every round
 extern "C" void wein_b200_engine_lite(uint32_t on) { g_lite = on != 0; }
 extern "C" void wein_b200_engine_ablate(uint32_t mask) { g_ablate = mask; }
@@ -450,7 +452,7 @@ static int32_t full_attn_block(Engine *e, const wein_b200_layer_weights &w, void
 
 static int32_t mlp_block(Engine *e, const wein_b200_layer_weights &w, uint32_t T, cudaStream_t st) {
     uint32_t H = e->H, II = e->II;
-    if (T <= 32 && adjacent(w.wg, w.wu, (size_t)II * H)) {
+    if (T <= wb_gemm_skinny_max() && adjacent(w.wg, w.wu, (size_t)II * H)) {
         // gate|up projection with the SwiGLU activation in the epilogue: one launch, no [T, 2*inter] round trip
         e->launches++;
         chain_hint(e, w.wg);
@@ -595,7 +597,7 @@ static void build_chain(Engine *e, uint32_t k, uint32_t T) {
 // on the engine's own buffers (activations are scratch between rounds) and the winner is kept.  Not capturable: called
 // before a round is captured or run.
 static int32_t tune_rows(Engine *e, uint32_t m, bool mtp, cudaStream_t st) {
-    if (m <= 32 || e->lt_tuned.count(m | (mtp ? 0x80000000u : 0u))) return WB_OK;
+    if (m <= wb_gemm_skinny_max() || e->lt_tuned.count(m | (mtp ? 0x80000000u : 0u))) return WB_OK;
     const wein_b200_model_cfg &c = e->cfg;
     const uint32_t H = e->H, II = e->II, qd = c.q_heads * c.head_dim;
     auto tune_layer = [&](const wein_b200_layer_weights &w, bool full) -> int32_t {
@@ -697,6 +699,9 @@ extern "C" int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, c
     uint32_t bucket = 256;
     while (bucket < ctx_bound) bucket *= 2;
     if (bucket > e->bpr * 16) bucket = e->bpr * 16;
+    // Rounds with sampled chains give up the batch-independent bits of the skinny GEMM between 17 and 32 rows for the
+    // library's speed there (acceptance is then exact in distribution, not bitwise against a plain decode run)
+    struct SkinnyScope { SkinnyScope(uint32_t m) { wb_gemm_set_skinny_max(m); } ~SkinnyScope() { wb_gemm_set_skinny_max(32); } } skinny(sampled && g_fast_sampled ? 16 : 32);
     TRY(tune_rows(e, n * (k + 1), false, st));
     if (k) TRY(tune_rows(e, n, true, st));
     if (!use_graph) {
@@ -705,7 +710,7 @@ extern "C" int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, c
         e->last_launches = e->launches;
         return WB_OK;
     }
-    auto key = std::make_tuple(n, k, (uint32_t)sampled, bucket, g_ablate | (g_lite ? 0u : 0x8000u));
+    auto key = std::make_tuple(n, k, (uint32_t)sampled, bucket, g_ablate | (g_lite ? 0u : 0x8000u) | (g_fast_sampled ? 0u : 0x4000u));
     const std::string gname = "graph_launches:" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string((int)sampled) + ":" +
                               std::to_string(bucket) + ":" + std::to_string(g_ablate);
     auto it = e->graphs.find(key);

@@ -346,6 +346,14 @@ int32_t wb_gemm_warmup() {
     return lt_init();
 }
 
+// Largest row count the skinny kernel takes; above it the product goes to cuBLASLt.  32 by default.  The skinny kernel
+// keeps a row's bits independent of the batch, which greedy speculation needs (a verify row must equal the same row of a
+// plain decode step), but from 17 rows on it streams at only ~3 TB/s where the library reaches ~5 TB/s: a caller that does
+// not need that property (a round of sampled chains) may lower the limit to 16 for the duration of its launches.
+static uint32_t g_skinny_max = 32;
+void wb_gemm_set_skinny_max(uint32_t m) { g_skinny_max = m < 32 ? m : 32; }
+uint32_t wb_gemm_skinny_max() { return g_skinny_max; }
+
 // Shape -> algorithm chosen for it: the heuristic's first answer, or the fastest of its first 16 answers once the
 // shape has been tuned (wb_gemm_lt_autotune: timed on the device, outside any capture).
 struct LtKey {
@@ -412,7 +420,7 @@ static int32_t lt_gemm(const void *a, const void *w, void *c, uint32_t m, uint32
 static bool g_lt_tune_on = true;
 extern "C" void wein_b200_gemm_lt_tune(uint32_t on) { g_lt_tune_on = on != 0; }   // A/B switch: 0 keeps the heuristic's first answer
 int32_t wb_gemm_lt_autotune(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, cudaStream_t st) {
-    if (m <= 32 || !g_lt_tune_on) return WB_OK;
+    if (m <= g_skinny_max || !g_lt_tune_on) return WB_OK;
     std::lock_guard<std::mutex> lk(g_lt.mu);
     if (lt_init() != WB_OK) return WB_ERR_CUDA;
     const LtKey key{m, n, k, lda, ldc};
@@ -462,7 +470,7 @@ int32_t wb_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n
     WB_CHECK_ARG(lda >= k && ldc >= n && lda % 8 == 0, "gemm_wt: bad leading dimensions");
     WB_CHECK_ARG(((((uintptr_t)a) | ((uintptr_t)w)) & 15u) == 0, "gemm_wt: operands must be 16-byte aligned");
     if (m == 0) return WB_OK;
-    if (m <= 32) return wgemm_launch(a, w, c, m, n, k, lda, ldc, scratch, scratch_bytes, false, st);
+    if (m <= g_skinny_max) return wgemm_launch(a, w, c, m, n, k, lda, ldc, scratch, scratch_bytes, false, st);
     return lt_gemm(a, w, c, m, n, k, lda, ldc, st);
 }
 

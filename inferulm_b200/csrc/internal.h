@@ -14,6 +14,8 @@ bool wb_tgemm_supports(uint32_t n, uint32_t k, bool swiglu);
 int32_t wb_tgemm_init();  // its one-time shared-memory opt-in, outside any stream capture
 int32_t wb_gemm_lt_autotune(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc,
                             cudaStream_t st);  // picks the fastest library algorithm for a shape with m > 32; synchronises, not capturable
+void wb_gemm_set_skinny_max(uint32_t m);  // rows up to which the batch-invariant skinny kernel is used (<= 32, default 32)
+uint32_t wb_gemm_skinny_max();
 int32_t wb_gemm_warmup();  // creates the cuBLASLt handle and workspace outside any stream capture
 int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, const void *block_table, const void *seq_ids,
                        const void *positions, const void *row_start, const void *row_count, const void *gate, void *out,

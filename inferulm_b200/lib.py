@@ -46,6 +46,8 @@ def load():
             _lib.wein_b200_gemm_lt_tune(C.c_uint32(int(os.environ["WEIN_B200_LT_TUNE"])))
         if os.environ.get("WEIN_B200_LITE"):  # A/B switch: 0 = a DeltaNet state snapshot per verify position instead of update records
             _lib.wein_b200_engine_lite(C.c_uint32(int(os.environ["WEIN_B200_LITE"])))
+        if os.environ.get("WEIN_B200_FAST_SAMPLED"):  # A/B switch: 0 = sampled rounds keep the skinny GEMM up to 32 rows
+            _lib.wein_b200_engine_fast_sampled(C.c_uint32(int(os.environ["WEIN_B200_FAST_SAMPLED"])))
         if os.environ.get("WEIN_B200_ABLATE"):  # profiling only: see wein_b200_engine_ablate
             _lib.wein_b200_engine_ablate(C.c_uint32(int(os.environ["WEIN_B200_ABLATE"])))
         if os.environ.get("WEIN_B200_PDL", "1") != "1":  # A/B switch: 0 = every kernel fully serialised, 3 = all but the GEMMs overlap
