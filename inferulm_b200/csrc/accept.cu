@@ -79,17 +79,26 @@ struct FilterParams {
     uint32_t *pcg_out;         // [s]; the compact-distribution outputs may then be null
 };
 
-// Applies fn(key, index) to every element of the row, 8 elements per 16-byte load when aligned.
+// Applies fn(key, index) to every element of the row, 8 elements per 16-byte load when aligned; a thread issues four loads
+// before it consumes them (a row is read by one CTA: what bounds a pass is load latency, not bandwidth).
 template <typename F>
 __device__ __forceinline__ void scan_row(const bf16_t *row, uint32_t n, F fn) {
     if ((((uintptr_t)row) & 15u) == 0) {
-        uint32_t nv = n / 8;
-        for (uint32_t v = threadIdx.x; v < nv; v += blockDim.x) {
-            uint4 q = *reinterpret_cast<const uint4 *>(row + (size_t)v * 8);
-            uint32_t wv[4] = {q.x, q.y, q.z, q.w};
+        const uint32_t nv = n / 8, step = blockDim.x;
+        auto eat = [&](const uint4 &q, uint32_t v) {
+            const uint32_t wv[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
             for (int j = 0; j < 4; j++) { fn(ord_key(wv[j]), v * 8 + 2 * j); fn(ord_key(wv[j] >> 16), v * 8 + 2 * j + 1); }
+        };
+        uint32_t v = threadIdx.x;
+        for (; v + 3 * step < nv; v += 4 * step) {
+            const uint4 q0 = *reinterpret_cast<const uint4 *>(row + (size_t)v * 8);
+            const uint4 q1 = *reinterpret_cast<const uint4 *>(row + (size_t)(v + step) * 8);
+            const uint4 q2 = *reinterpret_cast<const uint4 *>(row + (size_t)(v + 2 * step) * 8);
+            const uint4 q3 = *reinterpret_cast<const uint4 *>(row + (size_t)(v + 3 * step) * 8);
+            eat(q0, v); eat(q1, v + step); eat(q2, v + 2 * step); eat(q3, v + 3 * step);
         }
+        for (; v < nv; v += step) eat(*reinterpret_cast<const uint4 *>(row + (size_t)v * 8), v);
         for (uint32_t i = nv * 8 + threadIdx.x; i < n; i += blockDim.x) fn(ord_key(row[i]), i);
     } else {
         for (uint32_t i = threadIdx.x; i < n; i += blockDim.x) fn(ord_key(row[i]), i);
@@ -102,7 +111,8 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
     __shared__ __align__(16) uint32_t lm[1024];
     __shared__ uint32_t hist[256];
     __shared__ uint32_t warp_cnt[32];
-    __shared__ uint32_t sh[8];        // 0: bound key, 1: bin hi, 2: k left inside bin, 3: tau, 4: need, 5: count_eq, 6: list length, 7: ties emitted
+    __shared__ uint32_t sv_idx[1024]; // survivors of the bound (their keys reuse lm)
+    __shared__ uint32_t sh[9];        // 8: number of survivors; 0: bound key, 1: bin hi, 2: k left inside bin, 3: tau, 4: need, 5: count_eq, 6: list length, 7: ties emitted
     __shared__ uint32_t cand_key[DIST_CAP], cand_idx[DIST_CAP];
     __shared__ uint32_t srt_idx[DIST_CAP];
     __shared__ float srt_v[DIST_CAP], e_s[DIST_CAP];
@@ -130,7 +140,7 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
     scan_row(row, P.n, [&](uint32_t key, uint32_t) { best = max(best, key); });
     lm[tid] = best;
     if (tid < 256) hist[tid] = 0;
-    if (tid < 8) sh[tid] = 0;
+    if (tid < 9) sh[tid] = 0;
     __syncthreads();
     {
         uint32_t rank = 0;
@@ -146,7 +156,25 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
     }
     __syncthreads();
     const uint32_t bound = sh[0];
-    // pass 2: histogram of the high byte over the survivors; find the byte holding the k-th largest
+    const float inv_t = greedy ? 1.0f : __fdiv_rn(1.0f, temp);
+    // pass 2: the survivors of the bound.  At most k threads hold a maximum >= bound, so barring heavy ties there are
+    // barely more than k of them: list them (key, index) and rank the list by (value descending, index ascending) --
+    // ranks 0..k-1 are the answer, ties at the threshold resolved towards the lowest index, already in output order.
+    scan_row(row, P.n, [&](uint32_t key, uint32_t i) {
+        if (key >= bound) { uint32_t slot = atomicAdd(&sh[8], 1u); if (slot < 1024u) { lm[slot] = key; sv_idx[slot] = i; } }
+    });
+    __syncthreads();
+    const uint32_t n_surv = sh[8];
+    if (n_surv <= 1024u) {
+        if (tid < n_surv) {
+            const uint32_t mk = lm[tid], mi = sv_idx[tid];
+            uint32_t rank = 0;
+            for (uint32_t u = 0; u < n_surv; u++) { const uint32_t ok = lm[u]; rank += (ok > mk) || (ok == mk && sv_idx[u] < mi); }
+            if (rank < k) { srt_idx[rank] = mi; srt_v[rank] = __fmul_rn(bf2f(key_to_bf16(mk)), inv_t); }
+        }
+    } else {
+    // more than 1024 elements at or above the bound (massive ties): exact selection by two histogram passes
+    // pass 2b: histogram of the high byte over the survivors; find the byte holding the k-th largest
     scan_row(row, P.n, [&](uint32_t key, uint32_t) { if (key >= bound) atomicAdd(&hist[key >> 8], 1u); });
     __syncthreads();
     if (tid == 0) {
@@ -199,13 +227,13 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
     }
     __syncthreads();
     // sort the k candidates: value descending, index ascending
-    const float inv_t = greedy ? 1.0f : __fdiv_rn(1.0f, temp);
     if (tid < k) {
         uint32_t mk = cand_key[tid], mi = cand_idx[tid], rank = 0;
         for (uint32_t u = 0; u < k; u++) rank += (cand_key[u] > mk) || (cand_key[u] == mk && cand_idx[u] < mi);
         srt_idx[rank] = mi;
         srt_v[rank] = __fmul_rn(bf2f(key_to_bf16(mk)), inv_t);
     }
+    }   // end of the massive-ties path
     __syncthreads();
     if (tid < k) e_s[tid] = expf_ref(__fsub_rn(srt_v[tid], srt_v[0]));
     __syncthreads();

@@ -290,6 +290,10 @@ struct GdnLayerParams {
 };
 #define GDN_LOG_W 264          // floats per (token, v-head) record: delta at 0, k-hat at 128, decay at 256; 1056 bytes, 16-byte aligned
 
+// Measured and dropped: the 128 v-rows of a head split over a cluster of 4 CTAs of 128 threads (gated-norm leaders exchanged
+// through distributed shared memory, bit-identical).  The recurrence gets faster, but every CTA repeats the q / k conv, l2
+// norms and k-hat / q-hat with a quarter of the threads, and those phases are half of the kernel: 2.78 vs 2.71 ms per round
+// at batch 1, 6.80 vs 6.33 ms at batch 32.
 // MINB = CTAs per SM the register budget is planned for: 2 for large grids (bandwidth: more bytes in flight per SM),
 // 1 for small ones (latency: no spills in the token loop)
 template <bool F32, int MINB>
