@@ -115,7 +115,7 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
     __shared__ uint32_t sh[9];        // 8: number of survivors; 0: bound key, 1: bin hi, 2: k left inside bin, 3: tau, 4: need, 5: count_eq, 6: list length, 7: ties emitted
     __shared__ uint32_t cand_key[DIST_CAP], cand_idx[DIST_CAP];
     __shared__ uint32_t srt_idx[DIST_CAP];
-    __shared__ float srt_v[DIST_CAP], e_s[DIST_CAP];
+    __shared__ float srt_v[DIST_CAP], e_s[DIST_CAP], pn[DIST_CAP], shf[2];
     const uint32_t r = blockIdx.x, tid = threadIdx.x;
     const uint32_t seq = P.row_seq ? P.row_seq[r] : r / P.rows_per_seq;
     const bf16_t *row = P.x + (size_t)(P.rows ? P.rows[r] : r) * P.n;
@@ -138,23 +138,34 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
     // pass 1: a lower bound of the k-th largest key = the k-th largest of the per-thread maxima
     uint32_t best = 0;
     scan_row(row, P.n, [&](uint32_t key, uint32_t) { best = max(best, key); });
-    lm[tid] = best;
     if (tid < 256) hist[tid] = 0;
     if (tid < 9) sh[tid] = 0;
     __syncthreads();
-    {
-        uint32_t rank = 0;
-#pragma unroll 4
-        for (uint32_t u = 0; u < 1024; u += 4) {   // vector reads: four candidates per shared-memory round trip
-            const uint4 o4 = *reinterpret_cast<const uint4 *>(&lm[u]);
-            rank += (o4.x > best) || (o4.x == best && u < tid);
-            rank += (o4.y > best) || (o4.y == best && u + 1 < tid);
-            rank += (o4.z > best) || (o4.z == best && u + 2 < tid);
-            rank += (o4.w > best) || (o4.w == best && u + 3 < tid);
-        }
-        if (rank == k - 1) sh[0] = best;
+    // the k-th largest of the 1024 per-thread maxima by a two-level radix select (high byte, then low byte, of the 16-bit key)
+    atomicAdd(&hist[best >> 8], 1u);
+    __syncthreads();
+    if (tid == 0) {
+        uint32_t above = 0;
+        int b = 255;
+        for (; b > 0; b--) { if (above + hist[b] >= k) break; above += hist[b]; }
+        sh[1] = (uint32_t)b; sh[2] = k - above;
     }
     __syncthreads();
+    {
+        const uint32_t mhi = sh[1];
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        if ((best >> 8) == mhi) atomicAdd(&hist[best & 255u], 1u);
+        __syncthreads();
+        if (tid == 0) {
+            const uint32_t kin0 = sh[2];
+            uint32_t above = 0;
+            int b = 255;
+            for (; b > 0; b--) { if (above + hist[b] >= kin0) break; above += hist[b]; }
+            sh[0] = (mhi << 8) | (uint32_t)b;
+        }
+        __syncthreads();
+    }
     const uint32_t bound = sh[0];
     const float inv_t = greedy ? 1.0f : __fdiv_rn(1.0f, temp);
     // pass 2: the survivors of the bound.  At most k threads hold a maximum >= bound, so barring heavy ties there are
@@ -175,6 +186,8 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
     } else {
     // more than 1024 elements at or above the bound (massive ties): exact selection by two histogram passes
     // pass 2b: histogram of the high byte over the survivors; find the byte holding the k-th largest
+    if (tid < 256) hist[tid] = 0;
+    __syncthreads();
     scan_row(row, P.n, [&](uint32_t key, uint32_t) { if (key >= bound) atomicAdd(&hist[key >> 8], 1u); });
     __syncthreads();
     if (tid == 0) {
@@ -237,16 +250,23 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
     __syncthreads();
     if (tid < k) e_s[tid] = expf_ref(__fsub_rn(srt_v[tid], srt_v[0]));
     __syncthreads();
+    // top-p (reference.rs:845-856): the ordered sums stay with thread 0, the divisions run one per thread
+    if (tid == 0) {
+        float denom = 0.0f;
+        for (uint32_t j = 0; j < k; j++) denom = __fadd_rn(e_s[j], denom);
+        shf[0] = denom;
+    }
+    __syncthreads();
+    if (tid < k) pn[tid] = __fdiv_rn(e_s[tid], shf[0]);
+    __syncthreads();
     if (tid == 0) {
         uint32_t keep = 1;
         if (!greedy) {
             float pp = P.top_p[seq];
             pp = (pp > 0.0f && pp < 1.0f) ? pp : 1.0f;
-            float denom = 0.0f;
-            for (uint32_t j = 0; j < k; j++) denom = __fadd_rn(e_s[j], denom);
             float cacc = 0.0f;
             for (uint32_t j = 0; j < k; j++) {
-                cacc = __fadd_rn(__fdiv_rn(e_s[j], denom), cacc);
+                cacc = __fadd_rn(pn[j], cacc);
                 keep = j + 1;
                 if (cacc >= pp) break;
             }
@@ -267,7 +287,7 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
                 float acc = 0.0f;
                 uint32_t pick = keep - 1;
                 for (uint32_t j = 0; j < keep; j++) {
-                    acc = __fadd_rn(__fdiv_rn(e_s[j], denom), acc);
+                    acc = __fadd_rn(pn[j], acc);
                     if (u < acc) { pick = j; break; }
                 }
                 P.pcg_out[r] = srt_idx[pick];
@@ -277,8 +297,14 @@ __global__ void __launch_bounds__(1024) topk_filter_kernel(const FilterParams P)
         }
         float z = 0.0f;
         for (uint32_t j = 0; j < keep; j++) z = __fadd_rn(e_s[j], z);
-        for (uint32_t j = 0; j < keep; j++) e_s[j] = __fdiv_rn(e_s[j], z);
+        shf[1] = z;
         sh[6] = keep;
+    }
+    __syncthreads();
+    if (tid < sh[6]) e_s[tid] = __fdiv_rn(e_s[tid], shf[1]);
+    __syncthreads();
+    if (tid == 0) {
+        const uint32_t keep = sh[6];
         if (P.out_n) P.out_n[oslot] = keep;
         if (P.sample_out) {
             uint32_t tok = srt_idx[0];
