@@ -52,6 +52,7 @@ struct wein_b200_engine {
     uint64_t bytes = 0;
     std::vector<void *> lin_state, conv_state, k_pool, v_pool;  // k/v pools: full layers then the MTP layer
     std::vector<float *> lin_log;      // per DeltaNet layer: update records of a round's positions (snapshot-lite verification)
+    float *gdn_kq = nullptr;           // k-hat / q-hat of a layer's tokens, [T, k_heads, 256]: scratch of the large-grid DeltaNet path
     void **d_state_ptrs = nullptr;     // device copies of lin_state / lin_log for the one-launch commit
     float **d_log_ptrs = nullptr;
     // per-slot device state
@@ -268,6 +269,7 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
         TRY(dalloc(e, &c, (size_t)S * e->rows_per_slot * conv_row, ("conv_state:" + std::to_string(i)).c_str(), false));
         e->lin_state.push_back(p); e->conv_state.push_back(c);
     }
+    if (e->n_lin) TRY(dalloc(e, &e->gdn_kq, (size_t)T * cfg->lin_k_heads * 256, "gdn_kq", false));
     if (e->P >= 3 && e->n_lin) {
         // from three positions per round on, a round logs its state updates instead of writing a snapshot per position
         for (uint32_t i = 0; i < e->n_lin; i++) {
@@ -501,7 +503,7 @@ static int32_t forward(Engine *e, uint32_t T, uint32_t n_spans, uint32_t max_cou
             // conv + SiLU + conv rows + l2 norms + gates + chain recurrence + gated norm: one launch per layer
             if (!(g_ablate & 4u)) TRY(wb_gdn_layer(e->proj, e->lpn, w.conv, e->conv_state[li], w.a_log, w.dt_bias, w.norm, e->lin_state[li], c.state_f32, e->normed,
                              e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base, n_spans, c.lin_k_heads, vh, c.l2_eps, c.rms_eps,
-                             lite ? e->lin_log[li] : nullptr, st));
+                             lite ? e->lin_log[li] : nullptr, e->gdn_kq, st));
             e->launches += 1;
             TRY(gemm(e, e->normed, w.out, e->o, T, H, e->vald, e->vald, H, st));
             li++;

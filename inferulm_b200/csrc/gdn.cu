@@ -285,6 +285,7 @@ struct GdnLayerParams {
     const uint32_t *row_start, *row_count, *in_row, *out_base;
     uint32_t n_rows, k_heads, v_heads;
     float l2_eps, rms_eps;
+    float *kq;                 // null: this kernel derives k-hat / q-hat itself.  Else [tokens, k_heads, 256] f32 from gdn_qk_kernel
     float *log;                // null: write a state snapshot per position.  Else [tokens, v_heads, GDN_LOG_W]: write only what a
                                // position did to the state (delta[128], k-hat[128], decay) and no state at all
 };
@@ -332,7 +333,13 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
         n_z[q2] = t < cnt ? P.proj[(size_t)(t0 + t) * P.ld + cd + h * VD + n_i] : (bf16_t)0;
     }
     // ---- conv + SiLU (reference.rs:476-506) and conv-state rows (reference.rs:511-562): one thread per channel
-    if (tid < 3 * KD) {
+    if (P.kq && tid < 2 * KD) {
+        // k-hat and q-hat of the span's tokens were made once per k-head by gdn_qk_kernel: stage them (256 floats per token)
+        for (uint32_t t = 0; t < cnt; t++) {
+            const float v = P.kq[((size_t)(t0 + t) * P.k_heads + kh) * 256 + tid];
+            if (tid < KD) kk_s[t][tid] = v; else qq_s[t][tid - KD] = v;
+        }
+    } else if (tid < 3 * KD) {
         const uint32_t part = tid / KD, i = tid % KD;
         const uint32_t ch = part == 0 ? kh * KD + i : (part == 1 ? keyd + kh * KD + i : 2 * keyd + h * VD + i);
         const bool owns_state = part == 2 || (h % group) == 0;   // q / k channels are shared by the v-heads of a k-head
@@ -372,6 +379,7 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
         }
     }
     __syncthreads();
+    if (!P.kq) {
     // ---- l2 norms of q and k (reference.rs:629-637): thread (t, which) sums 128 squares in order, two roundings per term
     if (tid < 2 * (int)cnt) {
         const bf16_t *src = (tid & 1) ? kc[tid >> 1] : qc[tid >> 1];
@@ -402,6 +410,7 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
         }
     }
     __syncthreads();
+    }   // !P.kq
     for (uint32_t i = 0; i < cnt; i++) {
         const float decay = gate_s[i][0], beta = gate_s[i][1];
         float kk[4], qq[4];
@@ -506,10 +515,84 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
     }
 }
 
+// k-hat and q-hat once per (span, k-head) instead of once per v-head: conv + SiLU of the head's q and k channels with their
+// conv-state rows, the two l2 norms and the scaling, for every token of the span.  Used in front of gdn_layer_kernel when
+// the grid is large: there the layer kernel is bound by the instructions and serial chains of its CTAs, and this part is
+// repeated by the v-heads that share a k-head.  Output kq [tokens, k_heads, 256] f32: k-hat then q-hat.  Same arithmetic.
+__global__ void __launch_bounds__(256) gdn_qk_kernel(const GdnLayerParams P) {
+    PDL_ENTRY();
+    constexpr int KD = 128, VD = 128, MAXT = 8;
+    __shared__ __align__(16) bf16_t qk[2][MAXT][KD];   // [0] q, [1] k
+    __shared__ float inv_s[MAXT][2];
+    const int tid = threadIdx.x;
+    const uint32_t r = blockIdx.x / P.k_heads, kh = blockIdx.x % P.k_heads;
+    const uint32_t t0 = P.row_start[r], cnt = min(P.row_count[r], (uint32_t)MAXT);
+    if (cnt == 0) return;
+    const size_t in_row = P.in_row[r], base = P.out_base[r];
+    const uint32_t keyd = P.k_heads * KD, vald = P.v_heads * VD, cd = 2 * keyd + vald;
+    {
+        const uint32_t part = tid / KD, i = tid % KD;
+        const uint32_t ch = part == 0 ? kh * KD + i : keyd + kh * KD + i;
+        const bf16_t *sp = P.conv_state + ((size_t)in_row * cd + ch) * 3;
+        bf16_t w0 = sp[0], w1 = sp[1], w2 = sp[2];
+        const float k0 = bf2f(P.conv_w[(size_t)ch * 4 + 0]), k1 = bf2f(P.conv_w[(size_t)ch * 4 + 1]),
+                    k2 = bf2f(P.conv_w[(size_t)ch * 4 + 2]), k3 = bf2f(P.conv_w[(size_t)ch * 4 + 3]);
+        bf16_t xs[MAXT];
+#pragma unroll
+        for (int t = 0; t < MAXT; t++) xs[t] = (uint32_t)t < cnt ? P.proj[(size_t)(t0 + t) * P.ld + ch] : (bf16_t)0;
+#pragma unroll
+        for (int t = 0; t < MAXT; t++) {
+            if ((uint32_t)t >= cnt) break;
+            bf16_t xv = xs[t];
+            float acc = 0.0f;
+            acc = __fadd_rn(__fmul_rn(bf2f(w0), k0), acc);
+            acc = __fadd_rn(__fmul_rn(bf2f(w1), k1), acc);
+            acc = __fadd_rn(__fmul_rn(bf2f(w2), k2), acc);
+            acc = __fadd_rn(__fmul_rn(bf2f(xv), k3), acc);
+            qk[part][t][i] = f2bf(silu_ref(rbf(acc)));
+            w0 = w1; w1 = w2; w2 = xv;
+            bf16_t *dp = P.conv_state + ((size_t)(base + t) * cd + ch) * 3;
+            dp[0] = w0; dp[1] = w1; dp[2] = w2;
+        }
+    }
+    __syncthreads();
+    if (tid < 2 * (int)cnt) {
+        const bf16_t *src = qk[tid & 1][tid >> 1];
+        float s = 0.0f;
+        uint4 raw[KD / 8];
+#pragma unroll
+        for (int v8 = 0; v8 < KD / 8; v8++) raw[v8] = *reinterpret_cast<const uint4 *>(src + v8 * 8);
+#pragma unroll
+        for (int v8 = 0; v8 < KD / 8; v8++) {
+            const uint32_t wv[4] = {raw[v8].x, raw[v8].y, raw[v8].z, raw[v8].w};
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                float x0 = __uint_as_float(wv[u] << 16), x1 = __uint_as_float(wv[u] & 0xffff0000u);
+                s = __fadd_rn(__fmul_rn(x0, x0), s);
+                s = __fadd_rn(__fmul_rn(x1, x1), s);
+            }
+        }
+        inv_s[tid >> 1][tid & 1] = __fdiv_rn(1.0f, sqrtf(__fadd_rn(s, P.l2_eps)));
+    }
+    __syncthreads();
+    const float kd_sqrt = sqrtf((float)KD);
+    for (uint32_t idx = tid; idx < cnt * 256; idx += 256) {
+        const uint32_t t = idx / 256, j = idx % 256;
+        float v;
+        if (j < (uint32_t)KD) v = __fmul_rn(bf2f(qk[1][t][j]), inv_s[t][1]);
+        else v = __fdiv_rn(__fmul_rn(bf2f(qk[0][t][j - KD]), inv_s[t][0]), kd_sqrt);
+        P.kq[((size_t)(t0 + t) * P.k_heads + kh) * 256 + j] = v;
+    }
+}
+
+// A/B switch: 0 keeps the one-launch layer at every grid size
+static bool g_gdn_split = true;
+extern "C" void wein_b200_gdn_split(uint32_t on) { g_gdn_split = on != 0; }
+
 int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log, const void *dt_bias,
                      const void *norm_w, void *state, uint32_t state_f32, void *out, const void *row_start, const void *row_count,
                      const void *in_row, const void *out_base, uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps,
-                     float rms_eps, void *log, cudaStream_t st) {
+                     float rms_eps, void *log, void *kq_scratch, cudaStream_t st) {
     WB_CHECK_ARG(proj && conv_w && conv_state && a_log && dt_bias && norm_w && state && out && row_start && row_count && in_row && out_base,
                  "gdn_layer: null pointer");
     WB_CHECK_ARG(k_heads > 0 && v_heads % k_heads == 0, "gdn_layer: v_heads %u must be a multiple of k_heads %u", v_heads, k_heads);
@@ -522,6 +605,13 @@ int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *co
     p.n_rows = n_rows; p.k_heads = k_heads; p.v_heads = v_heads; p.l2_eps = l2_eps; p.rms_eps = rms_eps; p.log = (float *)log;
     WB_CHECK_ARG(((uintptr_t)log & 15u) == 0, "gdn_layer: the update log must be 16-byte aligned");
     const bool big = (uint64_t)n_rows * v_heads >= 296;
+    if (big && kq_scratch && g_gdn_split) {
+        // large grid: k-hat / q-hat once per k-head in a launch of their own
+        WB_CHECK_ARG(((uintptr_t)kq_scratch & 15u) == 0, "gdn_layer: the k-hat / q-hat scratch must be 16-byte aligned");
+        p.kq = (float *)kq_scratch;
+        WB_LAUNCH((gdn_qk_kernel), n_rows * k_heads, 256, 0, st, p);
+        WB_LAUNCH_CHECK();
+    }
     if (state_f32) {
         if (big) WB_LAUNCH((gdn_layer_kernel<true, 2>), n_rows * v_heads, 512, 0, st, p);
         else WB_LAUNCH((gdn_layer_kernel<true, 1>), n_rows * v_heads, 512, 0, st, p);
@@ -539,7 +629,7 @@ extern "C" int32_t wein_b200_gdn_layer(const void *proj, uint32_t ld, const void
                                        const void *row_start, const void *row_count, const void *in_row, const void *out_base,
                                        uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps, float rms_eps, void *stream) {
     return wb_gdn_layer(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state_f32, out, row_start, row_count, in_row, out_base,
-                        n_rows, k_heads, v_heads, l2_eps, rms_eps, nullptr, (cudaStream_t)stream);
+                        n_rows, k_heads, v_heads, l2_eps, rms_eps, nullptr, nullptr, (cudaStream_t)stream);
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -623,7 +713,19 @@ extern "C" int32_t wein_b200_gdn_layer_lite(const void *proj, uint32_t ld, const
                                             void *stream) {
     WB_CHECK_ARG(log != nullptr, "gdn_layer_lite: the update log is required");
     return wb_gdn_layer(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, const_cast<void *>(state), state_f32, out, row_start, row_count,
-                        in_row, out_base, n_rows, k_heads, v_heads, l2_eps, rms_eps, log, (cudaStream_t)stream);
+                        in_row, out_base, n_rows, k_heads, v_heads, l2_eps, rms_eps, log, nullptr, (cudaStream_t)stream);
+}
+
+// The general form: optional update log (null = state snapshots) and optional scratch kq [tokens, k_heads, 256] f32
+// (16-byte aligned, sized by the caller for all tokens of the call).  With the scratch and at least 296 (span, v-head)
+// pairs, k-hat and q-hat are computed once per k-head by a launch of their own; results never depend on it.
+extern "C" int32_t wein_b200_gdn_layer_ws(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log,
+                                          const void *dt_bias, const void *norm_w, void *state, uint32_t state_f32, void *out,
+                                          const void *row_start, const void *row_count, const void *in_row, const void *out_base,
+                                          uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps, float rms_eps, void *log,
+                                          void *kq_scratch, void *stream) {
+    return wb_gdn_layer(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state_f32, out, row_start, row_count, in_row, out_base,
+                        n_rows, k_heads, v_heads, l2_eps, rms_eps, log, kq_scratch, (cudaStream_t)stream);
 }
 
 // Replays the records 0..accept_len[r] of span r on state row in_row[r] and stores row out_base[r] + accept_len[r], for

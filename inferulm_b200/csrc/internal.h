@@ -56,7 +56,8 @@ int32_t wb_rms_norm_gated_rows(const void *x, const void *z, uint32_t z_tok_stri
 int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log, const void *dt_bias,
                      const void *norm_w, void *state, uint32_t state_f32, void *out, const void *row_start, const void *row_count,
                      const void *in_row, const void *out_base, uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps,
-                     float rms_eps, void *log, cudaStream_t st);  // log != null: no state snapshots, one update record per position
+                     float rms_eps, void *log, void *kq_scratch, cudaStream_t st);  // log != null: no state snapshots, one update record per
+                     // position; kq_scratch != null ([tokens, k_heads, 256] f32): large grids compute k-hat / q-hat once per k-head
 int32_t wb_gdn_commit(void *const *states, const float *const *logs, uint32_t n_layers, uint32_t state_f32, const void *row_start,
                       const void *row_count, const void *in_row, const void *out_base, const void *accept_len, uint32_t n_rows,
                       uint32_t v_heads, cudaStream_t st);  // replays records 0..accept_len on row in_row, stores row out_base + accept_len

@@ -48,6 +48,8 @@ def load():
             _lib.wein_b200_engine_lite(C.c_uint32(int(os.environ["WEIN_B200_LITE"])))
         if os.environ.get("WEIN_B200_FAST_SAMPLED"):  # A/B switch: 0 = sampled rounds keep the skinny GEMM up to 32 rows
             _lib.wein_b200_engine_fast_sampled(C.c_uint32(int(os.environ["WEIN_B200_FAST_SAMPLED"])))
+        if os.environ.get("WEIN_B200_GDN_SPLIT"):  # A/B switch: 0 = one-launch DeltaNet layer at every batch size
+            _lib.wein_b200_gdn_split(C.c_uint32(int(os.environ["WEIN_B200_GDN_SPLIT"])))
         if os.environ.get("WEIN_B200_ABLATE"):  # profiling only: see wein_b200_engine_ablate
             _lib.wein_b200_engine_ablate(C.c_uint32(int(os.environ["WEIN_B200_ABLATE"])))
         if os.environ.get("WEIN_B200_PDL", "1") != "1":  # A/B switch: 0 = every kernel fully serialised, 3 = all but the GEMMs overlap

@@ -195,6 +195,15 @@ def gdn_layer_lite(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, 
                                           _stream()))
 
 
+def gdn_layer_ws(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state_f32, out, row_start, row_count, in_row, out_base,
+                 n_rows, k_heads, v_heads, l2_eps, rms_eps, log=None, kq_scratch=None):
+    """General form of gdn_layer: optional update log, optional k-hat / q-hat scratch [tokens, k_heads, 256] f32."""
+    check(load().wein_b200_gdn_layer_ws(_ptr(proj), U32(ld), _ptr(conv_w), _ptr(conv_state), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w),
+                                        _ptr(state), U32(state_f32), _ptr(out), _ptr(row_start), _ptr(row_count), _ptr(in_row),
+                                        _ptr(out_base), U32(n_rows), U32(k_heads), U32(v_heads), F32(l2_eps), F32(rms_eps), _ptr(log),
+                                        _ptr(kq_scratch), _stream()))
+
+
 def gdn_commit(states, logs, state_f32, row_start, row_count, in_row, out_base, accept_len, n_rows, v_heads):
     """Replays records 0..accept_len[r] on row in_row[r] of every layer's pool and stores row out_base[r] + accept_len[r].
     states / logs: lists of device tensors (one per layer)."""

@@ -336,3 +336,45 @@ def test_gdn_lite_commit_equals_snapshot(ops, state_f32):
             a = min(acc[s_], counts[s_] - 1)
             want[out_base[s_] + a] = snap[out_base[s_] + a]
         assert np.array_equal(got, want), trial
+
+
+@pytest.mark.parametrize("state_f32,lite", [(1, 0), (0, 1)])
+def test_gdn_layer_two_launch_path_equals_one_launch(ops, state_f32, lite):
+    """From 296 (span, v-head) pairs on and given a scratch, k-hat / q-hat are computed once per k-head by a launch of their
+    own: outputs, conv-state rows, state rows (or update records) are bit for bit those of the one-launch kernel."""
+    rs = np.random.default_rng(44)
+    kh, vh = 16, 32
+    keyd, vald = kh * 128, vh * 128
+    cd = 2 * keyd + vald
+    ld = cd + vald + 2 * vh
+    counts = [4, 1, 8, 3, 5, 4, 4, 2, 7, 4, 4, 6]
+    n = len(counts)
+    T = sum(counts)
+    row_start = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.uint32)
+    row_count = np.array(counts, np.uint32)
+    pool_rows = n * 10
+    in_row = (np.arange(n) * 10).astype(np.uint32)
+    out_base = (np.arange(n) * 10 + 1).astype(np.uint32)
+    proj = rand_bf16(rs, T * ld, 1.0)
+    conv_w = rand_bf16(rs, cd * 4, 0.5)
+    conv_state = rand_bf16(rs, pool_rows * cd * 3, 1.0)
+    a_log = (rs.standard_normal(vh) * 0.5).astype(np.float32)
+    dtb = rand_bf16(rs, vh, 0.5)
+    norm_w = (1 + 0.1 * rs.standard_normal(128)).astype(np.float32)
+    st16 = rand_bf16(rs, pool_rows * vh * 128 * 128, 0.3)
+    state = orc.bf16_to_f32(st16).copy() if state_f32 else st16
+    tabs = (dev(row_start), dev(row_count), dev(in_row), dev(out_base))
+    res = []
+    for scratch in (None, torch.zeros(T * kh * 256, dtype=torch.float32, device="cuda")):
+        cs, st = dev(conv_state), dev(state)
+        out = torch.zeros(T * vald, dtype=torch.int16, device="cuda")
+        log = torch.zeros(T * vh * 264, dtype=torch.float32, device="cuda") if lite else None
+        ops.gdn_layer_ws(dev(proj), ld, dev(conv_w), cs, dev(a_log), dev(dtb), dev(norm_w), st, state_f32, out, *tabs, n, kh, vh,
+                         1e-6, 1e-6, log, scratch)
+        res.append((u16(out), u16(cs), host(st, np.float32 if state_f32 else np.uint16).view(np.uint32 if state_f32 else np.uint16),
+                    host(log, np.float32).view(np.uint32) if lite else None))
+    assert np.array_equal(res[0][0], res[1][0])
+    assert np.array_equal(res[0][1], res[1][1])
+    assert np.array_equal(res[0][2], res[1][2])
+    if lite:
+        assert np.array_equal(res[0][3], res[1][3])
