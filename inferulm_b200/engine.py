@@ -264,3 +264,30 @@ class Engine:
                 bound = min(bound + k + 1, self.max_pos)
                 self.spec_step(slots, k, bound, use_graph)
                 rounds += 1
+
+    def generate_adaptive(self, slots, n_new, k_cap, use_graph=True):
+        """As generate(), with the draft length chosen per round by the reference's adaptive policy (spec_policy.SpecPolicy,
+        one state per slot; the batch drafts as far as its most optimistic slot).  The policy needs each round's accept
+        counts, so the counters are read back after every round: this is the host-paced mode the reference runs in.
+        Returns (rounds, list of the k used per round)."""
+        from .spec_policy import SpecPolicy, batch_k
+        slots = list(slots)
+        k_max = self.k_max
+        pol = {s: SpecPolicy(k_cap=k_cap, engine_k_max=k_max) for s in slots}
+        prev = {s: self.read(s, cap=1)[2] for s in slots}
+        ks = []
+        while True:
+            cnt = self.counts(slots)
+            bound = max(p for _, p in cnt)
+            for p in pol.values():
+                p.before_step()
+            k = batch_k(pol.values())
+            if n_new - min(c for c, _ in cnt) <= 0 or bound + k + 1 > self.max_pos:
+                return len(ks), ks
+            self.spec_step(slots, k, min(bound + k + 1, self.max_pos), use_graph)
+            ks.append(k)
+            for s in slots:
+                st = self.read(s, cap=1)[2]
+                pol[s].observe(st["accepted"] - prev[s]["accepted"], st["drafts"] - prev[s]["drafts"])
+                prev[s] = st
+

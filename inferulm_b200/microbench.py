@@ -1,6 +1,6 @@
 """Small, self-contained cases of the hot kernels: CUDA-event timing and the target of `ncu` captures.
 
-    python -m inferulm_b200.microbench gemm|gdn|attn|accept [--reps N]
+    python -m inferulm_b200.microbench gemm|gdn|gdn_lite|attn|accept|filter [--reps N] [--set NAME=INT ...]
 
 Each case holds well under 2 GB on the device, rotates its big operands through more than the 126 MB L2 so DRAM
 figures mean something, launches the kernel a handful of times (eagerly: one kernel per launch, easy to select with
@@ -38,15 +38,18 @@ def _time(fn, n_launch, reps):
     return best * 1e-3
 
 
-def case_gemm(reps, m=4, inter=9216, k=2560, n_mat=8):
-    """gate|up projection with the SwiGLU epilogue (the round's dominant launch), m = 4 rows, 8 matrices of 94 MB."""
+def case_gemm(reps, m=4, inter=9216, k=2560, n_mat=8, impl=0):
+    """gate|up projection with the SwiGLU epilogue (the round's dominant launch), m = 4 rows, 8 matrices of 94 MB.
+    impl=1 selects the TMA-staged kernel instead of the register-streaming one."""
+    ops.gemm_impl(impl)
     ws = [torch.randn(2 * inter, k, device="cuda").to(torch.bfloat16) * 0.02 for _ in range(n_mat)]
     a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     out = torch.empty(m, inter, dtype=torch.bfloat16, device="cuda")
     scratch = torch.zeros(ops.gemm_scratch_bytes(2 * inter) // 4, dtype=torch.int32, device="cuda")
     sec = _time(lambda i: ops.gemm_swiglu(a, ws[i], out, m, inter, k, scratch), n_mat, reps)
     byt = 2 * inter * k * 2 + m * k * 2 + m * inter * 2
-    return dict(kernel="wgemm_kernel (gate|up + SwiGLU)", m=m, n=2 * inter, k=k, us=sec * 1e6, bytes=byt, gbs=byt / sec / 1e9,
+    ops.gemm_impl(0)
+    return dict(kernel=("tgemm_kernel" if impl else "wgemm_kernel") + " (gate|up + SwiGLU)", m=m, n=2 * inter, k=k, us=sec * 1e6, bytes=byt, gbs=byt / sec / 1e9,
                 note="eager launches: the host launch gap is inside the time; bench.py times the same kernel by graph replay")
 
 
@@ -70,6 +73,37 @@ def case_gdn(reps, B=32, P=4, n_layers=2):
                 n_layers, reps)
     byt = B * VH * (1 + P) * 65536 + B * (1 + P) * CD * 3 * 2 + T * LD * 2 + T * VALD * 2
     return dict(kernel="gdn_layer_kernel<f32>", batch=B, positions=P, us=sec * 1e6, bytes=byt, gbs=byt / sec / 1e9)
+
+
+def case_gdn_lite(reps, B=32, P=4, n_layers=2, accept=3):
+    """Snapshot-lite pair: the layer kernel in log mode (state only read, 1 KiB update record per position and head) and
+    the commit kernel that replays records 0..accept on the input state and stores the one kept row, over n_layers layers."""
+    T = B * P
+    proj = torch.randn(T, LD, device="cuda").to(torch.bfloat16)
+    conv_w = (torch.randn(CD, 4, device="cuda") * 0.3).to(torch.bfloat16)
+    rows = B * 2 * P
+    a_log = torch.randn(VH, device="cuda")
+    dtb = torch.randn(VH, device="cuda").to(torch.bfloat16)
+    nw = torch.ones(128, device="cuda")
+    states = [torch.randn(rows * VH * 128 * 128, device="cuda") * 0.1 for _ in range(n_layers)]
+    convs = [torch.randn(rows * CD * 3, device="cuda").to(torch.bfloat16) for _ in range(n_layers)]
+    logs = [torch.zeros(T * VH * 264, device="cuda") for _ in range(n_layers)]
+    kq = torch.zeros(T * KH * 256, device="cuda")
+    out = torch.empty(T * VALD, dtype=torch.bfloat16, device="cuda")
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    rs, rc = i32([b * P for b in range(B)]), i32([P] * B)
+    ir, ob = i32([b * 2 * P for b in range(B)]), i32([b * 2 * P + P for b in range(B)])
+    acc = i32([accept] * B)
+    pf = proj.view(-1)
+    sec_layer = _time(lambda i: ops.gdn_layer_ws(pf, LD, conv_w, convs[i], a_log, dtb, nw, states[i], 1, out, rs, rc, ir, ob, B, KH, VH,
+                                                 1e-6, 1e-6, logs[i], kq), n_layers, reps)
+    sp, lp = ops.ptr_table(states), ops.ptr_table(logs)
+    sec_commit = _time(lambda i: ops.gdn_commit(sp, lp, 1, rs, rc, ir, ob, acc, B, VH), 1, reps)
+    byt_layer = B * VH * 65536 + B * P * VH * 1056 + B * (1 + P) * CD * 3 * 2 + T * LD * 2 + T * VALD * 2
+    byt_commit = n_layers * B * VH * (2 * 65536 + (accept + 1) * 1056)
+    return dict(kernel="gdn_qk_kernel + gdn_layer_kernel<f32> (log mode); gdn_commit_kernel<f32>", batch=B, positions=P, layer_us=sec_layer * 1e6,
+                layer_bytes=byt_layer, layer_gbs=byt_layer / sec_layer / 1e9, commit_layers=n_layers, commit_us=sec_commit * 1e6,
+                commit_bytes=byt_commit, commit_gbs=byt_commit / sec_commit / 1e9)
 
 
 def case_attn(reps, B=8, ctx=8192, P=4, n_pools=2, seg_pages=16):
@@ -113,7 +147,23 @@ def case_accept(reps, B=32, k=3, V=151936, n_buf=4):
     return dict(kernel="argmax_p1_kernel + accept_kernel", batch=B, k=k, vocab=V, us=sec * 1e6, bytes=byt, gbs=byt / sec / 1e9)
 
 
-CASES = dict(gemm=case_gemm, gdn=case_gdn, attn=case_attn, accept=case_accept)
+def case_filter(reps, S=128, V=151936, top_k=50, n_buf=3):
+    """Temperature / top-k / top-p filter of S bf16 logits rows (one CTA per row) into compact renormalised distributions."""
+    logits = [torch.randn(S * V, device="cuda").to(torch.bfloat16) for _ in range(n_buf)]
+    rows = torch.arange(S, dtype=torch.int32, device="cuda")
+    temp = torch.full((S,), 0.7, device="cuda")
+    tk = torch.full((S,), top_k, dtype=torch.int32, device="cuda")
+    tp = torch.full((S,), 0.9, device="cuda")
+    ids = torch.zeros(S * 64, dtype=torch.int32, device="cuda")
+    pr = torch.zeros(S * 64, device="cuda")
+    nn = torch.zeros(S, dtype=torch.int32, device="cuda")
+    sec = _time(lambda i: ops.topk_filter(logits[i], rows, rows, 1, temp, tk, tp, V, S, ids, pr, nn), n_buf, reps)
+    byt = 2 * S * V * 2   # two passes over the row
+    return dict(kernel="topk_filter_kernel", rows=S, vocab=V, top_k=top_k, us=sec * 1e6, bytes=byt, gbs=byt / sec / 1e9,
+                kept_mean=float(nn.float().mean()))
+
+
+CASES = dict(gemm=case_gemm, gdn=case_gdn, gdn_lite=case_gdn_lite, attn=case_attn, accept=case_accept, filter=case_filter)
 
 
 def main():

@@ -204,14 +204,21 @@ def gdn_layer_ws(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, st
                                         _ptr(kq_scratch), _stream()))
 
 
+def ptr_table(tensors):
+    """Device array of the tensors' device pointers (for entries that take an array of per-layer pointers)."""
+    return torch.tensor([t.data_ptr() for t in tensors], dtype=torch.int64, device="cuda")
+
+
 def gdn_commit(states, logs, state_f32, row_start, row_count, in_row, out_base, accept_len, n_rows, v_heads):
     """Replays records 0..accept_len[r] on row in_row[r] of every layer's pool and stores row out_base[r] + accept_len[r].
-    states / logs: lists of device tensors (one per layer)."""
-    sp = torch.tensor([t.data_ptr() for t in states], dtype=torch.int64, device="cuda")
-    lp = torch.tensor([t.data_ptr() for t in logs], dtype=torch.int64, device="cuda")
-    check(load().wein_b200_gdn_commit(_ptr(sp), _ptr(lp), U32(len(states)), U32(state_f32), _ptr(row_start), _ptr(row_count), _ptr(in_row),
+    states / logs: lists of device tensors (one per layer), or pointer tables made once with ptr_table()."""
+    own = not torch.is_tensor(states)
+    sp = ptr_table(states) if own else states
+    lp = ptr_table(logs) if not torch.is_tensor(logs) else logs
+    check(load().wein_b200_gdn_commit(_ptr(sp), _ptr(lp), U32(sp.numel()), U32(state_f32), _ptr(row_start), _ptr(row_count), _ptr(in_row),
                                       _ptr(out_base), _ptr(accept_len), U32(n_rows), U32(v_heads), _stream()))
-    torch.cuda.current_stream().synchronize()   # the pointer arrays above are temporaries
+    if own:
+        torch.cuda.current_stream().synchronize()   # the pointer tables above are temporaries
 
 
 def gemm_impl(impl=0):

@@ -227,3 +227,26 @@ def test_max_draft_length_k7(small_weights):
         outs.append(eng.read(0)[0][:30])
         eng.close()
     assert np.array_equal(outs[0], outs[1])
+
+
+def test_adaptive_draft_length_keeps_greedy_output(small_weights):
+    """Host-paced rounds with the adaptive policy choosing k: whatever lengths it picks (random weights make the MTP
+    head miss, so it falls to k = 1, switches drafting off and probes again), the tokens equal plain greedy decoding."""
+    from inferulm_b200.engine import Engine
+    w = small_weights
+    prompt = _prompt(31, w.shape.vocab, 9)
+    eng = Engine(w, max_seqs=1, k_max=3, max_pos=512)
+    eng.admit(0, 400)
+    eng.prefill([0], [prompt])
+    eng.generate([0], 40, 0)
+    want = eng.read(0)[0][:40]
+    eng.close()
+    eng = Engine(w, max_seqs=1, k_max=3, max_pos=512)
+    eng.admit(0, 400)
+    eng.prefill([0], [prompt])
+    rounds, ks = eng.generate_adaptive([0], 40, 3)
+    got = eng.read(0)[0][:40]
+    eng.close()
+    assert np.array_equal(got, want)
+    assert rounds == len(ks) and ks[0] == 2 and set(ks) <= {0, 1, 2, 3}
+    assert 0 in ks and 1 in ks            # drafting was switched off and probed again
