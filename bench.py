@@ -196,8 +196,7 @@ def run_ours(args, wl):
                 bound = min(bound + k + 1, max_pos)
                 eng.spec_step(slots, k, bound, use_graph=3 if mode == "e2e" else 1)
                 if mode == "e2e":
-                    for s in slots:
-                        eng.read(s, cap=k + 1)
+                    eng.read_round(len(slots))
             ev1.record(eng.stream)
         barrier()
         ms = ev0.elapsed_time(ev1)
@@ -309,7 +308,7 @@ def run_ours(args, wl):
                                 l2="per-round working set (7.9 GB of weights) exceeds L2; no flush needed", state="f32",
                                 draft_acceptance=acc, tokens_per_round=toks / max(1, args.steps) / B),
                     e2e=dict(value=toks_e2e_all / (ms_e2e_max * 1e-3), unit="tok/s", h2d_bytes_per_step=4 * B,
-                             d2h_bytes_per_step=B * (4 + 4 + 24 + 4 * (k + 1)), ms_per_step=ms_e2e_max / args.steps),
+                             d2h_bytes_per_step=B * 4 * (3 + k + 1), ms_per_step=ms_e2e_max / args.steps),
                     gpu_launches=launches,
                     roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
                                   traffic=(98.2e6 if fused and M == 4 else None),  # ncu dram read+write per launch, profiles/wgemm_gateup_swiglu_m4.md

@@ -280,6 +280,12 @@ int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, const uint32_t
 int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, uint32_t ctx_bound,
                                    uint32_t use_graph, void *stream);
 
+/* The readback of a round for the whole batch in one copy (the reference reads back its [B*P] argmax table once per step,
+ * forward_batch_mixed, qwen.rs:3453-3703): host_out [n, 3 + k_max + 1] u32 = per batch row of the most recent spec_step the
+ * accept length a, the position, the tokens emitted since admission, then the round's a + 1 tokens (other words 0xFFFFFFFF).
+ * Synchronises the stream. */
+int32_t wein_b200_engine_read_round(wein_b200_engine *e, uint32_t *host_out, uint32_t host_words, void *stream);
+
 /* Synchronises the stream and reads a slot: the most recent min(cap, emitted) tokens (oldest first), the number of
  * tokens emitted since admission (host_n_tokens), the position, and the counters of
  * spec_stats() (crates/wein-exec/src/qwen.rs:4257-4259): rounds, drafts, accepted. */

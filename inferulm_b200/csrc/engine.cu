@@ -79,6 +79,8 @@ struct wein_b200_engine {
     size_t h_stage_words = 0;
     std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint32_t, uint32_t>, cudaGraphExec_t> graphs;
     uint32_t launches = 0, last_launches = 0;
+    uint32_t last_n = 0, last_P = 0;     // shape of the most recent round (for read_round)
+    uint32_t *d_pack = nullptr, *h_pack = nullptr;   // per-round readback, device and pinned host: [max_seqs, 3 + P]
     // weight matrices in the order a round multiplies them (for the next-weights L2 prefetch); empty = no prefetch
     std::vector<std::pair<const void *, uint64_t>> chain;
     size_t chain_pos = 0;
@@ -159,6 +161,20 @@ __global__ void commit_kernel(const uint32_t *slots, SlotState S, const uint32_t
         S.stats[slot * 3 + 1] += k;
         S.stats[slot * 3 + 2] += a;
     }
+}
+
+// What the host reads back after a round, packed for one copy: per batch row [accept length, position, tokens emitted since
+// admission, the round's a+1 tokens (padded to P words)].  Stands in for the reference's per-step readback of its u32 [B*P]
+// argmax table (forward_batch_mixed, qwen.rs:3453-3703).
+__global__ void round_pack_kernel(const uint32_t *slots, SlotState S, const uint32_t *accept_len, const uint32_t *out_tokens,
+                                  uint32_t n, uint32_t P, uint32_t P_stride, uint32_t *out) {
+    PDL_ENTRY();
+    uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
+    if (b >= n) return;
+    const uint32_t slot = slots[b], a = min(accept_len[b], P - 1);
+    uint32_t *o = out + (size_t)b * (3 + P_stride);
+    o[0] = a; o[1] = S.pos[slot]; o[2] = S.out_count[slot];
+    for (uint32_t j = 0; j < P_stride; j++) o[3 + j] = (j <= a && j < P) ? out_tokens[b * P + j] : 0xffffffffu;
 }
 
 // Prefill chunk tables: span b holds cnt[b] prompt tokens of slot slots[b] (tokens concatenated in tok_in).
@@ -352,6 +368,8 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
     TRY(dalloc(e, &e->p_ids, (size_t)T * 64, "p_ids")); TRY(dalloc(e, &e->p_probs, (size_t)T * 64, "p_probs")); TRY(dalloc(e, &e->p_n, T, "p_n"));
     TRY(dalloc(e, &e->q_ids, (size_t)T * 64, "q_ids")); TRY(dalloc(e, &e->q_probs, (size_t)T * 64, "q_probs")); TRY(dalloc(e, &e->q_n, T, "q_n"));
     e->h_temp.assign(S, 0.0f);
+    TRY(dalloc(e, &e->d_pack, (size_t)S * (3 + e->P), "round_pack"));
+    CUDA_TRY(cudaMallocHost((void **)&e->h_pack, (size_t)S * (3 + e->P) * 4));
     e->h_stage_words = (size_t)T + 5 * S + 16;
     CUDA_TRY(cudaMallocHost((void **)&e->h_stage, e->h_stage_words * 4));
     CUDA_TRY(cudaDeviceSynchronize());
@@ -364,6 +382,7 @@ extern "C" void wein_b200_engine_destroy(wein_b200_engine *e) {
     for (auto &g : e->graphs) cudaGraphExecDestroy(g.second);
     for (void *p : e->allocs) cudaFree(p);
     if (e->h_stage) cudaFreeHost(e->h_stage);
+    if (e->h_pack) cudaFreeHost(e->h_pack);
     delete e;
 }
 extern "C" uint64_t wein_b200_engine_device_bytes(const wein_b200_engine *e) { return e ? e->bytes : 0; }
@@ -695,6 +714,7 @@ extern "C" int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, c
     WB_CHECK_ARG(!use_graph || st != nullptr, "spec_step: a CUDA graph cannot be captured on the default stream; pass a created stream");
     TRY(set_slots(e, n, host_slots, st, (use_graph & 2u) != 0));
     use_graph &= 1u;
+    e->last_n = n; e->last_P = k + 1;
     bool sampled = false;
     for (uint32_t i = 0; i < n; i++) sampled |= e->h_temp[host_slots[i]] > 0.0f;
     // the context bound only sizes the attention grid: round it up to a bucket so graphs are reused
@@ -798,6 +818,23 @@ extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, con
         WB_LAUNCH_CHECK();
     }
     CUDA_TRY(cudaStreamSynchronize(st));
+    return WB_OK;
+}
+
+// One readback for the whole batch of the most recent spec_step: host_out [n, 3 + k_max + 1] = per batch row the accept
+// length a, the position, the tokens emitted since admission, and the round's a+1 tokens (unused words 0xFFFFFFFF).  One small
+// kernel, one copy to pinned memory, one synchronisation.
+extern "C" int32_t wein_b200_engine_read_round(wein_b200_engine *e, uint32_t *host_out, uint32_t host_words, void *stream) {
+    WB_CHECK_ARG(e && host_out, "engine_read_round: null pointer");
+    WB_CHECK_ARG(e->last_n > 0, "engine_read_round: no round has run yet");
+    const uint32_t n = e->last_n, stride = 3 + e->P;
+    WB_CHECK_ARG(host_words >= n * stride, "engine_read_round: %u words given, %u needed", host_words, n * stride);
+    cudaStream_t st = (cudaStream_t)stream;
+    WB_LAUNCH((round_pack_kernel), (n + 127) / 128, 128, 0, st, e->d_slots, slot_state(e), e->d_accept_len, e->d_out_tokens, n, e->last_P, e->P, e->d_pack);
+    WB_LAUNCH_CHECK();
+    CUDA_TRY(cudaMemcpyAsync(e->h_pack, e->d_pack, (size_t)n * stride * 4, cudaMemcpyDeviceToHost, st));
+    CUDA_TRY(cudaStreamSynchronize(st));
+    memcpy(host_out, e->h_pack, (size_t)n * stride * 4);
     return WB_OK;
 }
 

@@ -221,6 +221,14 @@ class Engine:
                                              C.byref(pos), stats, self._stream()))
         return toks[: min(n.value, cap)].copy(), pos.value, dict(rounds=int(stats[0]), drafts=int(stats[1]), accepted=int(stats[2]))
 
+    def read_round(self, n):
+        """One readback for the batch of the most recent round: array [n, 3 + k_max + 1] of
+        (accept length, position, tokens emitted since admission, the round's tokens padded with 0xFFFFFFFF)."""
+        stride = 3 + self.k_max + 1
+        out = np.empty(n * stride, np.uint32)
+        check(self.lib.wein_b200_engine_read_round(self.h, out.ctypes.data_as(C.c_void_p), C.c_uint32(out.size), self._stream()))
+        return out.reshape(n, stride)
+
     def last_launches(self):
         return int(self.lib.wein_b200_engine_last_launches(self.h))
 

@@ -250,3 +250,27 @@ def test_adaptive_draft_length_keeps_greedy_output(small_weights):
     assert np.array_equal(got, want)
     assert rounds == len(ks) and ks[0] == 2 and set(ks) <= {0, 1, 2, 3}
     assert 0 in ks and 1 in ks            # drafting was switched off and probed again
+
+
+def test_read_round_matches_per_slot_reads(small_weights):
+    """The one-copy readback of a round agrees with the per-slot reads: accept length, position, emitted count, tokens."""
+    from inferulm_b200.engine import Engine
+    w = small_weights
+    eng = Engine(w, max_seqs=3, k_max=3, max_pos=256)
+    slots = [2, 0, 1]
+    for s in slots:
+        eng.admit(s, 200)
+    eng.prefill(slots, [_prompt(40 + s, w.shape.vocab, 5 + s) for s in slots])
+    before = {s: eng.read(s)[0] for s in slots}
+    for k in (3, 1, 0):
+        eng.spec_step(slots, k, 64)
+        rr = eng.read_round(len(slots))
+        assert rr.shape == (3, 3 + 4)
+        for b, s in enumerate(slots):
+            toks, pos, st = eng.read(s)
+            a = int(rr[b, 0])
+            assert a <= k and int(rr[b, 1]) == pos and int(rr[b, 2]) == len(toks)
+            assert np.array_equal(rr[b, 3:3 + a + 1], toks[len(before[s]):])
+            assert (rr[b, 3 + a + 1:] == 0xFFFFFFFF).all()
+            before[s] = toks
+    eng.close()
