@@ -24,6 +24,7 @@
 #include "internal.h"
 
 #define ATT_PAGE 16
+#define ATT_STAGES 2   // per-warp page pipeline depth.  Measured: 3 stages (200 KB per CTA) is no faster on its own and slows the whole round (batch 1: 2.71 -> 3.6 ms): the SM has to be re-split towards shared memory for this kernel and back to L1 for the GEMM that follows
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
@@ -63,8 +64,9 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
     constexpr int KS = HD / 16, ND = HD / 8, CH = HD / 8;       // k-steps of QK^T, d n-tiles of PV, 16-byte chunks per row
     constexpr int KL = 4;                                        // the four warps take the segment's pages round-robin
     constexpr int PAGE_BYTES = ATT_PAGE * HD * 2;
+    constexpr int NS = ATT_STAGES;                               // (K, V) page pairs per warp: NS - 1 of them in flight while one is used
     extern __shared__ __align__(128) unsigned char smem[];
-    // layout: Q tile [16][HD] | per warp: 2 stages x (K page, V page) ; merge area aliases the stages
+    // layout: Q tile [16][HD] | per warp: NS stages x (K page, V page) ; merge area aliases the stages
     unsigned char *q_s = smem;
     unsigned char *stage = smem + 16 * HD * 2;
     __shared__ int qpos_s[16];
@@ -100,7 +102,7 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
     __syncthreads();
 
     const int mi = 0, kl = w;
-    unsigned char *my_stage = stage + (size_t)w * 4 * PAGE_BYTES;
+    unsigned char *my_stage = stage + (size_t)w * NS * 2 * PAGE_BYTES;
     const uint32_t q_base = smem_u32(q_s), st_base = smem_u32(my_stage);
     const uint32_t *bt = P.block_table + (size_t)seq * P.bpr;
 
@@ -125,12 +127,15 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
 
     uint32_t pg = pg0 + kl;
     int buf = 0;
-    if (pg < pg1) load_page(pg, 0);
-    cp_async_commit();
-    for (; pg < pg1; pg += KL) {
-        if (pg + KL < pg1) load_page(pg + KL, buf ^ 1);
+#pragma unroll
+    for (int s0 = 0; s0 < NS - 1; s0++) {
+        if (pg + s0 * KL < pg1) load_page(pg + s0 * KL, s0);
         cp_async_commit();
-        cp_async_wait<1>();
+    }
+    for (; pg < pg1; pg += KL) {
+        if (pg + (NS - 1) * KL < pg1) load_page(pg + (NS - 1) * KL, (buf + NS - 1) % NS);
+        cp_async_commit();
+        cp_async_wait<NS - 1>();
         __syncwarp();
         const uint32_t k_s = st_base + buf * 2 * PAGE_BYTES, v_s = k_s + PAGE_BYTES;
         // S = Q K^T for 16 keys
@@ -189,7 +194,7 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
             mma16816(o[2 * nd + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
         }
         __syncwarp();
-        buf ^= 1;
+        buf = (buf + 1) % NS;
     }
     cp_async_wait<0>();
 #pragma unroll
@@ -272,7 +277,7 @@ __global__ void attn_combine_kernel(const AttnParams P) {
 
 template <int HD>
 static int32_t attn_launch(const AttnParams &p, cudaStream_t st) {
-    size_t smem = 16 * HD * 2 + 4 * 4 * (size_t)ATT_PAGE * HD * 2;
+    size_t smem = 16 * HD * 2 + 4 * ATT_STAGES * 2 * (size_t)ATT_PAGE * HD * 2;
     size_t merge = 16 * HD * 2 + 4 * 16 * (size_t)(HD + 4) * 4;
     if (smem < merge) smem = merge;
     static bool attr_done = false;
@@ -298,7 +303,7 @@ int32_t wb_attn_init(uint32_t head_dim) {
     (void)p;
     size_t smem;
     cudaError_t e = cudaSuccess;
-    auto bytes = [](size_t hd) { size_t a = 16 * hd * 2 + 4 * 4 * (size_t)ATT_PAGE * hd * 2, b = 16 * hd * 2 + 4 * 16 * (hd + 4) * 4; return a > b ? a : b; };
+    auto bytes = [](size_t hd) { size_t a = 16 * hd * 2 + 4 * ATT_STAGES * 2 * (size_t)ATT_PAGE * hd * 2, b = 16 * hd * 2 + 4 * 16 * (hd + 4) * 4; return a > b ? a : b; };
     smem = bytes(head_dim);
     if (head_dim == 256) e = cudaFuncSetAttribute(attn_verify_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     else if (head_dim == 128) e = cudaFuncSetAttribute(attn_verify_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);

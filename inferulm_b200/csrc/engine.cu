@@ -263,13 +263,22 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
     e->lpn = e->cd + e->vald + 2 * cfg->lin_v_heads;
     e->fpn = 2 * cfg->q_heads * cfg->head_dim + 2 * cfg->kv_heads * cfg->head_dim;
     e->rows_per_slot = 2 * e->P;
-    // pages per attention segment: fixed per engine (it fixes the summation order), about 16 segments at the longest context --
-    // short contexts need many small CTAs, long ones amortise the per-CTA merge (measured: 32K tokens, 128 pages: 4.7 TB/s)
+    // Pages per attention segment: fixed per engine, because it fixes the summation order (two engines agree bit for bit only
+    // with the same value: pin cfg.attn_seg_pages to compare engines of different capacity).  A CTA reduces one segment of
+    // one (chain, kv head): short segments cost a launch, a Q stage and a merge per 128 KB of KV, long ones leave SMs idle.
+    // Aim at ~3 CTAs per SM when every slot is at the longest context (measured, 32 chains x 2K tokens: 16 pages 105 us,
+    // 64 pages 78 us; 8 chains x 32K tokens: 128 pages 214 us, 256 pages 199 us = 5.4 TB/s).
     e->seg_pages = cfg->attn_seg_pages;
     if (!e->seg_pages) {
-        uint32_t want = e->bpr / 16;
+        int dev = 0, sms = 148;
+        if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        cudaGetLastError();
+        const uint32_t pairs = cfg->max_seqs * cfg->kv_heads;
+        uint32_t segs = (3u * (uint32_t)sms + pairs - 1) / pairs;
+        if (segs < 1) segs = 1;
+        const uint32_t want = (e->bpr + segs - 1) / segs;
         e->seg_pages = 4;
-        while (e->seg_pages < want && e->seg_pages < 128) e->seg_pages *= 2;
+        while (e->seg_pages < want && e->seg_pages < 128) e->seg_pages *= 2;   // 256 pages: faster alone, slower in a round (1.7 waves)
     }
     for (uint32_t l = 0; l < cfg->n_layers; l++) (cfg->layer_is_full[l] ? e->n_full : e->n_lin)++;
     *out = e;
