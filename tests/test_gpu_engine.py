@@ -205,6 +205,8 @@ def test_engine_rejects_bad_arguments(small_weights):
         eng.admit(0, 32, temp=1.0, top_k=0)    # whole-vocabulary sampling is not built
     eng.admit(0, 64)
     with pytest.raises(WeinB200Error):
+        eng.read_round(1)                      # no round has run yet
+    with pytest.raises(WeinB200Error):
         eng.spec_step([0], 5, 64)              # k > k_max
     with pytest.raises(WeinB200Error):
         eng.spec_step([0, 0], 1, 64)           # slot listed twice

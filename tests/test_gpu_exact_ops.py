@@ -378,3 +378,24 @@ def test_gdn_layer_two_launch_path_equals_one_launch(ops, state_f32, lite):
     assert np.array_equal(res[0][2], res[1][2])
     if lite:
         assert np.array_equal(res[0][3], res[1][3])
+
+
+def test_snapshot_lite_entries_reject_bad_arguments_and_accept_empty_calls(ops):
+    """gdn_layer_lite needs its log, logs must be 16-byte aligned, gdn_commit needs its tables; empty calls succeed."""
+    from inferulm_b200.lib import WeinB200Error
+    z16 = torch.zeros(4096, dtype=torch.int16, device="cuda")
+    z32 = torch.zeros(64, dtype=torch.int32, device="cuda")
+    zf = torch.zeros(4096, dtype=torch.float32, device="cuda")
+    args = (z16, 64, z16, z16, zf, z16, zf, zf, 1, z16, z32, z32, z32, z32)
+    with pytest.raises(WeinB200Error):
+        ops.gdn_layer_lite(*args, 1, 16, 32, 1e-6, 1e-6, None)
+    with pytest.raises(WeinB200Error):
+        ops.gdn_layer_lite(*args, 1, 16, 32, 1e-6, 1e-6, zf[1:])          # misaligned log
+    with pytest.raises(WeinB200Error):
+        ops.gdn_layer_ws(*args, 1, 15, 32, 1e-6, 1e-6)                    # v_heads not a multiple of k_heads
+    ops.gdn_layer_lite(*args, 0, 16, 32, 1e-6, 1e-6, zf)                   # no spans: nothing launched
+    ops.gdn_commit([zf], [zf], 1, z32, z32, z32, z32, z32, 0, 32)          # no spans
+    tbl = ops.ptr_table([zf])
+    with pytest.raises(WeinB200Error):
+        ops.gdn_commit(tbl, tbl, 1, None, z32, z32, z32, z32, 1, 32)       # missing table
+    torch.cuda.synchronize()
