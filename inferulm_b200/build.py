@@ -2,6 +2,7 @@
 
     python -m inferulm_b200.build            # build if sources are newer than the library
     python -m inferulm_b200.build --force
+    python -m inferulm_b200.build --trace    # diagnostic twin libwein_b200_trace.so with kernel-start time stamps (see trace.py)
 """
 import os
 import subprocess
@@ -41,7 +42,15 @@ def _headers():
         os.path.join(os.path.dirname(HERE), "include", "wein_b200.h")]
 
 
-def build(force=False, verbose=False):
+LIB_TRACE = os.path.join(HERE, "libwein_b200_trace.so")
+
+
+def build(force=False, verbose=False, trace=False):
+    lib, objdir, defs = (LIB_TRACE, OBJ + "_trace", ["-DWB_TRACE"]) if trace else (LIB, OBJ, [])
+    return _build(lib, objdir, defs, force, verbose)
+
+
+def _build(LIB, OBJ, defs, force, verbose):
     os.makedirs(OBJ, exist_ok=True)
     hdr_m = max((os.path.getmtime(h) for h in _headers() if os.path.exists(h)), default=0)
     objs, changed = [], False
@@ -53,7 +62,7 @@ def build(force=False, verbose=False):
         obj = os.path.join(OBJ, src.replace(".cu", ".o"))
         objs.append(obj)
         if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(path), hdr_m):
-            cmd = [_nvcc()] + ARCH + COMMON + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", "-o", obj, path]
+            cmd = [_nvcc()] + ARCH + COMMON + defs + extra + (["-Xptxas", "-v"] if verbose else []) + ["-c", "-o", obj, path]
             procs.append((src, subprocess.Popen(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)))
             changed = True
     for src, p in procs:
@@ -71,4 +80,4 @@ def build(force=False, verbose=False):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))

@@ -376,3 +376,5 @@ int32_t wein_b200_attn_verify(const void *q, const void *k_cache, const void *v_
 }
 
 }  // extern "C"
+
+WB_TRACE_SETTER(attn)   // diagnostic builds only (see common.cuh); expands to nothing otherwise

@@ -42,3 +42,5 @@ void wein_b200_set_pdl(uint32_t on) { g_wb_pdl = (on & 1u) != 0; g_wb_pdl_gemm =
 // A/B switch, to be called before the first launch: shared-memory carve-out preference of every kernel, -1 = driver default
 void wein_b200_set_carveout(int32_t percent) { g_carveout = percent; }
 }
+
+WB_TRACE_SETTER(capi)   // diagnostic builds only (see common.cuh); expands to nothing otherwise

@@ -869,3 +869,5 @@ extern "C" int32_t wein_b200_engine_read(wein_b200_engine *e, uint32_t slot, uin
     }
     return WB_OK;
 }
+
+WB_TRACE_SETTER(engine)   // diagnostic builds only (see common.cuh); expands to nothing otherwise

@@ -184,3 +184,5 @@ int32_t wb_rms_norm_gated_rows(const void *x, const void *z, uint32_t z_tok_stri
     WB_LAUNCH_CHECK();
     return WB_OK;
 }
+
+WB_TRACE_SETTER(fused_glue)   // diagnostic builds only (see common.cuh); expands to nothing otherwise

@@ -736,3 +736,5 @@ extern "C" int32_t wein_b200_gdn_commit(const void *states, const void *logs, ui
     return wb_gdn_commit((void *const *)states, (const float *const *)logs, n_layers, state_f32, row_start, row_count, in_row, out_base,
                          accept_len, n_rows, v_heads, (cudaStream_t)stream);
 }
+
+WB_TRACE_SETTER(gdn)   // diagnostic builds only (see common.cuh); expands to nothing otherwise

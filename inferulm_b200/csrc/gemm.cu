@@ -495,3 +495,5 @@ extern "C" int32_t wein_b200_gemm_swiglu(const void *a, const void *w_gate_up, v
                                          void *scratch, uint64_t scratch_bytes, void *stream) {
     return wb_gemm_swiglu(a, w_gate_up, out, m, inter, k, k, inter, scratch, scratch_bytes, (cudaStream_t)stream);
 }
+
+WB_TRACE_SETTER(gemm)   // diagnostic builds only (see common.cuh); expands to nothing otherwise

@@ -341,3 +341,5 @@ extern "C" int32_t wein_b200_gemm_stream_timeouts(uint32_t *out) {
     if (out) *out = v;
     return WB_OK;
 }
+
+WB_TRACE_SETTER(gemm_stream)   // diagnostic builds only (see common.cuh); expands to nothing otherwise

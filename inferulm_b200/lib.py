@@ -3,7 +3,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libwein_b200.so")
+# WEIN_B200_TRACE=1 loads the diagnostic twin built by `python -m inferulm_b200.build --trace` (kernel-start time stamps)
+LIB_PATH = os.path.join(HERE, "libwein_b200_trace.so" if os.environ.get("WEIN_B200_TRACE") == "1" else "libwein_b200.so")
 
 
 class LibraryMissing(RuntimeError):
