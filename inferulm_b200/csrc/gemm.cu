@@ -51,6 +51,7 @@ struct WgemmParams {
     uint32_t m, n, k, lda, ldc, ksplit, kslice;  // kslice: k elements per CTA slice (multiple of 32)
     const void *next_w;   // weights of the stream's next product (or null): their head is pulled into L2 by this kernel's
     uint32_t next_lines;  //   CTAs as they finish, so HBM keeps streaming through the kernels in between; count of 128-byte lines
+    uint32_t pf_row_bytes; // per weight row of a warp's slab: how far ahead of the register window the pre-wait L2 prefetch reaches
     uint32_t swiglu;      // 1: W = [gate; up] (n = 2*inter rows); tile rows 0-7 are gate rows, 8-15 the matching up rows, and
                           //    the epilogue writes bf16(bf16(silu(bf16 g)) * bf16 u) into C[m, inter]
 };
@@ -113,7 +114,7 @@ __global__ void __launch_bounds__(256, (MT == 1 && UNR <= 4) ? 3 : 2) wgemm_kern
         if (P.swiglu) { uint32_t j = min(tile * 8 + (row & 7), half_n - 1); rr = (row < 8) ? j : half_n + j; }
         else rr = min(tile * 16 + row, P.n - 1);
         const char *base = reinterpret_cast<const char *>(P.W + (size_t)rr * P.k + (size_t)b_lo * 32);
-        const uint32_t bytes = (b_hi - b_lo) * 64;
+        const uint32_t bytes = min((b_hi - b_lo) * 64, P.pf_row_bytes);
         if (tile_ok)
             for (uint32_t off = (lane & 1) * 128 + UNR * 64; off < bytes; off += 256)
                 asm volatile("prefetch.global.L2 [%0];" ::"l"(base + off));
@@ -222,7 +223,13 @@ __global__ void __launch_bounds__(256, (MT == 1 && UNR <= 4) ? 3 : 2) wgemm_kern
 // Decomposition of a product: KW warps per row tile inside a CTA, ksplit k slices over CTAs.  It depends on (n, k)
 // only -- never on m -- so a row's accumulation order is the same at every batch size.
 struct WgemmPlan { uint32_t kw, ksplit; };
-static uint32_t g_force_kw = 0, g_force_ks = 0, g_force_unr = 0;
+// Reach of the pre-wait L2 prefetch per weight row (bytes from the start of the warp's slab; the register window covers
+// the first UNR x 64).  Measured on the captured round: prefetching the whole slab floods the memory system while the small
+// kernel in front of this GEMM (a residual norm of 40 KB) is on the critical path -- its interval grows from ~2.4 to 4.8 us.
+// Whole slab 2.714 ms per round, nothing 2.705, 512 B 2.663, 640-768 B 2.612-2.622, 1024 B 2.66, 2048 B 2.68.  Loading fewer slots
+// of the register window before the wait was worse (none 2.78, half 2.64).
+static uint32_t g_force_kw = 0, g_force_ks = 0, g_force_unr = 0, g_pf_row_bytes = 768;
+extern "C" void wein_b200_gemm_prefetch_row_bytes(uint32_t b) { g_pf_row_bytes = b; }
 extern "C" void wein_b200_gemm_tune(uint32_t kw, uint32_t ksplit, uint32_t unr) { g_force_kw = kw; g_force_ks = ksplit; g_force_unr = unr; }
 
 static WgemmPlan plan_for(uint32_t n_tiles, uint32_t k, bool has_scratch) {
@@ -293,7 +300,7 @@ static int32_t wgemm_launch(const void *a, const void *w, void *c, uint32_t m, u
     }
     WgemmParams p{};
     p.A = (const bf16_t *)a; p.W = (const bf16_t *)w; p.C = (bf16_t *)c;
-    p.m = m; p.n = n; p.k = k; p.lda = lda; p.ldc = ldc; p.swiglu = swiglu ? 1 : 0;
+    p.m = m; p.n = n; p.k = k; p.lda = lda; p.ldc = ldc; p.swiglu = swiglu ? 1 : 0; p.pf_row_bytes = g_pf_row_bytes;
     if (t_next_w && g_prefetch_cap) {
         uint64_t nbytes = t_next_bytes < g_prefetch_cap ? t_next_bytes : g_prefetch_cap;
         p.next_w = t_next_w; p.next_lines = (uint32_t)(nbytes / 128);

@@ -51,6 +51,8 @@ def load():
             _lib.wein_b200_engine_fast_sampled(C.c_uint32(int(os.environ["WEIN_B200_FAST_SAMPLED"])))
         if os.environ.get("WEIN_B200_GDN_SPLIT"):  # A/B switch: 0 = one-launch DeltaNet layer at every batch size
             _lib.wein_b200_gdn_split(C.c_uint32(int(os.environ["WEIN_B200_GDN_SPLIT"])))
+        if os.environ.get("WEIN_B200_PF_ROW_BYTES"):  # A/B switch: reach of the skinny GEMM's pre-wait L2 prefetch per weight row
+            _lib.wein_b200_gemm_prefetch_row_bytes(C.c_uint32(int(os.environ["WEIN_B200_PF_ROW_BYTES"])))
         if os.environ.get("WEIN_B200_ABLATE"):  # profiling only: see wein_b200_engine_ablate
             _lib.wein_b200_engine_ablate(C.c_uint32(int(os.environ["WEIN_B200_ABLATE"])))
         if os.environ.get("WEIN_B200_PDL", "1") != "1":  # A/B switch: 0 = every kernel fully serialised, 3 = all but the GEMMs overlap
