@@ -6,6 +6,7 @@ sequences, prefill, run speculative rounds, read tokens and counters.  torch is
 used only to own device memory (the synthetic weights) and the CUDA stream.
 """
 import ctypes as C
+import os
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -162,7 +163,8 @@ class Engine:
         self.bpr = (max_pos + 15) // 16
         self.n_pages = n_pages if n_pages is not None else max_seqs * self.bpr
         cfg.has_mtp, cfg.max_seqs, cfg.k_max, cfg.max_pos, cfg.n_pages = int(s.has_mtp), max_seqs, k_max, max_pos, self.n_pages
-        cfg.state_f32, cfg.attn_seg_pages = int(state_f32), attn_seg_pages
+        # A/B switch for measurements: WEIN_B200_SEG_PAGES overrides the automatic attention segment size
+        cfg.state_f32, cfg.attn_seg_pages = int(state_f32), attn_seg_pages or int(os.environ.get("WEIN_B200_SEG_PAGES", "0"))
         self.cfg, self.max_seqs, self.k_max, self.max_pos = cfg, max_seqs, k_max, max_pos
         # rounds are replayed as CUDA graphs, which cannot be captured on the legacy default stream
         self.stream = torch.cuda.Stream()
