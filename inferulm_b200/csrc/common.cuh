@@ -123,27 +123,37 @@ __device__ __forceinline__ float block_sum_tree(float v, float *smem /* >= 33 fl
 // Because a kernel's lifetime now overlaps its producer's, data written by earlier kernels must never be read through the
 // non-coherent path: no __ldg and no `const __restrict__` on such pointers (only weights use ld.global.nc).
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
+// Identity of a call site for the diagnostic build: hash of the source file's base name, and the line
+__host__ __device__ constexpr unsigned int wb_file_id(const char *path) {
+    unsigned int h = 2166136261u;
+    const char *base = path;
+    for (const char *p = path; *p; p++) if (*p == '/') base = p + 1;
+    for (const char *p = base; *p; p++) h = (h ^ (unsigned char)*p) * 16777619u;
+    return h;
+}
 #ifdef WB_TRACE
 // Diagnostic build (python -m inferulm_b200.build --trace): block 0 / thread 0 of every kernel records the global timer when
-// its dependency wait returns, in the order kernels become runnable.  In a captured round every kernel waits for its
-// predecessor, so the difference between consecutive stamps is what each kernel adds to the round's critical path
-// (inferulm_b200/trace.py prints it).  The buffer pointer is a per-translation-unit copy set through WB_TRACE_SETTER.
-static __device__ unsigned long long *wb_trace_buf;   // [0] = count, then the stamps
-__device__ __forceinline__ void pdl_wait() {
+// its dependency wait returns, with the call site of the wait (which identifies the kernel), in the order kernels become
+// runnable.  In a captured round every kernel waits for its predecessor, so the difference between consecutive stamps is
+// what each kernel adds to the round's critical path (inferulm_b200/trace.py prints it).  The buffer pointer is a
+// per-translation-unit copy set through WB_TRACE_SETTER.
+static __device__ unsigned long long *wb_trace_buf;   // [0] = count, then (time, file id << 32 | line) pairs
+__device__ __forceinline__ void pdl_wait_at(unsigned int file_id, unsigned int line) {
     asm volatile("griddepcontrol.wait;" ::: "memory");
     if ((threadIdx.x | blockIdx.x | blockIdx.y | blockIdx.z) == 0 && wb_trace_buf) {
         unsigned long long t;
         asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
         const unsigned int i = atomicAdd(reinterpret_cast<unsigned int *>(wb_trace_buf), 1u);
-        if (i < 16000u) wb_trace_buf[1 + i] = t;
+        if (i < 30000u) { wb_trace_buf[1 + 2 * i] = t; wb_trace_buf[2 + 2 * i] = ((unsigned long long)file_id << 32) | line; }
     }
 }
 #define WB_TRACE_SETTER(name) \
     extern "C" void wb_trace_set_##name(unsigned long long *p) { cudaMemcpyToSymbol(wb_trace_buf, &p, sizeof p); }
 #else
-__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait_at(unsigned int, unsigned int) { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 #define WB_TRACE_SETTER(name)
 #endif
+#define pdl_wait() do { constexpr unsigned int wb_fid_ = wb_file_id(__FILE__); pdl_wait_at(wb_fid_, __LINE__); } while (0)
 #define PDL_ENTRY() do { pdl_trigger(); pdl_wait(); } while (0)
 
 // Host-side launch helper: every kernel goes through cudaLaunchKernelEx so the attribute can be switched globally.
