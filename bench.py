@@ -1,15 +1,18 @@
 """Benchmark of the MTP draft -> verify -> accept round on B200.
 
-    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3]
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload c2|c3|c4] [--only-headline]
 
 A "step" is one speculative round (k draft forwards, one verify forward over k+1 positions, device acceptance and
-commit) over one batch of sequences.  Workload c2 (default, BASELINE config 1): synthetic Qwen3.5-4B-shape hybrid
-decoder, random-init bf16 weights N(0, 0.02), greedy MTP k = 3, batch 1, 1024-token uniform-random prompt.  With
-N > 1 every rank runs its own sequences on its own GPU (no collective on the data path): weak scaling.
+commit) over one batch of sequences.  The headline workload c2 is the second configuration of BASELINE.json: synthetic
+Qwen3.5-4B-shape hybrid decoder, random-init bf16 weights N(0, 0.02), greedy MTP k = 3, batch 1, 1024-token uniform-random
+prompt.  With N > 1 every rank runs its own sequences on its own GPU (no collective on the data path): weak scaling.
 
-One JSON line is printed by rank 0.  `value` = emitted ("accepted") tokens per second over the K timed rounds,
-replayed as CUDA graphs with all inputs resident; `e2e` = the same rounds driven through the public step API with the
-per-round host inputs uploaded from pinned memory and the per-round results (tokens, accept counters) read back.
+One JSON line is printed by rank 0.  `value` = emitted ("accepted") tokens per second over the K timed rounds, replayed as
+CUDA graphs with all inputs resident; `e2e` = the same rounds driven through the public step API with the per-round host
+inputs uploaded from pinned memory and the per-round results (tokens, accept counters) read back.  The same line carries,
+as objects, the other configurations the metric is quoted on: `bs32` (batch 32, sampled acceptance), `c4` (batch 8,
+32,768-token context, k = 4, acceptance imposed by drafts drawn from target logits + N(0, sigma) noise) and `c5` (256
+sequences of log-uniform prompt length sharded over the ranks by longest-first bin packing: strong scaling of a fixed job).
 """
 import argparse
 import json
@@ -24,15 +27,17 @@ import numpy as np
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+MODEL = "Qwen3.5-4B-shape hybrid decoder (24 GDN + 8 GQA, hidden 2560, FFN 9216, vocab 151936)"
 WORKLOADS = {
-    # name: batch, k, prompt, temp, top_k, top_p
-    "c2": dict(batch=1, k=3, prompt=1024, temp=0.0, top_k=0, top_p=1.0,
-               desc="Qwen3.5-4B-shape hybrid decoder (24 GDN + 8 GQA, hidden 2560, FFN 9216, vocab 151936), greedy MTP k=3, batch 1, 1024-token prompt"),
-    "c4": dict(batch=8, k=4, prompt=32768, temp=0.0, top_k=0, top_p=1.0,
-               desc="same model, long context: batch 8, 32768-token prompts (paged bf16 KV, 16-token pages) + f32 recurrent state, greedy k=4"),
+    "c2": dict(batch=1, k=3, prompt=1024, temp=0.0, top_k=0, top_p=1.0, desc=MODEL + ", greedy MTP k=3, batch 1, 1024-token prompt"),
     "c3": dict(batch=32, k=3, prompt=2048, temp=0.7, top_k=50, top_p=0.9,
                desc="same model, batch 32, sampled acceptance T=0.7 top-k 50 top-p 0.9, k=3, 2048-token prompts"),
+    "c4": dict(batch=8, k=4, prompt=32768, temp=0.0, top_k=0, top_p=1.0,
+               desc="same model, long context: batch 8, 32768-token paged bf16 KV (16-token pages) + f32 recurrent state, k=4"),
 }
+# ncu capture of the headline's dominant launch (wgemm_kernel, gate|up + SwiGLU, m = 4): dram__bytes_read.sum + dram__bytes_write.sum
+# per launch as recorded in the committed capture summary of that kernel and shape; null for shapes without a capture
+NCU_TRAFFIC = {("wgemm", 4): 97.6e6}
 
 
 def peaks():
@@ -74,182 +79,234 @@ class ClockSampler(threading.Thread):
                     samples=len(self.rows))
 
 
-# ------------------------------------------------------------------------------------------------ CPU baseline (oracle)
-def cpu_unit(threads, shape, P=4, ctx=512):
-    """Times the reference's CPU kernels (oracle port) on the BASELINE unit: one gated-DeltaNet layer over P positions,
-    one GQA layer against a ctx-token paged KV, greedy acceptance over P x vocab logits, and one gate|up projection
-    (f64-accumulate GEMM) as the GEMM sample.  Returns seconds per piece."""
-    from oracle import oracle as orc
-    rs = np.random.default_rng(0)
-    kh, vh, kd, vd = shape.lin_k_heads, shape.lin_v_heads, shape.lin_k_dim, shape.lin_v_dim
-    r16 = lambda n, sc=1.0: orc.f32_to_bf16((rs.standard_normal(n) * sc).astype(np.float32))
-    q, k, v = r16(P * kh * kd), r16(P * kh * kd), r16(P * vh * vd)
-    a, b = r16(P * vh), r16(P * vh)
-    a_log, dtb = rs.standard_normal(vh).astype(np.float32) * 0.5, r16(vh, 0.5)
-    state = (rs.standard_normal((P + 1) * vh * vd * kd) * 0.1).astype(np.float32)
-    t = {}
-    t0 = time.perf_counter()
-    orc.deltanet(q, k, v, a, b, a_log, dtb, state, [0], [P], [0], kh, vh, kd, vd, 1e-6, [1], state_mode=1, threads=threads)
-    t["gdn_layer"] = time.perf_counter() - t0
-    qh, kvh, hd = shape.q_heads, shape.kv_heads, shape.head_dim
-    pages = (ctx + 15) // 16
-    kc, vc = r16(pages * 16 * kvh * hd), r16(pages * 16 * kvh * hd)
-    qq = r16(P * qh * hd)
-    t0 = time.perf_counter()
-    orc.paged_attn(qq, kc, vc, rs.permutation(pages).astype(np.uint32), [0] * P, list(range(ctx - P, ctx)), 1.0 / 16.0, pages, 16, qh, kvh, hd,
-                   threads=threads)
-    t["gqa_layer"] = time.perf_counter() - t0
-    lg = r16(P * shape.vocab)
-    t0 = time.perf_counter()
-    tg = orc.argmax_rows(lg, np.arange(P), shape.vocab, threads=threads)
-    orc.accept_greedy(tg[:P - 1], tg)
-    t["accept"] = time.perf_counter() - t0
-    n, kk = 2 * shape.inter // 8, shape.hidden      # one eighth of a gate|up projection
-    A, W = r16(P * kk), r16(n * kk, 0.02)
-    t0 = time.perf_counter()
-    orc.gemm_wt_bf16(A, W, P, n, kk, threads=threads)
-    t["gemm_sample"] = time.perf_counter() - t0
-    t["gemm_sample_macs"] = P * n * kk
-    return t
+# ------------------------------------------------------------------------------------------------ CPU arm (oracle)
+class CpuRound:
+    """One whole speculative round on the host cores with the reference's CPU kernels (the C restatement of its
+    reference.rs; the Rust toolchain is absent, so kind = "port"): k MTP draft forwards and one verify forward of k + 1
+    rows through every layer -- every weight product as the reference's f64-accumulate GEMM, the gated-DeltaNet recurrence,
+    paged attention over the context, norms, gates, argmax and the greedy acceptance rule.  Nothing is extrapolated: a step
+    is the full work of a round.  Weights are random bf16 words, one matrix per distinct shape shared by the layers of
+    that shape (values do not change the time; a layer's matrices exceed every CPU cache)."""
 
+    def __init__(self, shape, batch, k, ctx, threads):
+        from oracle import oracle as orc
+        self.orc, self.s, self.B, self.k, self.ctx, self.th = orc, shape, batch, k, ctx, threads
+        rs = np.random.default_rng(0)
+        s = shape
+        self.qd, self.he = s.q_heads * s.head_dim, s.kv_heads * s.head_dim
+        self.keyd, self.vald = s.lin_k_heads * s.lin_k_dim, s.lin_v_heads * s.lin_v_dim
+        self.cd = 2 * self.keyd + self.vald
 
-def cpu_round_seconds(t, shape, batch, k, ctx):
-    """Scales the unit timings to one full round (verify forward of k+1 rows + k draft forwards) of `batch` sequences."""
-    P = k + 1
-    n_full = sum(shape.is_full(l) for l in range(shape.n_layers))
-    n_lin = shape.n_layers - n_full
-    macs_verify = (shape.weight_bytes() // 2) * P * batch
-    macs_draft = (shape.mtp_bytes() // 2) * batch * k
-    gemm = (macs_verify + macs_draft) / t["gemm_sample_macs"] * t["gemm_sample"]
-    attn = n_full * t["gqa_layer"] * batch * (ctx / 512.0)
-    return gemm + batch * n_lin * t["gdn_layer"] + attn + batch * t["accept"]
+        def mat(n, kk):
+            blk = orc.f32_to_bf16((rs.standard_normal(min(n, 4096) * kk) * 0.02).astype(np.float32)).reshape(-1, kk)
+            return np.ascontiguousarray(np.tile(blk, ((n + blk.shape[0] - 1) // blk.shape[0], 1))[:n]).reshape(-1)
+
+        h, ii = s.hidden, s.inter
+        self.w = dict(lin_proj=mat(self.cd + self.vald + 2 * s.lin_v_heads, h), lin_out=mat(h, self.vald), full_proj=mat(2 * self.qd + 2 * self.he, h),
+                      full_o=mat(h, self.qd), gate=mat(ii, h), up=mat(ii, h), down=mat(h, ii), embed=mat(s.vocab, h), fc=mat(h, 2 * h))
+        r16 = lambda n, sc=1.0: orc.f32_to_bf16((rs.standard_normal(n) * sc).astype(np.float32))
+        self.vec_h, self.vec_hd = r16(h, 0.1), r16(s.head_dim, 0.1)
+        self.conv_w = r16(self.cd * 4, 0.3)
+        self.a_log, self.dtb = (rs.standard_normal(s.lin_v_heads) * 0.5).astype(np.float32), r16(s.lin_v_heads, 0.5)
+        self.norm_w = (1.0 + 0.1 * rs.standard_normal(s.lin_v_dim)).astype(np.float32)
+        self.state = (rs.standard_normal((k + 2) * s.lin_v_heads * s.lin_v_dim * s.lin_k_dim) * 0.1).astype(np.float32)
+        self.conv_state = r16(self.cd * 3)
+        pages = (ctx + k + 1 + 15) // 16
+        self.pages = pages
+        self.kc, self.vc = r16(pages * 16 * self.he), r16(pages * 16 * self.he)
+        self.bt = rs.permutation(pages).astype(np.uint32)
+        self.cos, self.sin = orc.rope_table(ctx + k + 2, s.rot_dim // 2, s.rope_theta, round_bf16=True)
+        self.r16 = r16
+
+    def _gemm(self, a, w, m, n, kk):
+        return self.orc.gemm_wt_bf16(a, w, m, n, kk, threads=self.th)
+
+    def _mlp(self, n2, T):
+        s, o = self.s, self.orc
+        g, u = self._gemm(n2, self.w["gate"], T, s.inter, s.hidden), self._gemm(n2, self.w["up"], T, s.inter, s.hidden)
+        return self._gemm(o.silu_mul(g, u), self.w["down"], T, s.hidden, s.inter)
+
+    def _full(self, n1, T, positions, seq_rows, kc, vc, bt, pages):
+        s, o = self.s, self.orc
+        p = self._gemm(n1, self.w["full_proj"], T, 2 * self.qd + 2 * self.he, s.hidden).reshape(T, -1)
+        qg = p[:, :2 * self.qd].reshape(T, s.q_heads, 2, s.head_dim)
+        q = o.rms_norm_zc(np.ascontiguousarray(qg[:, :, 0]).reshape(-1), self.vec_hd, T * s.q_heads, s.head_dim, s.rms_eps)
+        gate = np.ascontiguousarray(qg[:, :, 1]).reshape(-1)
+        kk = o.rms_norm_zc(np.ascontiguousarray(p[:, 2 * self.qd:2 * self.qd + self.he]).reshape(-1), self.vec_hd, T * s.kv_heads, s.head_dim, s.rms_eps)
+        v = np.ascontiguousarray(p[:, 2 * self.qd + self.he:]).reshape(-1)
+        q = o.rope_pt(q, self.cos, self.sin, positions, s.rot_dim, s.head_dim, s.q_heads)
+        kk = o.rope_pt(kk, self.cos, self.sin, positions, s.rot_dim, s.head_dim, s.kv_heads)
+        kc, vc = o.kv_scatter(kk, v, bt, seq_rows, positions, kc, vc, pages, 16, self.he)
+        att = o.paged_attn(q, kc, vc, bt, seq_rows, positions, 1.0 / np.sqrt(np.float32(s.head_dim)), pages, 16, s.q_heads, s.kv_heads, s.head_dim,
+                           threads=self.th)
+        return self._gemm(o.sigmul(att, gate), self.w["full_o"], T, s.hidden, self.qd)
+
+    def _lin(self, n1, T, P):
+        s, o = self.s, self.orc
+        vh = s.lin_v_heads
+        out = []
+        pr = self._gemm(n1, self.w["lin_proj"], T, self.cd + self.vald + 2 * vh, s.hidden).reshape(T, -1)
+        for b in range(T // P):   # one chain of P positions per sequence
+            rows = pr[b * P:(b + 1) * P]
+            qkv = np.ascontiguousarray(rows[:, :self.cd]).reshape(-1)
+            conv = o.conv1d_dw(qkv, self.conv_w, self.conv_state, [0] * P, list(range(P)), self.cd, 4).reshape(P, self.cd)
+            o.conv_state_roll(qkv, np.tile(self.conv_state, P + 1), [0], [P], [0], self.cd, 4, [1])
+            z = np.ascontiguousarray(rows[:, self.cd:self.cd + self.vald]).reshape(-1)
+            a = np.ascontiguousarray(rows[:, self.cd + self.vald:self.cd + self.vald + vh]).reshape(-1)
+            bb = np.ascontiguousarray(rows[:, self.cd + self.vald + vh:]).reshape(-1)
+            core, _ = o.deltanet(np.ascontiguousarray(conv[:, :self.keyd]).reshape(-1), np.ascontiguousarray(conv[:, self.keyd:2 * self.keyd]).reshape(-1),
+                                 np.ascontiguousarray(conv[:, 2 * self.keyd:]).reshape(-1), a, bb, self.a_log, self.dtb, self.state[: (P + 1) * vh * 128 * 128],
+                                 [0], [P], [0], s.lin_k_heads, vh, 128, 128, s.l2_eps, [1], state_mode=1, threads=self.th)
+            out.append(o.rms_norm_gated(core, z, self.norm_w, P * vh, s.lin_v_dim, s.rms_eps))
+        return self._gemm(np.concatenate(out), self.w["lin_out"], T, s.hidden, self.vald)
+
+    def run(self):
+        """Executes one round; returns seconds."""
+        s, o, B, k = self.s, self.orc, self.B, self.k
+        h = s.hidden
+        t0 = time.perf_counter()
+        # k draft forwards of the MTP head: one row per sequence, a one-page chain of its own
+        x = self.r16(B * h)
+        for i in range(k):
+            cat = np.concatenate([o.rms_norm_zc(x, self.vec_h, B, h, s.rms_eps).reshape(B, h), o.rms_norm_zc(x, self.vec_h, B, h, s.rms_eps).reshape(B, h)], axis=1)
+            x = self._gemm(cat.reshape(-1), self.w["fc"], B, h, 2 * h)
+            n1 = o.rms_norm_zc(x, self.vec_h, B, h, s.rms_eps)
+            kc, vc = np.zeros(B * 16 * self.he, np.uint16), np.zeros(B * 16 * self.he, np.uint16)
+            att = self._full(n1, B, np.full(B, i, np.uint32), np.arange(B, dtype=np.uint32), kc, vc, np.arange(B, dtype=np.uint32), 1)
+            h2, n2 = o.add_norm_zc(x, att, self.vec_h, B, h, s.rms_eps)
+            x, n2 = o.add_norm_zc(h2, self._mlp(n2, B), self.vec_h, B, h, s.rms_eps)
+            o.argmax_rows(self._gemm(n2, self.w["embed"], B, s.vocab, h), np.arange(B), s.vocab, threads=self.th)
+        # verify forward over B chains of P rows
+        P = k + 1
+        T = B * P
+        x = self.r16(T * h)
+        n1 = o.rms_norm_zc(x, self.vec_h, T, h, s.rms_eps)
+        positions = np.tile(np.arange(self.ctx, self.ctx + P, dtype=np.uint32), B)
+        seq_rows = np.zeros(T, np.uint32)     # every chain reads a context of the same length: the one synthetic page table
+        for l in range(s.n_layers):
+            att = self._full(n1, T, positions, seq_rows, self.kc, self.vc, self.bt, self.pages) if s.is_full(l) else self._lin(n1, T, P)
+            h2, n2 = o.add_norm_zc(x, att, self.vec_h, T, h, s.rms_eps)
+            x, n1 = o.add_norm_zc(h2, self._mlp(n2, T), self.vec_h, T, h, s.rms_eps)
+        tg = o.argmax_rows(self._gemm(n1, self.w["embed"], T, s.vocab, h), np.arange(T), s.vocab, threads=self.th).reshape(B, P)
+        for b in range(B):
+            o.accept_greedy(tg[b, :k], tg[b])
+        return time.perf_counter() - t0
 
 
 def run_reference(args, wl):
-    """The reference's CPU implementation of the path (C port of its reference.rs kernels, the Rust toolchain being
-    absent), all host threads, each step = one bounded sample unit scaled to a full round."""
+    """The reference's CPU implementation of the path (C port of its reference.rs kernels), all host threads: every step is
+    one whole round of the headline workload, computed for real."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     from inferulm_b200.engine import ModelShape
     shape = ModelShape()
     threads = os.cpu_count() or 1
+    cpu = CpuRound(shape, wl["batch"], wl["k"], wl["prompt"] + 24, threads)
     for _ in range(min(args.warmup, 1)):
-        cpu_unit(threads, shape)
-    secs = []
-    t_all = time.perf_counter()
-    for _ in range(min(args.steps, 8)):
-        u = cpu_unit(threads, shape)
-        secs.append(cpu_round_seconds(u, shape, wl["batch"], wl["k"], wl["prompt"]))
-    wall = time.perf_counter() - t_all
-    sec = float(np.median(secs))
+        cpu.run()
+    secs = [cpu.run() for _ in range(args.steps)]
+    sec = float(np.mean(secs))
     value = wl["batch"] * 1.0 / sec      # one token per sequence per round (draft acceptance of random weights ~ 0)
-    line = dict(metric="accepted_tok_per_s", value=value, unit="tok/s", n_gpus=args.gpus, steps=args.steps, warmup=args.warmup,
+    line = dict(metric="accepted_tok_per_s", value=value, unit="tok/s", n_gpus=args.gpus, steps=args.steps, warmup=min(args.warmup, 1),
                 ms_per_step=sec * 1e3, higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
-                impl="reference", config=dict(workload=wl["desc"], name=args.workload),
+                impl="reference", extrapolated=False, config=dict(workload=wl["desc"], name=args.workload),
                 cpu_baseline=dict(value=value, unit="tok/s", cores=threads, kind="port",
-                                  sample=f"BASELINE unit (1 GDN layer x4 positions, 1 GQA layer ctx 512, accept 4x151936, 1/8 gate|up GEMM) "
-                                         f"scaled to a full round; {wall:.1f} s of CPU work"),
+                                  sample=f"{args.steps} whole rounds (k draft forwards + verify forward of k+1 rows through all 32 layers + acceptance), "
+                                         f"{sum(secs):.1f} s of CPU work"),
                 e2e=dict(value=value, unit="tok/s", h2d_bytes_per_step=0, d2h_bytes_per_step=0))
     print(json.dumps(line))
 
 
 # ------------------------------------------------------------------------------------------------ our arm
-def run_ours(args, wl):
-    import torch
-    import torch.distributed as dist
-    from inferulm_b200.engine import Engine, ModelShape, SyntheticWeights
+def verify_bytes_of(shape, B, k, ctx, snapshots=False):
+    """Algorithmic bytes of one verify step: weights + recurrent state + conv rows + KV + logits (written and read)."""
+    P = k + 1
+    n_full = sum(shape.is_full(l) for l in range(shape.n_layers))
+    n_lin = shape.n_layers - n_full
+    st_row = shape.lin_v_heads * 128 * 128 * 4
+    conv_row = (2 * shape.lin_k_heads * 128 + shape.lin_v_heads * 128) * 3 * 2
+    kv_tok = 2 * shape.kv_heads * shape.head_dim * 2
+    # with three or more positions the engine logs per-position updates and materialises one state per chain (read by the
+    # layer, read + written by the commit: 3 rows, plus the 1056-byte records written and read back); otherwise one row
+    # is read and a snapshot per position written (1 + P rows)
+    lite = P >= 3 and not snapshots
+    state_bytes = (3 * st_row + 2 * P * shape.lin_v_heads * 1056) if lite else (1 + P) * st_row
+    return (shape.weight_bytes() + B * n_lin * (state_bytes + (1 + P) * conv_row) + B * n_full * kv_tok * (ctx + P) + 2 * B * P * shape.vocab * 2), lite
 
-    from inferulm_b200 import dist_util as du
-    rank, world, local = du.rank_world()
-    torch.cuda.set_device(local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
-    shape = ModelShape()
-    weights = SyntheticWeights(shape, seed=0, std=0.02)
-    B, k, prompt_len = wl["batch"], wl["k"], wl["prompt"]
-    rounds_total = args.warmup + args.steps
-    max_pos = prompt_len + 2 * (rounds_total + 8) * (k + 1) + 64
-    eng = Engine(weights, max_seqs=B, k_max=k, max_pos=max_pos, state_f32=True)
-    rs = np.random.default_rng(7000 + rank)
-    prompts = du.rank_prompts(rank, B, prompt_len, shape.vocab)
-    slots = list(range(B))
-    for s in slots:
-        eng.admit(s, max_pos, temp=wl["temp"], top_k=wl["top_k"], top_p=wl["top_p"], seed=rank * 1000 + s, rng=rs)
-    eng.prefill(slots, prompts)
 
-    def barrier():
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
+class Job:
+    """One engine with its sequences admitted and prefilled (or resumed on synthetic KV), and the timed loops over it."""
 
-    def timed(nrounds, mode):
-        """mode 'graph': back-to-back replays, no host work between rounds.  mode 'e2e': every round re-uploads its host
-        inputs (the slot table, from pinned memory) and reads its results back (tokens emitted, position, counters)."""
+    def __init__(self, torch, dist, world, weights, wl, rounds_total, rank, synthetic_kv=False):
+        from inferulm_b200.engine import Engine
+        from inferulm_b200 import dist_util as du
+        self.torch, self.dist, self.world, self.wl = torch, dist, world, wl
+        B, k, prompt_len = wl["batch"], wl["k"], wl["prompt"]
+        self.B, self.k = B, k
+        self.max_pos = prompt_len + 2 * (rounds_total + 8) * (k + 1) + 64
+        self.eng = eng = Engine(weights, max_seqs=B, k_max=k, max_pos=self.max_pos, state_f32=True)
+        rs = np.random.default_rng(7000 + rank)
+        self.slots = list(range(B))
+        self.rank = rank
+        self.admit_all(wl["temp"], wl["top_k"], wl["top_p"], rs)
+        if synthetic_kv:
+            # long contexts: the KV pages hold N(0, 1) values (the first BASELINE configuration's description of a paged KV) and
+            # every sequence resumes at its prompt length, as after a prefix-cache hit; the recurrent state starts at zero
+            g = torch.Generator(device="cuda")
+            g.manual_seed(rank)
+            for i in range(sum(weights.shape.is_full(l) for l in range(weights.shape.n_layers))):
+                for nm in ("k_pool", "v_pool"):
+                    eng.buffer(f"{nm}:{i}", torch.int16).view(torch.bfloat16).normal_(0.0, 1.0, generator=g)
+            for s in self.slots:
+                eng.resume(s, prompt_len, int(rs.integers(0, weights.shape.vocab)))
+        else:
+            eng.prefill(self.slots, du.rank_prompts(rank, B, prompt_len, weights.shape.vocab))
+
+    def admit_all(self, temp, top_k, top_p, rs):
+        self.eng._free_pages = list(range(self.eng.n_pages))
+        for s in self.slots:
+            self.eng.admit(s, self.max_pos, temp=temp, top_k=top_k, top_p=top_p, seed=self.rank * 1000 + s, rng=rs)
+
+    def barrier(self):
+        if self.world > 1:
+            self.dist.barrier()
+        self.torch.cuda.synchronize()
+
+    def timed(self, nrounds, mode, drafts=None):
+        """mode 'graph': back-to-back replays of the whole round, no host work between rounds.  'e2e': every round re-uploads
+        its host inputs (the slot table, from pinned memory) and reads its results back.  'verify': the verify step alone
+        (verify forward + acceptance + commit) through spec_verify with the caller's drafts, graph replay."""
+        torch, eng, slots, k = self.torch, self.eng, self.slots, self.k
         cnt0 = eng.counts(slots)
         bound = max(p for _, p in cnt0)
-        barrier()
+        self.barrier()
         ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         with torch.cuda.stream(eng.stream):
             ev0.record(eng.stream)
             for _ in range(nrounds):
-                bound = min(bound + k + 1, max_pos)
-                eng.spec_step(slots, k, bound, use_graph=3 if mode == "e2e" else 1)
-                if mode == "e2e":
-                    eng.read_round(len(slots))
+                bound = min(bound + k + 1, self.max_pos)
+                if mode == "verify":
+                    eng.spec_verify(slots, k, drafts, bound, use_graph=True)
+                else:
+                    eng.spec_step(slots, k, bound, use_graph=3 if mode == "e2e" else 1)
+                    if mode == "e2e":
+                        eng.read_round(len(slots))
             ev1.record(eng.stream)
-        barrier()
+        self.barrier()
         ms = ev0.elapsed_time(ev1)
         cnt1 = eng.counts(slots)
-        toks = sum(c1 - c0 for (c0, _), (c1, _) in zip(cnt0, cnt1))
-        return ms, toks
+        return ms, sum(c1 - c0 for (c0, _), (c1, _) in zip(cnt0, cnt1))
 
-    timed(args.warmup, "graph")
-    sampler = ClockSampler(local)
-    sampler.start()
-    if args.profile:
-        torch.cuda.profiler.start()
-    ms, toks = timed(args.steps, "graph")
-    if args.profile:
-        torch.cuda.profiler.stop()
-    sampler.stop_flag = True
-    launches = eng.last_launches() * args.steps
-    ctx_now = max(p for _, p in eng.counts(slots))
-    # the verify step alone (verify forward over k+1 rows + acceptance + commit): the same round with the draft forwards
-    # skipped through the library's measurement hook (the verify rows then carry stale draft tokens: timing only)
-    import ctypes as C
-    eng.lib.wein_b200_engine_ablate(C.c_uint32(16))
-    timed(min(args.warmup, 3), "graph")
-    ms_verify, _ = timed(args.steps, "graph")
-    eng.lib.wein_b200_engine_ablate(C.c_uint32(int(os.environ.get("WEIN_B200_ABLATE", "0"))))
-    timed(min(args.warmup, 3), "e2e")
-    ms_e2e, toks_e2e = timed(args.steps, "e2e")
 
-    dev0 = torch.device("cuda", local)
-    ms_max, toks_all = du.reduce_job(ms, toks, dev0)
-    ms_e2e_max, toks_e2e_all = du.reduce_job(ms_e2e, toks_e2e, dev0)
-    ms_verify_max, _ = du.reduce_job(ms_verify, 0, dev0)
-    stats = [eng.read(s, cap=1)[2] for s in slots]
-    acc = sum(s["accepted"] for s in stats) / max(1, sum(s["drafts"] for s in stats))
-
-    # ---- roofline of the dominant kernel: the weight-streaming GEMM, timed alone over the 32 layers' gate|up
-    # matrices (94 MB each, 3 GB in rotation: every launch reads its weights from HBM, not from L2)
-    peak, peak_kind = peaks()
+def gateup_roofline(torch, weights, shape, M, tc, peak):
+    """The dominant launch of a round -- the gate|up projection with the SwiGLU epilogue (94 MB of weights) -- timed alone:
+    a graph over the 32 layers' matrices (3 GB in rotation: every launch reads its weights from HBM, not from L2)."""
     from inferulm_b200 import ops
-    P = k + 1
-    M = B * P
     a_in = torch.randn(M, shape.hidden, device="cuda").to(torch.bfloat16)
-    fused = M <= 32   # the engine's launch for this projection: skinny GEMM with the SwiGLU epilogue, else cuBLASLt
-    c_out = torch.empty(M, shape.inter if fused else 2 * shape.inter, dtype=torch.bfloat16, device="cuda")
-    scratch = torch.zeros(ops.gemm_scratch_bytes(2 * shape.inter) // 4, dtype=torch.int32, device="cuda")
+    c_out = torch.empty(M, shape.inter, dtype=torch.bfloat16, device="cuda")
     gus = [d["gu"] for d in weights.layers]
-
-    def one(g):
-        if fused:
-            ops.gemm_swiglu(a_in, g, c_out, M, shape.inter, shape.hidden, scratch)
-        else:
-            ops.gemm_wt(a_in, g, c_out, M, 2 * shape.inter, shape.hidden, scratch)
-
+    one = lambda g: ops.gemm_swiglu(a_in, g, c_out, M, shape.inter, shape.hidden, tc=tc)
     side = torch.cuda.Stream()
     with torch.cuda.stream(side):
         for g in gus[:3]:
@@ -269,69 +326,274 @@ def run_ours(args, wl):
         e1.record()
         torch.cuda.synchronize()
         gemm_ms = min(gemm_ms, e0.elapsed_time(e1) / len(gus))
-    gemm_bytes = 2 * shape.inter * shape.hidden * 2 + M * shape.hidden * 2 + M * (shape.inter if fused else 2 * shape.inter) * 2
+    gemm_bytes = 2 * shape.inter * shape.hidden * 2 + M * shape.hidden * 2 + M * shape.inter * 2
     achieved = gemm_bytes / (gemm_ms * 1e-3) / 1e9
-    kernel_name = (f"wgemm_kernel (gate|up + SwiGLU) m={M} n={2 * shape.inter} k={shape.hidden}" if fused
-                   else f"cuBLASLt gate|up m={M} n={2 * shape.inter} k={shape.hidden}")
+    name = ("ugemm_kernel (tcgen05, gate|up + SwiGLU)" if tc else "wgemm_kernel (gate|up + SwiGLU)") + f" m={M} n={2 * shape.inter} k={shape.hidden}"
+    return dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak, traffic=NCU_TRAFFIC.get(("ugemm" if tc else "wgemm", M)),
+                kernel=name, us_per_launch=gemm_ms * 1e3, algorithmic_bytes=gemm_bytes)
 
-    # ---- algorithmic bytes of one round: verify step (weights + state + conv + KV + logits) + k draft forwards
-    n_full = sum(shape.is_full(l) for l in range(shape.n_layers))
-    n_lin = shape.n_layers - n_full
-    st_row = shape.lin_v_heads * 128 * 128 * 4
-    conv_row = (2 * shape.lin_k_heads * 128 + shape.lin_v_heads * 128) * 3 * 2
-    kv_tok = 2 * shape.kv_heads * shape.head_dim * 2
-    # DeltaNet state: with three or more positions the engine logs per-position updates and materialises one state per chain
-    # (read by the layer, read + written by the commit: 3 rows, plus the 1056-byte records written and read back); below
-    # that, and with WEIN_B200_LITE=0, one row is read and a snapshot per position written (1 + P rows)
-    lite = P >= 3 and os.environ.get("WEIN_B200_LITE", "1") != "0"
-    state_bytes = (3 * st_row + 2 * P * shape.lin_v_heads * 1056) if lite else (1 + P) * st_row
-    verify_bytes = (shape.weight_bytes() + B * n_lin * (state_bytes + (1 + P) * conv_row) + B * n_full * kv_tok * (ctx_now + P)
-                    + 2 * B * P * shape.vocab * 2)
-    round_bytes = verify_bytes + k * shape.mtp_bytes()
-    step_s = ms_max * 1e-3 / args.steps
+
+def measure_workload(torch, dist, world, rank, weights, shape, wl, args, peak, synthetic_kv=False):
+    """Round time (graph replay), end-to-end time and the verify step of one workload; returns a dict of this rank's figures."""
+    from inferulm_b200 import dist_util as du
+    dev0 = torch.device("cuda", torch.cuda.current_device())
+    job = Job(torch, dist, world, weights, wl, 3 * (args.warmup + args.steps) + 8, rank, synthetic_kv)
+    eng, B, k = job.eng, job.B, job.k
+    job.timed(args.warmup, "graph")
+    ms, toks = job.timed(args.steps, "graph")
+    launches = eng.last_launches() * args.steps
+    ctx_now = max(p for _, p in eng.counts(job.slots))
+    # the verify step alone: the drafts handed in are the tokens the MTP head would have proposed or any ids -- the time of the
+    # verify forward does not depend on them
+    drafts = torch.randint(0, shape.vocab, (B, k), dtype=torch.int32, device="cuda")
+    job.timed(min(args.warmup, 3), "verify", drafts)
+    ms_verify, _ = job.timed(args.steps, "verify", drafts)
+    job.timed(min(args.warmup, 3), "e2e")
+    ms_e2e, toks_e2e = job.timed(args.steps, "e2e")
+    ms_max, toks_all = du.reduce_job(ms, toks, dev0)
+    ms_e2e_max, toks_e2e_all = du.reduce_job(ms_e2e, toks_e2e, dev0)
+    ms_verify_max, _ = du.reduce_job(ms_verify, 0, dev0)
+    stats = [eng.read(s, cap=1)[2] for s in job.slots]
+    acc = sum(s["accepted"] for s in stats) / max(1, sum(s["drafts"] for s in stats))
+    vbytes, lite = verify_bytes_of(shape, B, k, ctx_now)
+    vs = ms_verify_max / args.steps * 1e-3
+    out = dict(job=job, ms=ms_max, toks=toks_all, toks_local=toks, ms_e2e=ms_e2e_max, toks_e2e=toks_e2e_all, launches=launches, ctx=ctx_now, acc=acc,
+               verify=dict(us=vs * 1e6, bytes=vbytes, achieved_gbs=vbytes / vs / 1e9, frac_of_measured_peak=vbytes / vs / 1e9 / peak,
+                           frac_of_8tbs=vbytes / vs / 8e12, through="wein_b200_engine_spec_verify (caller drafts, graph replay)"),
+               lite=lite, round_bytes=vbytes + k * shape.mtp_bytes())
+    return out
+
+
+def summarize(m, shape, args, world, peak):
+    """The per-workload object of the JSON line."""
+    B, k = m["job"].B, m["job"].k
+    step_s = m["ms"] * 1e-3 / args.steps
+    return dict(ms_per_step=m["ms"] / args.steps, value=m["toks"] / (m["ms"] * 1e-3), unit="tok/s",
+                e2e=dict(value=m["toks_e2e"] / (m["ms_e2e"] * 1e-3), unit="tok/s", ms_per_step=m["ms_e2e"] / args.steps, h2d_bytes_per_step=4 * B,
+                         d2h_bytes_per_step=B * 4 * (4 + k + 1)),
+                batch_per_gpu=B, k=k, ctx_at_timing=m["ctx"], draft_acceptance=m["acc"], tokens_per_round=m["toks_local"] / max(1, args.steps) / B,
+                tok_s_if_every_draft_were_accepted=world * B * (k + 1) / step_s, verify_step=m["verify"],
+                step_roofline=dict(round_bytes=m["round_bytes"], round_us=step_s * 1e6, achieved_gbs=m["round_bytes"] / step_s / 1e9,
+                                   frac_of_measured_peak=m["round_bytes"] / step_s / 1e9 / peak, frac_of_8tbs=m["round_bytes"] / step_s / 8e12))
+
+
+def sweep_c4(torch, job, shape, peak, rounds=10):
+    """BASELINE configuration 4 as written: acceptance imposed by drafts drawn from target logits + N(0, sigma) noise,
+    sigma in {0.5, 2.0}, greedy and sampled (T = 1.0).  The target logits of chain position j depend on drafts 0..j-1, so a
+    round is built by k dry-run verify passes (nothing committed), each of which yields the true target logits of one more
+    position; the draft for that position is the argmax (greedy) or a sample (T = 1) of the noisy logits, with the noisy
+    distribution kept as the draft distribution q.  Then ONE committing spec_verify pass with those drafts is timed."""
+    from inferulm_b200 import ops
+    eng, slots, B, k = job.eng, job.slots, job.B, job.k
+    V, P = shape.vocab, k + 1
+    out = {}
+    t_draft = None
+    rs = np.random.default_rng(99)
+    for mode, temp in (("greedy", 0.0), ("sampled_T1", 1.0)):
+        for sigma in (0.5, 2.0):
+            job.admit_all(temp, 64 if temp > 0 else 0, 1.0, np.random.default_rng(7000 + job.rank))
+            for s in slots:
+                eng.resume(s, job.wl["prompt"], int(rs.integers(0, V)))
+            g = torch.Generator(device="cuda")
+            g.manual_seed(int(sigma * 10) + (1 if temp > 0 else 0))
+            logits = eng.buffer("logits", torch.int16).view(torch.bfloat16)[: B * P * V].view(B, P, V)
+            drafts = torch.zeros(B, k, dtype=torch.int32, device="cuda")
+            q_ids = torch.full((B, k, 64), -1, dtype=torch.int32, device="cuda")
+            q_probs = torch.zeros(B, k, 64, dtype=torch.float32, device="cuda")
+            q_n = torch.zeros(B, k, dtype=torch.int32, device="cuda")
+            tv, kv, pv = (torch.full((B,), temp, device="cuda"), torch.full((B,), 64, dtype=torch.int32, device="cuda"), torch.ones(B, device="cuda"))
+            ms_total, tok0 = 0.0, sum(c for c, _ in eng.counts(slots))
+            bound = job.wl["prompt"] + P
+            for r in range(rounds):
+                bound = min(bound + P, job.max_pos)
+                for j in range(k):
+                    nd = torch.full((B,), j, dtype=torch.int32, device="cuda")
+                    eng.spec_verify(slots, k, drafts, bound, n_drafts=nd, q=(q_ids, q_probs, q_n) if temp > 0 else None, dry_run=True)
+                    with torch.cuda.stream(eng.stream):
+                        noisy = (logits[:, j].float() + sigma * torch.randn(B, V, device="cuda", generator=g)).to(torch.bfloat16).contiguous()
+                        if temp > 0:
+                            ids = torch.zeros(B, 64, dtype=torch.int32, device="cuda")
+                            pr = torch.zeros(B, 64, dtype=torch.float32, device="cuda")
+                            nn = torch.zeros(B, dtype=torch.int32, device="cuda")
+                            ops.topk_filter(noisy.view(torch.int16), None, None, 1, tv, kv, pv, V, B, ids, pr, nn)
+                            pick = torch.multinomial(pr.clamp_min(0) + 1e-30, 1, generator=g).squeeze(1)
+                            drafts[:, j] = ids.gather(1, pick.unsqueeze(1).long()).squeeze(1)
+                            q_ids[:, j], q_probs[:, j], q_n[:, j] = ids, pr, nn
+                        else:
+                            drafts[:, j] = noisy.float().argmax(dim=1).to(torch.int32)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                with torch.cuda.stream(eng.stream):
+                    e0.record(eng.stream)
+                    eng.spec_verify(slots, k, drafts, bound, q=(q_ids, q_probs, q_n) if temp > 0 else None, use_graph=True)
+                    e1.record(eng.stream)
+                torch.cuda.synchronize()
+                if r >= 2:      # the first committing passes capture the graph and warm up
+                    ms_total += e0.elapsed_time(e1)
+                else:
+                    tok0 = sum(c for c, _ in eng.counts(slots))
+            if t_draft is None:     # the cost of drafting k tokens with the MTP head, graph replay, for the tok/s that includes it
+                eng.draft(slots, k)
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                with torch.cuda.stream(eng.stream):
+                    e0.record(eng.stream)
+                    for _ in range(5):
+                        eng.draft(slots, k)
+                    e1.record(eng.stream)
+                torch.cuda.synchronize()
+                t_draft = e0.elapsed_time(e1) / 5
+            st = [eng.stats(s) for s in slots]
+            toks = sum(c for c, _ in eng.counts(slots)) - tok0
+            n_t = rounds - 2
+            acc = sum(s["accepted"] for s in st) / max(1, sum(s["drafts"] for s in st))
+            vms = ms_total / n_t
+            out[f"{mode}_sigma{sigma}"] = dict(acceptance=acc, tokens_per_round_per_seq=toks / n_t / B, verify_ms=vms,
+                                              accepted_tok_s_verify_only=toks / (ms_total * 1e-3),
+                                              accepted_tok_s_with_mtp_draft_cost=toks / ((ms_total + n_t * t_draft) * 1e-3),
+                                              accept_length_histogram=[sum(s["by_accept"][i] for s in st) for i in range(P)])
+    out["mtp_draft_ms"] = t_draft
+    out["construction"] = ("draft j = argmax / sample of (target logits of position j + N(0, sigma)), target logits obtained by dry-run verify "
+                           "passes; the committing spec_verify pass is the timed one")
+    return out
+
+
+def run_c5(torch, dist, world, rank, weights, shape, peak, n_seqs=256, out_tokens=256, slots_per_gpu=32, k=3):
+    """BASELINE configuration 5: 256 sequences, prompt lengths log-uniform 256..8192, 256 output tokens each, k = 3, sampled
+    T = 0.7 / top-k 50 / top-p 0.9, assigned to the ranks by longest-first bin packing on prompt + output tokens; every rank
+    keeps `slots_per_gpu` sequences in flight and refills a slot when its sequence finishes.  The prompts' KV is synthetic
+    (N(0, 1) pages, sequences resume at their prompt length): prefill is outside this path.  Returns this job's figures."""
+    from inferulm_b200 import dist_util as du
+    from inferulm_b200.engine import Engine
+    rs = np.random.default_rng(555)
+    lens = np.exp(rs.uniform(np.log(256), np.log(8192), n_seqs)).astype(np.int64)
+    first = rs.integers(0, shape.vocab, n_seqs)
+    mine = du.pack_sequences(lens + out_tokens, world)[rank]
+    S = min(slots_per_gpu, max(1, len(mine)))
+    max_pos = int(8192 + out_tokens + 4 * (k + 1) + 16)
+    eng = Engine(weights, max_seqs=S, k_max=k, max_pos=max_pos, state_f32=True)
+    g = torch.Generator(device="cuda")
+    g.manual_seed(rank)
+    for i in range(sum(shape.is_full(l) for l in range(shape.n_layers))):
+        for nm in ("k_pool", "v_pool"):
+            eng.buffer(f"{nm}:{i}", torch.int16).view(torch.bfloat16).normal_(0.0, 1.0, generator=g)
+    pages_of = {s: list(range(s * eng.bpr, (s + 1) * eng.bpr)) for s in range(S)}
+    queue = list(mine)
+    live = {}
+
+    def start(slot):
+        i = queue.pop(0)
+        eng.admit(slot, max_pos, temp=0.7, top_k=50, top_p=0.9, seed=int(i), pages=pages_of[slot])
+        eng.resume(slot, int(lens[i]), int(first[i]))
+        live[slot] = [i, 0]
+
+    for s in range(S):
+        if queue:
+            start(s)
+    eng.warm(sorted(live), k, max_pos, what=1)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    toks = rounds = 0
+    with torch.cuda.stream(eng.stream):
+        ev0.record(eng.stream)
+        while live:
+            slots = sorted(live)
+            bound = max(int(lens[live[s][0]]) + live[s][1] for s in slots) + k + 1
+            eng.spec_step(slots, k, min(bound, max_pos), use_graph=3)
+            rr = eng.read_round(len(slots))
+            rounds += 1
+            for b, s in enumerate(slots):
+                n_new = int(rr[b, 0]) + 1
+                live[s][1] += n_new
+                toks += n_new
+                if live[s][1] >= out_tokens:
+                    del live[s]
+                    if queue:
+                        start(s)
+        ev1.record(eng.stream)
+    torch.cuda.synchronize()
+    ms = ev0.elapsed_time(ev1)
+    eng.close()
+    dev0 = torch.device("cuda", torch.cuda.current_device())
+    ms_max, toks_all = du.reduce_job(ms, toks, dev0)
+    ms_min = -du.reduce_job(-ms, 0, dev0)[0]
+    work = float((lens + out_tokens)[mine].sum()) if len(mine) else 0.0
+    work_max, work_sum = du.reduce_job(work, work, dev0)
+    return dict(value=toks_all / (ms_max * 1e-3), unit="tok/s", scaling="strong", sequences=n_seqs, output_tokens_each=out_tokens, slots_per_gpu=slots_per_gpu,
+                k=k, sampling="T=0.7 top-k 50 top-p 0.9", job_ms=ms_max, fastest_rank_ms=ms_min, rank_finish_spread=(ms_max - ms_min) / ms_max,
+                packing="longest-first greedy bin packing on prompt + output tokens", packing_imbalance=work_max / (work_sum / world) - 1.0,
+                rounds_rank0=rounds, prompt_kv="synthetic N(0,1) pages, sequences resume at their prompt length (prefill is outside the path)",
+                e2e="every round goes through spec_step + read_round (host-paced: slot refill needs each round's counts)")
+
+
+def run_ours(args, wl):
+    import torch
+    import torch.distributed as dist
+    from inferulm_b200.engine import ModelShape, SyntheticWeights
+    from inferulm_b200 import dist_util as du
+    rank, world, local = du.rank_world()
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    shape = ModelShape()
+    weights = SyntheticWeights(shape, seed=0, std=0.02)
+    peak, peak_kind = peaks()
+    sampler = ClockSampler(local)
+    sampler.start()
+    head = measure_workload(torch, dist, world, rank, weights, shape, wl, args, peak, synthetic_kv=wl["prompt"] > 8192)
+    sampler.stop_flag = True
+    B, k = wl["batch"], wl["k"]
+    roof = gateup_roofline(torch, weights, shape, B * (k + 1), B * (k + 1) > 32, peak)
+    roof["peak_kind"] = peak_kind
+    extra = {}
+    if args.workload == "c4":
+        extra["c4_sweep"] = sweep_c4(torch, head["job"], shape, peak)
+    head["job"].eng.close()
+    if not args.only_headline and args.workload == "c2":
+        sub = argparse.Namespace(**vars(args))
+        sub.steps, sub.warmup = min(args.steps, 20), min(args.warmup, 5)
+        m3 = measure_workload(torch, dist, world, rank, weights, shape, WORKLOADS["c3"], sub, peak)
+        o3 = summarize(m3, shape, sub, world, peak)
+        o3["workload"] = WORKLOADS["c3"]["desc"]
+        o3["roofline"] = gateup_roofline(torch, weights, shape, 32 * 4, True, peak)
+        m3["job"].eng.close()
+        extra["bs32"] = o3
+        m4 = measure_workload(torch, dist, world, rank, weights, shape, WORKLOADS["c4"], sub, peak, synthetic_kv=True)
+        o4 = summarize(m4, shape, sub, world, peak)
+        o4["workload"] = WORKLOADS["c4"]["desc"]
+        o4["roofline"] = gateup_roofline(torch, weights, shape, 8 * 5, True, peak)
+        o4["acceptance_sweep"] = sweep_c4(torch, m4["job"], shape, peak)
+        m4["job"].eng.close()
+        extra["c4"] = o4
+        extra["c5"] = run_c5(torch, dist, world, rank, weights, shape, peak)
 
     if rank == 0:
         cpu = None
-        if world == 1 or True:
+        if world == 1:
             threads = os.cpu_count() or 1
-            t0 = time.perf_counter()
-            u = cpu_unit(threads, shape)
-            sec = cpu_round_seconds(u, shape, B, k, ctx_now)
-            per_round = toks / max(1, args.steps) / B
-            cpu = dict(value=B * per_round / sec, unit="tok/s", cores=threads, kind="port",
-                       sample=f"BASELINE unit (1 GDN layer x{P} positions, 1 GQA layer ctx 512, accept {P}x{shape.vocab}, 1/8 gate|up GEMM) "
-                              f"scaled to one round at ctx {ctx_now}; {time.perf_counter() - t0:.1f} s of CPU work")
-        line = dict(metric="accepted_tok_per_s", value=toks_all / (ms_max * 1e-3), unit="tok/s", n_gpus=world, steps=args.steps,
-                    warmup=args.warmup, ms_per_step=ms_max / args.steps, higher_is_better=True, scaling="weak", vs_baseline=None,
-                    dtype="bf16", data="synthetic",
-                    config=dict(workload=wl["desc"], name=args.workload, batch_per_gpu=B, k=k, prompt=prompt_len, ctx_at_timing=ctx_now,
+            cr = CpuRound(shape, B, k, head["ctx"], threads)
+            secs = [cr.run() for _ in range(2)]
+            per_round = head["toks_local"] / max(1, args.steps) / B
+            cpu = dict(value=B * per_round / float(np.mean(secs)), unit="tok/s", cores=threads, kind="port",
+                       sample=f"2 whole rounds of this workload at ctx {head['ctx']} (k draft forwards + verify forward through all layers + acceptance), "
+                              f"{sum(secs):.1f} s of CPU work")
+        o = summarize(head, shape, args, world, peak)
+        line = dict(metric="accepted_tok_per_s", value=o["value"], unit="tok/s", n_gpus=world, steps=args.steps, warmup=args.warmup,
+                    ms_per_step=o["ms_per_step"], higher_is_better=True, scaling="weak", vs_baseline=None, dtype="bf16", data="synthetic",
+                    config=dict(workload=wl["desc"], name=args.workload, batch_per_gpu=B, k=k, prompt=wl["prompt"], ctx_at_timing=head["ctx"],
                                 l2="per-round working set (7.9 GB of weights) exceeds L2; no flush needed", state="f32",
-                                draft_acceptance=acc, tokens_per_round=toks / max(1, args.steps) / B,
+                                draft_acceptance=head["acc"], tokens_per_round=o["tokens_per_round"],
                                 # the round is one fixed graph: its time does not depend on how many drafts are accepted, so
                                 # the same measurement gives the rate at any acceptance; random weights sit at the floor
-                                tok_s_if_every_draft_were_accepted=world * B * (k + 1) / (ms_max / args.steps * 1e-3)),
-                    e2e=dict(value=toks_e2e_all / (ms_e2e_max * 1e-3), unit="tok/s", h2d_bytes_per_step=4 * B,
-                             d2h_bytes_per_step=B * 4 * (3 + k + 1), ms_per_step=ms_e2e_max / args.steps),
-                    gpu_launches=launches,
-                    roofline=dict(bound="hbm", achieved=achieved, peak=peak, unit="GB/s", frac=achieved / peak,
-                                  traffic=(97.6e6 if fused and M == 4 else None),  # ncu dram read+write per launch, profiles/wgemm_gateup_swiglu_m4.md
-                                  kernel=kernel_name, peak_kind=peak_kind,
-                                  us_per_launch=gemm_ms * 1e3),
-                    verify_step=dict(us=ms_verify_max / args.steps * 1e3, bytes=verify_bytes,
-                                     achieved_gbs=verify_bytes / (ms_verify_max / args.steps * 1e-3) / 1e9,
-                                     frac_of_measured_peak=verify_bytes / (ms_verify_max / args.steps * 1e-3) / 1e9 / peak,
-                                     frac_of_8tbs=verify_bytes / (ms_verify_max / args.steps * 1e-3) / 8e12),
-                    state_traffic=("update records + one committed state per chain (3 state rows per layer)" if lite
+                                tok_s_if_every_draft_were_accepted=o["tok_s_if_every_draft_were_accepted"]),
+                    e2e=o["e2e"], gpu_launches=head["launches"], roofline=roof, verify_step=head["verify"],
+                    state_traffic=("update records + one committed state per chain (3 state rows per layer)" if head["lite"]
                                    else "one state snapshot per position (1 + P state rows per layer)"),
-                    step_roofline=dict(verify_bytes=verify_bytes, round_bytes=round_bytes, round_us=step_s * 1e6,
-                                       achieved_gbs=round_bytes / step_s / 1e9, frac_of_measured_peak=round_bytes / step_s / 1e9 / peak,
-                                       frac_of_8tbs=round_bytes / step_s / 8e12),
-                    cpu_baseline=cpu, clocks=sampler.summary())
+                    step_roofline=o["step_roofline"], cpu_baseline=cpu, clocks=sampler.summary(), **extra)
         print(json.dumps(line))
     if world > 1:
         dist.barrier()
         dist.destroy_process_group()
-    eng.close()
 
 
 def main():
@@ -342,13 +604,13 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--prompt", type=int, default=0, help="override the workload's prompt length (profiling captures use a short one)")
-    ap.add_argument("--profile", action="store_true", help="bracket the timed rounds with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
+    ap.add_argument("--only-headline", action="store_true", help="skip the bs32 / c4 / c5 objects (profiling captures)")
     args = ap.parse_args()
     wl = dict(WORKLOADS[args.workload])
     if args.prompt:
         wl["prompt"] = args.prompt
     if args.impl == "reference":
-        run_reference(args, wl)
+        run_reference(args, WORKLOADS["c2"] if args.workload != "c2" else wl)
     else:
         run_ours(args, wl)
 

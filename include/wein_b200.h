@@ -27,6 +27,14 @@ extern "C" {
 #define WEIN_B200_ERR_CUDA (-3)
 #define WEIN_B200_ERR_CAPACITY (-4)
 
+/* Device status word of a sequence slot: bits OR-ed in by kernels when a round meets an anomaly (the pattern of the reference's
+ * in-band sampler error, kernels/src/lib.rs:8197-8202).  Kernels clamp and flag; they never trap and never touch memory
+ * outside what the slot was admitted with.  Read with wein_b200_engine_status or in the last word of each read_round row. */
+#define WEIN_B200_STATUS_POS_LIMIT 1u  /* the slot sat a round out: position + 1 would pass its position limit */
+#define WEIN_B200_STATUS_K_CLAMPED 2u  /* fewer drafts than asked were verified: the chain would have passed the limit */
+#define WEIN_B200_STATUS_CTX_BOUND 4u  /* ctx_bound was below position + chain length: attention ignored later segments */
+#define WEIN_B200_STATUS_SAMPLER 8u    /* the sampler met an invalid parameter */
+
 const char *wein_b200_last_error(void);
 uint32_t wein_b200_abi_version(void);
 
@@ -142,24 +150,52 @@ int32_t wein_b200_paged_attn(const void *q, const void *k_cache, const void *v_c
  * rows row_start[r] .. +row_count[r] of one sequence at consecutive positions (<= 32 / group rows).  max_ctx bounds
  * position+1 over the call (sizes the grid only); seg_pages = pages per context segment (fixes the summation order: keep it
  * constant between runs that must agree bit for bit); gate (optional) applies out = sigmul(attn, gate).
- * scratch >= wein_b200_attn_scratch_bytes(n_spans, kv_heads, head_dim, ceil(ceil(max_ctx/16)/seg_pages)). */
+ * scratch >= wein_b200_attn_scratch_bytes(n_spans, kv_heads, head_dim, ceil(ceil(max_ctx/16)/seg_pages)).
+ * status (optional): u32 words indexed by sequence id; when max_ctx is below a row's position + 1 the row is reduced over the
+ * segments the grid covers only (no slot that nobody wrote is read) and WEIN_B200_STATUS_CTX_BOUND is OR-ed into its word. */
 int32_t wein_b200_attn_verify(const void *q, const void *k_cache, const void *v_cache, const void *block_table, const void *seq_ids,
                               const void *positions, const void *row_start, const void *row_count, const void *gate, void *out,
                               float q_scale, uint32_t bpr, uint32_t block_size, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
                               uint32_t n_spans, uint32_t max_count, uint32_t max_ctx, uint32_t seg_pages, void *scratch,
-                              uint64_t scratch_bytes, void *stream);
+                              uint64_t scratch_bytes, void *status, void *stream);
 
-/* GemmOp::run_wt (ops/mod.rs:3378-3449): C[m,n] = A[m,k] W[n,k]^T, bf16, f32 accumulate.  m <= 32 runs the hand-written
- * weight-streaming kernel (result of a row independent of the other rows), larger m goes to cuBLASLt like the reference.
- * scratch (optional, zero-filled once by the caller, wein_b200_gemm_scratch_bytes(n) bytes) enables split-k for narrow n. */
+/* GemmOp::run_wt (ops/mod.rs:3378-3449): C[m,n] = A[m,k] W[n,k]^T, bf16, f32 accumulate; k a multiple of 32, operands 16-byte
+ * aligned.  Two hand-written weight-streaming kernels, no library call (the reference sends m > 1 to cuBLASLt,
+ * cuda/cublaslt.rs:249-257): m <= 32 runs the register-streaming mma.sync kernel, larger m the tensor-memory kernel
+ * (tcgen05.mma, weights as the M operand, tensor-map bulk copies, k split over a thread-block cluster for narrow n).  In both
+ * the result of a row does not depend on the other rows of the call; the two kernels do not agree with each other bit for bit,
+ * so forwards that must agree across row counts use the _tc entries (the tensor-memory kernel at every m) throughout.
+ * scratch is optional and may be null (reserved for a split-k mode of the m <= 32 kernel). */
 uint64_t wein_b200_gemm_scratch_bytes(uint32_t n_max);
 int32_t wein_b200_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, void *scratch,
                           uint64_t scratch_bytes, void *stream);
+int32_t wein_b200_gemm_wt_tc(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, void *stream);
 /* Gate|up projection with the SwiGLU activation in the epilogue (GemmOp::run_wt x2 + SiluMulOp of the reference's MLP,
  * crates/wein-exec/src/qwen.rs:4090-4099): w_gate_up = [gate; up] of shape [2*inter, k]; out[m, inter] holds exactly the
- * values silu_mul produces from the two separately rounded projections.  m <= 32. */
+ * values silu_mul produces from the two separately rounded projections of the same kernel. */
 int32_t wein_b200_gemm_swiglu(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k,
                               void *scratch, uint64_t scratch_bytes, void *stream);
+int32_t wein_b200_gemm_swiglu_tc(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k,
+                                 void *stream);
+/* Barrier waits of the tensor-memory kernel that ran into their time limit since the library was loaded (0 in a healthy
+ * run; a non-zero count means a result was abandoned, not that a kernel hung).  Synchronises the device. */
+int32_t wein_b200_gemm_wait_timeouts(uint32_t *out);
+
+/* Fused glue of the forward passes; each writes, bit for bit, what the operator chain it replaces writes.
+ * qk_prep: row t of qgkv (stride ld) = [q_heads x (q | gate) x head_dim | k | v]; replaces the q / gate de-interleave
+ *   (2 x EmbedOp), RmsNormZcOp on the q and k heads, 2 x RopePtOp and KvScatterOp of a full-attention layer
+ *   (crates/wein-exec/src/qwen.rs:3888-3950): qh, gate [tokens, q_heads, head_dim]; K / V rows go to page slot
+ *   block_table[seq_ids[t]][kv_pos[t] / 16] * 16 + kv_pos[t] % 16.  rope_pos indexes the cos / sin tables [*, rot_dim / 2] f32.
+ * mtp_cat: cat[r] = [norm_zc(embed[tok[r]], pre_e) | norm_zc(hid[hid_rows ? hid_rows[r] : r], pre_h)], the input of the MTP
+ *   head's fc (2 gathers, 2 x RmsNormZcOp and a row copy in the reference, qwen.rs:4451-4468).
+ * silu_mul_rows: SiluMulOp over rows that hold gate | up side by side (row stride ld >= 2 * inter). */
+int32_t wein_b200_qk_prep(const void *qgkv, uint32_t ld, const void *qn, const void *kn, const void *cosv, const void *sinv,
+                          const void *rope_pos, const void *kv_pos, const void *seq_ids, const void *block_table, uint32_t bpr,
+                          void *qh, void *gate, void *k_pool, void *v_pool, uint32_t tokens, uint32_t q_heads, uint32_t kv_heads,
+                          uint32_t head_dim, uint32_t rot_dim, float eps, void *stream);
+int32_t wein_b200_mtp_cat(const void *tok, const void *embed, const void *hid, const void *hid_rows, const void *pre_e,
+                          const void *pre_h, void *cat, uint32_t rows, uint32_t hidden, float eps, void *stream);
+int32_t wein_b200_silu_mul_rows(const void *gu, uint32_t ld, void *out, uint32_t rows, uint32_t inter, void *stream);
 
 /* ArgmaxRowsOp::run (ops/mod.rs:1332-1367): total order (value desc, index asc); scratch = s*32 u64 words;
  * a row with no comparable element yields 0xFFFFFFFF, as the reference. */
@@ -226,6 +262,8 @@ typedef struct {
     uint32_t n_pages;        /* 16-token pages per KV pool */
     uint32_t state_f32;      /* recurrent state pool: 1 = f32, 0 = bf16 (the reference's pool) */
     uint32_t attn_seg_pages; /* pages per attention segment (0 = chosen from max_pos: 4 ... 128) */
+    uint32_t state_snapshots;/* 0: rounds of >= 3 positions log their state updates and materialise the accepted row once;
+                                1: every round writes one recurrent-state row per verify position (the reference's scheme) */
 } wein_b200_model_cfg;
 
 /* Weights stay caller-owned device memory for the life of the engine (bf16 unless noted; layouts as the safetensors
@@ -257,45 +295,102 @@ typedef struct {
 
 typedef struct wein_b200_engine wein_b200_engine;
 
-/* Allocates pools (recurrent / conv state rows, KV pages), scratch and tables.  The only entry that allocates. */
+/* Allocates pools (recurrent / conv state rows, KV pages), scratch and tables.  create, warm and the first call of a round
+ * shape (which captures its CUDA graph) are the only entries that allocate; every forward of an engine whose largest forward
+ * (max_seqs x (k_max+1) rows) exceeds 32 rows multiplies on the tensor-memory GEMM at every row count, smaller engines on
+ * the m <= 32 kernel, so that plain, draft and verify forwards of one engine sum in one order. */
 int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const wein_b200_weights *weights, wein_b200_engine **out);
 void wein_b200_engine_destroy(wein_b200_engine *e);
 uint64_t wein_b200_engine_device_bytes(const wein_b200_engine *e);
 
 /* Admission of a sequence into a slot: zeroes its state rows, installs its block-table row (host_pages: n_pages page
- * ids) and its sampling parameters (SampleParams of crates/wein-engine/src/protocol.rs:50-76; temp <= 0 = greedy). */
+ * ids) and its sampling parameters (SampleParams of crates/wein-engine/src/protocol.rs:50-76; temp <= 0 = greedy).  The slot's
+ * position limit becomes min(max_pos, 16 * n_pages): no round reads or writes a position at or past it (see the status bits). */
 int32_t wein_b200_engine_admit(wein_b200_engine *e, uint32_t slot, const uint32_t *host_pages, uint32_t n_pages, float temp,
                                uint32_t top_k, float top_p, uint64_t seed, void *stream);
 
+/* Per-request draft length (Qwen35Executor::set_spec, crates/wein-exec/src/qwen.rs:2604-2647): later rounds verify
+ * min(round k, k) drafts for this slot; 0 makes it a plain decode row inside a speculative round (the mixed batch of
+ * qwen.rs:5295-5361).  Admission resets it to "whatever the round drafts".  Stream-ordered. */
+int32_t wein_b200_engine_set_spec(wein_b200_engine *e, uint32_t slot, uint32_t k, void *stream);
+
+/* A sequence that does not start at position 0 (a prefix-cache hit: the reference restores KV pages and a recurrent-state
+ * snapshot from its radix cache, qwen.rs:3056-3100): after admit, the caller writes the first `position` tokens' K / V into
+ * the slot's pages and the state after them into row 2 * (k_max + 1) * slot of every "lin_state:<i>" / "conv_state:<i>" pool
+ * (wein_b200_engine_buffer), then names the position and the token to feed next.  The stashed hidden of the MTP head starts
+ * at zero.  Stream-ordered. */
+int32_t wein_b200_engine_resume(wein_b200_engine *e, uint32_t slot, uint32_t position, uint32_t pending_token, void *stream);
+
 /* Prefill: feeds host_lens[i] prompt tokens of slot host_slots[i] (tokens concatenated in host_tokens) through the verify
- * forward in chunks of k_max+1 positions, then emits each sequence's first token.  Not graph-captured; synchronises. */
+ * forward in chunks of k_max+1 positions starting at the slot's current position, then emits each sequence's next token.
+ * WEIN_B200_ERR_CAPACITY when a prompt does not fit below the slot's position limit.  Not graph-captured; synchronises. */
 int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, const uint32_t *host_tokens,
                                  const uint32_t *host_lens, void *stream);
 
 /* One round for the slots host_slots[0..n): draft k tokens with the MTP head (k = 0: plain decode step), verify the k+1
  * positions in one forward, accept on the device, commit (position, pending token, state row, hidden, token ring).
- * ctx_bound = an upper bound of (position + k + 1) over the batch (sizes the attention grid).  use_graph != 0 replays a
- * CUDA graph cached per (n, k, sampling mode, ctx bucket); bit 1 of use_graph forces the upload of the slot table even
- * when it is unchanged.  No host synchronisation unless the slot table changes. */
+ * ctx_bound = an upper bound of (position + k + 1) over the batch; it sizes the attention grid (an understated bound is
+ * flagged in the status word, never a memory error).  use_graph bit 0 replays a CUDA graph cached per (n, k, sampling mode,
+ * ctx bucket), captured on first use or by wein_b200_engine_warm; bit 1 forces the upload of the slot table even when it
+ * is unchanged.  No host synchronisation unless the slot table changes. */
 int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, uint32_t ctx_bound,
                                    uint32_t use_graph, void *stream);
 
+/* The draft phase alone (Qwen35Executor::spec_draft_batch, qwen.rs:2748-2853): k MTP forwards with the hidden chained on the
+ * device.  drafts_out (optional, DEVICE, [n, k] u32) receives the drafts; they also stay in the engine, with their
+ * distributions in sampled mode, for a following spec_verify with WEIN_B200_VERIFY_ENGINE_DRAFTS. */
+int32_t wein_b200_engine_draft(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, void *drafts_out,
+                               uint32_t use_graph, void *stream);
+
+/* Verify + accept + commit with the caller's drafts (Qwen35Executor::spec_verify / spec_commit_batch(&[(ReqId, Vec<u32>)]),
+ * qwen.rs:2261-2303).  DEVICE arrays: drafts [n, k] u32; n_drafts [n] (optional, ragged chains: row b verifies
+ * min(n_drafts[b], k, the slot's set_spec value) drafts); q_ids / q_probs [n, k, 64] and q_n [n, k] (optional, all three or
+ * none): the distributions the drafts were drawn from, as compact lists in the layout of wein_b200_topk_filter -- without
+ * them a sampled slot treats each draft as drawn from a point mass.  A draft id outside the vocabulary is rejected like any
+ * wrong draft. */
+#define WEIN_B200_VERIFY_GRAPH 1u          /* replay a CUDA graph (as use_graph of spec_step) */
+#define WEIN_B200_VERIFY_FORCE_SLOTS 2u    /* upload the slot table even when unchanged */
+#define WEIN_B200_VERIFY_DRY_RUN 4u        /* decide but commit nothing: slot state, token ring, counters and committed rows stay */
+#define WEIN_B200_VERIFY_ENGINE_DRAFTS 8u  /* use the drafts (and distributions) a preceding wein_b200_engine_draft left */
+int32_t wein_b200_engine_spec_verify(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, const void *drafts,
+                                     const void *n_drafts, const void *q_ids, const void *q_probs, const void *q_n,
+                                     uint32_t ctx_bound, uint32_t flags, void *stream);
+
+/* Captures and instantiates the graphs later calls with the same (n, k, sampling mode of the slots, ctx bucket) replay, so
+ * that those calls allocate nothing (the reference warms its graphs at open_graph, qwen.rs:1994-2034).  what: bit 0
+ * spec_step, bit 1 spec_verify, bit 2 spec_verify as a dry run, bit 3 engine_draft.  The slots must be admitted. */
+int32_t wein_b200_engine_warm(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, uint32_t ctx_bound,
+                              uint32_t what, void *stream);
+
 /* The readback of a round for the whole batch in one copy (the reference reads back its [B*P] argmax table once per step,
- * forward_batch_mixed, qwen.rs:3453-3703): host_out [n, 3 + k_max + 1] u32 = per batch row of the most recent spec_step the
- * accept length a, the position, the tokens emitted since admission, then the round's a + 1 tokens (other words 0xFFFFFFFF).
- * Synchronises the stream. */
+ * forward_batch_mixed, qwen.rs:3453-3703): host_out [n, 4 + k_max + 1] u32 = per batch row of the most recent round the
+ * accept length a, the position, the tokens emitted since admission, the round's a + 1 tokens (other words 0xFFFFFFFF; no
+ * token for a slot that sat the round out), then the slot's status word.  Synchronises the stream. */
 int32_t wein_b200_engine_read_round(wein_b200_engine *e, uint32_t *host_out, uint32_t host_words, void *stream);
 
 /* Synchronises the stream and reads a slot: the most recent min(cap, emitted) tokens (oldest first), the number of
- * tokens emitted since admission (host_n_tokens), the position, and the counters of
+ * tokens emitted since admission (host_n_tokens), the position, and the first three counters of
  * spec_stats() (crates/wein-exec/src/qwen.rs:4257-4259): rounds, drafts, accepted. */
 int32_t wein_b200_engine_read(wein_b200_engine *e, uint32_t slot, uint32_t *host_tokens, uint32_t cap, uint32_t *host_n_tokens,
                               uint32_t *host_pos, uint64_t *host_stats3, void *stream);
 
+/* All speculation counters of a slot since admission (spec_stats / spec_k_stats, qwen.rs:4257-4259, :2670):
+ * host_stats[WEIN_B200_STATS_WORDS] = rounds, drafts, accepted, fallbacks (rounds cut or refused at the position limit),
+ * draft-length switches, rounds by draft count [8], rounds by accept length [9], last draft count, spare.  Synchronises. */
+#define WEIN_B200_STATS_WORDS 24
+int32_t wein_b200_engine_stats(wein_b200_engine *e, uint32_t slot, uint64_t *host_stats, void *stream);
+
+/* Status word of a slot (WEIN_B200_STATUS_*); clear != 0 resets it after the read.  Synchronises the stream. */
+int32_t wein_b200_engine_status(wein_b200_engine *e, uint32_t slot, uint32_t *host_status, uint32_t clear, void *stream);
+
+/* Phase timers (spec_timing_ms, qwen.rs:4277-4279): while on, rounds run without a graph record device events around the
+ * draft phase, the verify forward and acceptance + commit; host_ms3 (optional) receives the totals in milliseconds. */
+int32_t wein_b200_engine_timing(wein_b200_engine *e, uint32_t on, double *host_ms3);
+
 /* Test / profiling access to engine-owned device buffers by name ("logits", "x", "accept_len", "state_row", "lin_state:<i>",
  * "k_pool:<i>", ...): returns the device pointer and its size in bytes, or NULL. */
 void *wein_b200_engine_buffer(wein_b200_engine *e, const char *name, uint64_t *bytes);
-/* Kernel launches recorded by the most recent spec_step (eager) or captured in the graph it replayed. */
+/* Kernel launches recorded by the most recent round (eager) or captured in the graph it replayed. */
 uint32_t wein_b200_engine_last_launches(const wein_b200_engine *e);
 
 #ifdef __cplusplus

@@ -2,7 +2,7 @@
 
     python -m inferulm_b200.build            # build if sources are newer than the library
     python -m inferulm_b200.build --force
-    python -m inferulm_b200.build --trace    # diagnostic twin libwein_b200_trace.so with kernel-start time stamps (see trace.py)
+    python -m inferulm_b200.build -v         # with ptxas resource usage per kernel
 """
 import os
 import subprocess
@@ -25,7 +25,7 @@ SOURCES = [
     ("fused_glue.cu", ["-fmad=false"]),
     ("attn.cu", []),
     ("gemm.cu", []),
-    ("gemm_stream.cu", []),
+    ("gemm_umma.cu", []),
     ("engine.cu", []),
 ]
 
@@ -42,12 +42,8 @@ def _headers():
         os.path.join(os.path.dirname(HERE), "include", "wein_b200.h")]
 
 
-LIB_TRACE = os.path.join(HERE, "libwein_b200_trace.so")
-
-
-def build(force=False, verbose=False, trace=False):
-    lib, objdir, defs = (LIB_TRACE, OBJ + "_trace", ["-DWB_TRACE"]) if trace else (LIB, OBJ, [])
-    return _build(lib, objdir, defs, force, verbose)
+def build(force=False, verbose=False):
+    return _build(LIB, OBJ, [], force, verbose)
 
 
 def _build(LIB, OBJ, defs, force, verbose):
@@ -72,7 +68,7 @@ def _build(LIB, OBJ, defs, force, verbose):
         if verbose and out:
             print(out)
     if changed or not os.path.exists(LIB):
-        cmd = [_nvcc()] + ARCH + ["-shared", "-o", LIB] + objs + ["-lcublasLt", "-lcublas"]
+        cmd = [_nvcc()] + ARCH + ["-shared", "-o", LIB] + objs
         r = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
         if r.returncode != 0:
             raise RuntimeError("link failed:\n" + r.stdout)
@@ -80,4 +76,4 @@ def _build(LIB, OBJ, defs, force, verbose):
 
 
 if __name__ == "__main__":
-    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv, trace="--trace" in sys.argv))
+    print(build(force="--force" in sys.argv, verbose="-v" in sys.argv))

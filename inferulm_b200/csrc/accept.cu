@@ -541,4 +541,3 @@ int32_t wein_b200_accept_sampled(const void *drafts, const void *n_drafts, const
 
 }  // extern "C"
 
-WB_TRACE_SETTER(accept)   // diagnostic builds only (see common.cuh); expands to nothing otherwise

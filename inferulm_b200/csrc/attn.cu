@@ -52,6 +52,8 @@ struct AttnParams {
     float *part_o, *part_ml;  // [span][kvh][seg][32][HD] and [...][32][2]
     float scale_log2;
     uint32_t bpr, q_heads, kv_heads, n_spans, seg_pages, max_segs, n_mtiles;
+    uint32_t *status;         // optional, indexed by sequence id: WB_STATUS_CTX_BOUND is OR-ed in when the caller's context bound
+                              // was too small for a row (the row is then reduced over the segments the grid covers only)
 };
 
 // byte offset of 16-byte chunk `ch` of row `r` in a [rows][HD] bf16 tile, XOR-swizzled over the row's low 3 bits
@@ -84,7 +86,7 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
     const uint32_t he = P.kv_heads * HD;
     uint32_t L = 0;  // keys any row of the chain may see
     for (uint32_t p = 0; p < cnt; p++) L = max(L, P.positions[t0 + p] + 1);
-    const uint32_t pages = (L + ATT_PAGE - 1) / ATT_PAGE;
+    const uint32_t pages = min((L + ATT_PAGE - 1) / ATT_PAGE, P.bpr);   // never past the block-table row
     const uint32_t pg0 = seg * P.seg_pages, pg1 = min(pages, pg0 + P.seg_pages);
     if (pg0 >= pages) return;  // the combine kernel only reads the segments below ceil(pages / seg_pages)
 
@@ -250,7 +252,13 @@ __global__ void attn_combine_kernel(const AttnParams P) {
     const uint32_t d4 = threadIdx.x * 4;
     uint32_t L = 0;
     for (uint32_t p = 0; p < cnt; p++) L = max(L, P.positions[t0 + p] + 1);
-    const uint32_t nseg = ((L + ATT_PAGE - 1) / ATT_PAGE + P.seg_pages - 1) / P.seg_pages;
+    uint32_t nseg = (min((L + ATT_PAGE - 1) / ATT_PAGE, P.bpr) + P.seg_pages - 1) / P.seg_pages;
+    if (nseg > P.max_segs) {
+        // the grid was sized from a context bound below this row's position: segments past it were never computed.  Merge
+        // what exists (never read a slot nobody wrote) and tell the host.
+        nseg = P.max_segs;
+        if (P.status && threadIdx.x == 0 && row == 0 && kvh == 0) atomicOr(&P.status[P.seq_ids[t0]], WB_STATUS_CTX_BOUND);
+    }
     size_t p0 = ((size_t)span * P.kv_heads + kvh) * P.max_segs * 32 + row;
     float M = -INFINITY;
     for (uint32_t s = 0; s < nseg; s++) M = fmaxf(M, P.part_ml[(p0 + (size_t)s * 32) * 2]);
@@ -276,20 +284,31 @@ __global__ void attn_combine_kernel(const AttnParams P) {
 }
 
 template <int HD>
-static int32_t attn_launch(const AttnParams &p, cudaStream_t st) {
+static size_t attn_smem_bytes() {
     size_t smem = 16 * HD * 2 + 4 * ATT_STAGES * 2 * (size_t)ATT_PAGE * HD * 2;
     size_t merge = 16 * HD * 2 + 4 * 16 * (size_t)(HD + 4) * 4;
-    if (smem < merge) smem = merge;
-    static bool attr_done = false;
-    if (!attr_done) {
-        if (cudaFuncSetAttribute(attn_verify_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
-            wb_set_error("attn_verify: cannot reserve %zu bytes of shared memory", smem);
-            return WB_ERR_CUDA;
-        }
-        attr_done = true;
-    }
+    return smem < merge ? merge : smem;
+}
+// The shared-memory opt-in is a per-device function attribute: one flag per device ordinal, set once (writing it twice from
+// two threads stores the same value).
+static bool g_attn_ready[3][64];
+template <int HD>
+static int32_t attn_prepare(int which) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { wb_set_error("attn: cudaGetDevice failed or device ordinal >= 64"); return WB_ERR_CUDA; }
+    if (g_attn_ready[which][dev]) return WB_OK;
+    const size_t smem = attn_smem_bytes<HD>();
+    cudaError_t e = cudaFuncSetAttribute(attn_verify_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { wb_set_error("attn: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return WB_ERR_CUDA; }
+    g_attn_ready[which][dev] = true;
+    return WB_OK;
+}
+
+template <int HD>
+static int32_t attn_launch(const AttnParams &p, int which, cudaStream_t st) {
+    if (int32_t rc = attn_prepare<HD>(which)) return rc;
     dim3 grid(p.max_segs, p.kv_heads, p.n_spans * p.n_mtiles);
-    WB_LAUNCH((attn_verify_kernel<HD>), grid, 128, smem, st, p);
+    WB_LAUNCH((attn_verify_kernel<HD>), grid, 128, attn_smem_bytes<HD>(), st, p);
     WB_LAUNCH_CHECK();
     dim3 g2(16 * p.n_mtiles, p.kv_heads, p.n_spans);
     WB_LAUNCH((attn_combine_kernel<HD>), g2, HD / 4, 0, st, p);
@@ -298,19 +317,12 @@ static int32_t attn_launch(const AttnParams &p, cudaStream_t st) {
 }
 
 int32_t wb_attn_init(uint32_t head_dim) {
-    AttnParams p{};
-    p.n_spans = 0;
-    (void)p;
-    size_t smem;
-    cudaError_t e = cudaSuccess;
-    auto bytes = [](size_t hd) { size_t a = 16 * hd * 2 + 4 * ATT_STAGES * 2 * (size_t)ATT_PAGE * hd * 2, b = 16 * hd * 2 + 4 * 16 * (hd + 4) * 4; return a > b ? a : b; };
-    smem = bytes(head_dim);
-    if (head_dim == 256) e = cudaFuncSetAttribute(attn_verify_kernel<256>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    else if (head_dim == 128) e = cudaFuncSetAttribute(attn_verify_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    else if (head_dim == 64) e = cudaFuncSetAttribute(attn_verify_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    else { wb_set_error("attn: head_dim %u not built", head_dim); return WB_ERR_SHAPE; }
-    if (e != cudaSuccess) { wb_set_error("attn: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return WB_ERR_CUDA; }
-    return WB_OK;
+    switch (head_dim) {
+        case 256: return attn_prepare<256>(0);
+        case 128: return attn_prepare<128>(1);
+        case 64: return attn_prepare<64>(2);
+        default: wb_set_error("attn: head_dim %u not built", head_dim); return WB_ERR_SHAPE;
+    }
 }
 
 extern "C" uint64_t wein_b200_attn_scratch_bytes(uint32_t n_spans, uint32_t kv_heads, uint32_t head_dim, uint32_t max_segs) {
@@ -324,7 +336,7 @@ int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, 
                        const void *positions, const void *row_start, const void *row_count, const void *gate, void *out,
                        float q_scale, uint32_t bpr, uint32_t block_size, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
                        uint32_t n_spans, uint32_t max_count, uint32_t max_ctx, uint32_t seg_pages, void *scratch,
-                       uint64_t scratch_bytes, cudaStream_t st) {
+                       uint64_t scratch_bytes, uint32_t *status, cudaStream_t st) {
     WB_CHECK_ARG(q && k_cache && v_cache && block_table && seq_ids && positions && out && scratch, "attn_verify: null pointer");
     if (block_size != ATT_PAGE) { wb_set_error("attn_verify: built for 16-token pages, got %u", block_size); return WB_ERR_SHAPE; }
     WB_CHECK_ARG(kv_heads > 0 && q_heads % kv_heads == 0, "attn_verify: q_heads %u not a multiple of kv_heads %u", q_heads, kv_heads);
@@ -344,11 +356,11 @@ int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, 
     p.part_o = (float *)scratch;
     p.part_ml = (float *)scratch + (size_t)n_spans * kv_heads * p.max_segs * 32 * head_dim;
     p.scale_log2 = q_scale * 1.4426950408889634f;
-    p.bpr = bpr; p.q_heads = q_heads; p.kv_heads = kv_heads; p.n_spans = n_spans;
+    p.bpr = bpr; p.q_heads = q_heads; p.kv_heads = kv_heads; p.n_spans = n_spans; p.status = status;
     switch (head_dim) {
-        case 256: return attn_launch<256>(p, st);
-        case 128: return attn_launch<128>(p, st);
-        case 64: return attn_launch<64>(p, st);
+        case 256: return attn_launch<256>(p, 0, st);
+        case 128: return attn_launch<128>(p, 1, st);
+        case 64: return attn_launch<64>(p, 2, st);
         default: wb_set_error("attn_verify: head_dim %u not built (64, 128, 256)", head_dim); return WB_ERR_SHAPE;
     }
 }
@@ -362,19 +374,18 @@ int32_t wein_b200_paged_attn(const void *q, const void *k_cache, const void *v_c
                              uint32_t kv_heads, uint32_t head_dim, uint32_t tokens, void *scratch, uint64_t scratch_bytes, void *stream) {
     uint32_t seg = (bpr + 15) / 16;  // at most 16 segments per row
     return wb_attn_verify(q, k_cache, v_cache, block_table, seq_ids, positions, nullptr, nullptr, nullptr, out, q_scale, bpr, block_size,
-                          q_heads, kv_heads, head_dim, tokens, 1, bpr * ATT_PAGE, seg, scratch, scratch_bytes, (cudaStream_t)stream);
+                          q_heads, kv_heads, head_dim, tokens, 1, bpr * ATT_PAGE, seg, scratch, scratch_bytes, nullptr, (cudaStream_t)stream);
 }
 
 int32_t wein_b200_attn_verify(const void *q, const void *k_cache, const void *v_cache, const void *block_table, const void *seq_ids,
                               const void *positions, const void *row_start, const void *row_count, const void *gate, void *out,
                               float q_scale, uint32_t bpr, uint32_t block_size, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
                               uint32_t n_spans, uint32_t max_count, uint32_t max_ctx, uint32_t seg_pages, void *scratch,
-                              uint64_t scratch_bytes, void *stream) {
+                              uint64_t scratch_bytes, void *status, void *stream) {
     WB_CHECK_ARG(row_start && row_count, "attn_verify: span tables are required");
     return wb_attn_verify(q, k_cache, v_cache, block_table, seq_ids, positions, row_start, row_count, gate, out, q_scale, bpr, block_size,
-                          q_heads, kv_heads, head_dim, n_spans, max_count, max_ctx, seg_pages, scratch, scratch_bytes, (cudaStream_t)stream);
+                          q_heads, kv_heads, head_dim, n_spans, max_count, max_ctx, seg_pages, scratch, scratch_bytes, (uint32_t *)status, (cudaStream_t)stream);
 }
 
 }  // extern "C"
 
-WB_TRACE_SETTER(attn)   // diagnostic builds only (see common.cuh); expands to nothing otherwise

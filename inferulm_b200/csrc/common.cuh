@@ -16,6 +16,12 @@
 #define WB_ERR_CUDA (-3)     // a CUDA runtime call failed (see wein_b200_last_error)
 #define WB_ERR_CAPACITY (-4) // caller-provided scratch too small
 
+// Bits of a device status word (one per sequence slot of an engine; OR-ed in by kernels, never cleared by them)
+#define WB_STATUS_POS_LIMIT 1u   // the round was refused for this slot: position + 1 would pass the slot's position limit
+#define WB_STATUS_K_CLAMPED 2u   // fewer drafts than asked were verified because the chain would have passed the position limit
+#define WB_STATUS_CTX_BOUND 4u   // the caller's context bound was below position + chain length: attention ignored later segments
+#define WB_STATUS_SAMPLER 8u     // the sampler met an invalid parameter (top_k = 0 with temperature > 0)
+
 typedef uint16_t bf16_t;
 
 __host__ __device__ __forceinline__ float bf2f(bf16_t h) {
@@ -123,51 +129,18 @@ __device__ __forceinline__ float block_sum_tree(float v, float *smem /* >= 33 fl
 // Because a kernel's lifetime now overlaps its producer's, data written by earlier kernels must never be read through the
 // non-coherent path: no __ldg and no `const __restrict__` on such pointers (only weights use ld.global.nc).
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;"); }
-// Identity of a call site for the diagnostic build: hash of the source file's base name, and the line
-__host__ __device__ constexpr unsigned int wb_file_id(const char *path) {
-    unsigned int h = 2166136261u;
-    const char *base = path;
-    for (const char *p = path; *p; p++) if (*p == '/') base = p + 1;
-    for (const char *p = base; *p; p++) h = (h ^ (unsigned char)*p) * 16777619u;
-    return h;
-}
-#ifdef WB_TRACE
-// Diagnostic build (python -m inferulm_b200.build --trace): block 0 / thread 0 of every kernel records the global timer when
-// its dependency wait returns, with the call site of the wait (which identifies the kernel), in the order kernels become
-// runnable.  In a captured round every kernel waits for its predecessor, so the difference between consecutive stamps is
-// what each kernel adds to the round's critical path (inferulm_b200/trace.py prints it).  The buffer pointer is a
-// per-translation-unit copy set through WB_TRACE_SETTER.
-static __device__ unsigned long long *wb_trace_buf;   // [0] = count, then (time, file id << 32 | line) pairs
-__device__ __forceinline__ void pdl_wait_at(unsigned int file_id, unsigned int line) {
-    asm volatile("griddepcontrol.wait;" ::: "memory");
-    if ((threadIdx.x | blockIdx.x | blockIdx.y | blockIdx.z) == 0 && wb_trace_buf) {
-        unsigned long long t;
-        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-        const unsigned int i = atomicAdd(reinterpret_cast<unsigned int *>(wb_trace_buf), 1u);
-        if (i < 30000u) { wb_trace_buf[1 + 2 * i] = t; wb_trace_buf[2 + 2 * i] = ((unsigned long long)file_id << 32) | line; }
-    }
-}
-#define WB_TRACE_SETTER(name) \
-    extern "C" void wb_trace_set_##name(unsigned long long *p) { cudaMemcpyToSymbol(wb_trace_buf, &p, sizeof p); }
-#else
-__device__ __forceinline__ void pdl_wait_at(unsigned int, unsigned int) { asm volatile("griddepcontrol.wait;" ::: "memory"); }
-#define WB_TRACE_SETTER(name)
-#endif
-#define pdl_wait() do { constexpr unsigned int wb_fid_ = wb_file_id(__FILE__); pdl_wait_at(wb_fid_, __LINE__); } while (0)
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 #define PDL_ENTRY() do { pdl_trigger(); pdl_wait(); } while (0)
 
-// Host-side launch helper: every kernel goes through cudaLaunchKernelEx so the attribute can be switched globally.
-extern bool g_wb_pdl;
-void wb_prepare_kernel(const void *kern);  // once per kernel: the same shared-memory carve-out preference for every kernel of the library
+// Host-side launch helper: every kernel goes through cudaLaunchKernelEx with the programmatic-serialization attribute.
 template <typename... KArgs, typename... Args>
 static inline cudaError_t wb_launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args &&...args) {
-    wb_prepare_kernel(reinterpret_cast<const void *>(kern));
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid; cfg.blockDim = block; cfg.dynamicSmemBytes = smem; cfg.stream = st;
     cudaLaunchAttribute at[1];
     at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = at; cfg.numAttrs = g_wb_pdl ? 1 : 0;
+    cfg.attrs = at; cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, kern, static_cast<KArgs>(args)...);
 }
 #define WB_LAUNCH(kern, grid, block, smem, st, ...) wb_launch_k(kern, grid, block, smem, st, __VA_ARGS__)

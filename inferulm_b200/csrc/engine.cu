@@ -17,7 +17,6 @@
 #include <stdio.h>
 #include <string.h>
 #include <map>
-#include <set>
 #include <string>
 #include <tuple>
 #include <vector>
@@ -43,6 +42,8 @@ int32_t wein_b200_add_norm_zc(const void *, const void *, const void *, void *, 
     } while (0)
 
 #define RING_CAP 8192u
+#define STATS_WORDS 24u   // per slot: rounds, drafts, accepted, fallbacks, k switches, rounds by draft count [8], rounds by accept length [9], last draft count, spare
+#define DEAD_ROW 0xffffffffu   // position of a batch row that belongs to no live chain position this round
 
 struct wein_b200_engine {
     wein_b200_model_cfg cfg;
@@ -57,6 +58,7 @@ struct wein_b200_engine {
     float **d_log_ptrs = nullptr;
     // per-slot device state
     uint32_t *d_pos, *d_pending, *d_state_row, *d_bank, *d_out_count, *d_top_k, *d_ring, *d_block_table;
+    uint32_t *d_limit, *d_status, *d_kreq;   // per slot: position limit (admitted pages), status bits, draft length asked for
     uint64_t *d_round, *d_seed, *d_stats;
     float *d_temp, *d_top_p;
     bf16_t *d_hid;
@@ -64,6 +66,7 @@ struct wein_b200_engine {
     uint32_t *d_slots, *d_tok, *d_pos_rows, *d_seq_rows, *d_row_start, *d_row_count, *d_in_row, *d_out_base, *d_lg_rows, *d_iota, *d_ones;
     uint32_t *d_cnt_in, *d_tok_in, *d_last_in, *d_first_tok, *d_lg_of;
     uint32_t *d_drafts, *d_accept_len, *d_out_tokens, *d_target;
+    uint32_t *d_nd, *d_nd_in;           // per batch row: drafts verified this round; the caller's draft counts (spec_verify)
     uint32_t *d_mtp_tok, *d_mtp_rope, *d_mtp_kvpos;
     // activations
     bf16_t *x, *n1, *h2, *n2, *o, *proj, *qkvc, *core, *normed, *qh, *gate, *attn, *gu, *m, *d, *logits, *lg_in, *cat;
@@ -74,18 +77,21 @@ struct wein_b200_engine {
     float *p_probs, *q_probs;
     // host mirrors
     std::vector<float> h_temp;
+    std::vector<uint32_t> h_limit;      // host mirror of d_limit
+    uint32_t gemm_path = WB_GEMM_AUTO;  // WB_GEMM_TC when a forward of this engine can exceed 32 rows (one kernel for every row count)
+    bool snapshots = false;             // true: a state snapshot per verify position in every round (no update records)
+    bool timing = false;                // eager rounds record phase events (draft / forward / finish)
+    cudaEvent_t ev[4] = {nullptr, nullptr, nullptr, nullptr};
+    bool ev_pending = false;
+    double ms_phase[3] = {0.0, 0.0, 0.0};
     std::vector<uint32_t> h_slots_cached;
     uint32_t *h_stage = nullptr;  // pinned
     size_t h_stage_words = 0;
-    std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint32_t, uint32_t>, cudaGraphExec_t> graphs;
+    std::map<std::tuple<uint32_t, uint32_t, uint32_t, uint32_t, uint32_t, uint32_t>, std::pair<cudaGraphExec_t, uint32_t>> graphs;
     uint32_t launches = 0, last_launches = 0;
     uint32_t last_n = 0, last_P = 0;     // shape of the most recent round (for read_round)
     uint32_t *d_pack = nullptr, *h_pack = nullptr;   // per-round readback, device and pinned host: [max_seqs, 3 + P]
-    // weight matrices in the order a round multiplies them (for the next-weights L2 prefetch); empty = no prefetch
-    std::vector<std::pair<const void *, uint64_t>> chain;
-    size_t chain_pos = 0;
     std::map<std::string, std::pair<void *, uint64_t>> named;
-    std::set<uint32_t> lt_tuned;   // row counts m > 32 whose library GEMM algorithms have been chosen by timing
 };
 typedef wein_b200_engine Engine;
 
@@ -106,7 +112,7 @@ static int32_t dalloc(Engine *e, T **p, size_t n, const char *name, bool zero = 
 
 // ------------------------------------------------------------------------------------------------ table kernels
 struct SlotState {
-    uint32_t *pos, *pending, *state_row, *bank, *out_count, *ring;
+    uint32_t *pos, *pending, *state_row, *bank, *out_count, *ring, *limit, *status, *kreq;
     uint64_t *round, *stats;
     bf16_t *hid;
 };
@@ -118,35 +124,58 @@ __device__ __forceinline__ void copy_row(bf16_t *dst, const bf16_t *src, uint32_
     for (uint32_t i = threadIdx.x; i < H / 8; i += blockDim.x) d[i] = s[i];
 }
 
-// Rows of a speculative round: batch row b = slot slots[b]; chain row j feeds the pending token (j = 0) or draft j-1.
-__global__ void verify_prep_kernel(const uint32_t *slots, SlotState S, const uint32_t *drafts, uint32_t k_max,
-                                   uint32_t n, uint32_t P, uint32_t rows_per_slot, uint32_t bankrows, uint32_t *tok, uint32_t *pos_rows,
-                                   uint32_t *seq_rows, uint32_t *row_start, uint32_t *row_count, uint32_t *in_row, uint32_t *out_base,
-                                   uint32_t *lg_rows) {
+// Rows of a speculative round: batch row b = slot slots[b] owns rows b*P .. b*P+P-1; its chain takes the first nd+1 of them
+// (the pending token, then drafts 0..nd-1), the others are dead rows (token 0, position DEAD_ROW: they are multiplied like
+// any row, write no KV and belong to no span).  nd = min(round k, the slot's own draft length, the caller's count) and is cut
+// further so that the chain stays below the slot's position limit (the reference cuts k to max_pos - (start + 1) and falls
+// back to a plain step, qwen.rs:2771-2777); a slot already at its limit sits the round out (span of 0 rows) and gets
+// WB_STATUS_POS_LIMIT: nothing is read or written past the pages it was admitted with.
+__global__ void verify_prep_kernel(const uint32_t *slots, SlotState S, const uint32_t *drafts, uint32_t k_max, const uint32_t *nd_in,
+                                   uint32_t n, uint32_t P, uint32_t vocab, uint32_t rows_per_slot, uint32_t bankrows, uint32_t *tok,
+                                   uint32_t *pos_rows, uint32_t *seq_rows, uint32_t *row_start, uint32_t *row_count, uint32_t *in_row,
+                                   uint32_t *out_base, uint32_t *lg_rows, uint32_t *nd_out) {
     PDL_ENTRY();
     uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n) return;
-    uint32_t slot = slots[b], p0 = S.pos[slot];
+    const uint32_t slot = slots[b], p0 = S.pos[slot], lim = S.limit[slot];
+    uint32_t nd = min(P - 1, S.kreq[slot]);
+    if (nd_in) nd = min(nd, nd_in[b]);
+    uint32_t cnt;
+    if (p0 + 1 > lim) { cnt = 0; nd = 0; atomicOr(&S.status[slot], WB_STATUS_POS_LIMIT); }
+    else {
+        if (p0 + nd + 1 > lim) { nd = lim - p0 - 1; atomicOr(&S.status[slot], WB_STATUS_K_CLAMPED); }
+        cnt = nd + 1;
+    }
     for (uint32_t j = 0; j < P; j++) {
-        uint32_t r = b * P + j;
-        tok[r] = j == 0 ? S.pending[slot] : drafts[b * k_max + j - 1];
-        pos_rows[r] = p0 + j;
+        const uint32_t r = b * P + j;
+        uint32_t t = 0;
+        if (j < cnt) t = j == 0 ? S.pending[slot] : drafts[b * k_max + j - 1];
+        tok[r] = t < vocab ? t : 0;    // a draft outside the vocabulary can never be accepted; the forward must not index with it
+        pos_rows[r] = j < cnt ? p0 + j : DEAD_ROW;
         seq_rows[r] = slot;
         lg_rows[r] = r;
     }
     row_start[b] = b * P;
-    row_count[b] = P;
+    row_count[b] = cnt;
     in_row[b] = S.state_row[slot];
     out_base[b] = slot * rows_per_slot + (S.bank[slot] ^ 1u) * bankrows;
+    nd_out[b] = nd;
 }
 
 // Commit of a round (spec_finish, qwen.rs:2433-2460): emitted tokens to the slot's ring, position += a+1, pending =
-// bonus token, state_row = snapshot a of this round's bank, hidden of chain row a stashed for the next draft.
-__global__ void commit_kernel(const uint32_t *slots, SlotState S, const uint32_t *accept_len,
-                              const uint32_t *out_tokens, const uint32_t *out_base, const bf16_t *x,
+// bonus token, state_row = snapshot a of this round's bank, hidden of chain row a stashed for the next draft; the counters
+// of spec_stats() / spec_k_stats() (qwen.rs:4257-4259, :2670).  A slot that sat the round out keeps everything.
+__global__ void commit_kernel(const uint32_t *slots, SlotState S, const uint32_t *accept_len, const uint32_t *row_count,
+                              const uint32_t *nd_row, const uint32_t *out_tokens, const uint32_t *out_base, const bf16_t *x,
                               uint32_t P, uint32_t k, uint32_t H) {
     PDL_ENTRY();
-    uint32_t b = blockIdx.x, slot = slots[b], a = accept_len[b];
+    const uint32_t b = blockIdx.x, slot = slots[b];
+    uint64_t *st = S.stats + (size_t)slot * STATS_WORDS;
+    if (row_count[b] == 0) {
+        if (threadIdx.x == 0) st[3] += 1;
+        return;
+    }
+    const uint32_t nd = nd_row[b], a = min(accept_len[b], nd);
     copy_row(S.hid + (size_t)slot * H, x + (size_t)(b * P + a) * H, H);
     if (threadIdx.x == 0) {
         uint32_t oc = S.out_count[slot];
@@ -157,24 +186,28 @@ __global__ void commit_kernel(const uint32_t *slots, SlotState S, const uint32_t
         S.state_row[slot] = out_base[b] + a;
         S.bank[slot] ^= 1u;
         S.round[slot] += 1;
-        S.stats[slot * 3 + 0] += 1;
-        S.stats[slot * 3 + 1] += k;
-        S.stats[slot * 3 + 2] += a;
+        if (st[0] != 0 && st[22] != nd) st[4] += 1;                 // the chain length changed against the slot's previous round
+        st[0] += 1; st[1] += nd; st[2] += a;
+        if (nd < min(k, S.kreq[slot])) st[3] += 1;                  // fewer drafts than asked: cut at the position limit
+        st[5 + min(nd, 7u)] += 1;
+        st[13 + min(a, 8u)] += 1;
+        st[22] = nd;
     }
 }
 
 // What the host reads back after a round, packed for one copy: per batch row [accept length, position, tokens emitted since
-// admission, the round's a+1 tokens (padded to P words)].  Stands in for the reference's per-step readback of its u32 [B*P]
+// admission, the round's a+1 tokens (padded to k_max+1 words; none for a slot that sat the round out), the slot's status word].  Stands in for the reference's per-step readback of its u32 [B*P]
 // argmax table (forward_batch_mixed, qwen.rs:3453-3703).
-__global__ void round_pack_kernel(const uint32_t *slots, SlotState S, const uint32_t *accept_len, const uint32_t *out_tokens,
-                                  uint32_t n, uint32_t P, uint32_t P_stride, uint32_t *out) {
+__global__ void round_pack_kernel(const uint32_t *slots, SlotState S, const uint32_t *accept_len, const uint32_t *row_count,
+                                  const uint32_t *out_tokens, uint32_t n, uint32_t P, uint32_t P_stride, uint32_t *out) {
     PDL_ENTRY();
     uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n) return;
-    const uint32_t slot = slots[b], a = min(accept_len[b], P - 1);
-    uint32_t *o = out + (size_t)b * (3 + P_stride);
+    const uint32_t slot = slots[b], live = row_count[b] != 0, a = live ? min(accept_len[b], P - 1) : 0u;
+    uint32_t *o = out + (size_t)b * (4 + P_stride);
     o[0] = a; o[1] = S.pos[slot]; o[2] = S.out_count[slot];
-    for (uint32_t j = 0; j < P_stride; j++) o[3 + j] = (j <= a && j < P) ? out_tokens[b * P + j] : 0xffffffffu;
+    for (uint32_t j = 0; j < P_stride; j++) o[3 + j] = (live && j <= a && j < P) ? out_tokens[b * P + j] : 0xffffffffu;
+    o[3 + P_stride] = S.status[slot];
 }
 
 // Prefill chunk tables: span b holds cnt[b] prompt tokens of slot slots[b] (tokens concatenated in tok_in).
@@ -220,20 +253,42 @@ __global__ void prefill_commit_kernel(const uint32_t *slots, SlotState S, const 
 }
 // Inputs of draft step i: token = pending (i = 0) or the previous draft; rotary position absolute, KV slot chain-local.
 __global__ void mtp_prep_kernel(const uint32_t *slots, SlotState S, const uint32_t *drafts, uint32_t k_max,
-                                uint32_t n, uint32_t i, uint32_t *tok, uint32_t *rope_pos, uint32_t *kv_pos) {
+                                uint32_t n, uint32_t i, uint32_t vocab, uint32_t max_pos, uint32_t *tok, uint32_t *rope_pos, uint32_t *kv_pos) {
     PDL_ENTRY();
     uint32_t b = blockIdx.x * blockDim.x + threadIdx.x;
     if (b >= n) return;
     uint32_t slot = slots[b];
-    tok[b] = i == 0 ? S.pending[slot] : drafts[b * k_max + i - 1];
-    rope_pos[b] = S.pos[slot] + i;
+    const uint32_t t = i == 0 ? S.pending[slot] : drafts[b * k_max + i - 1];
+    tok[b] = t < vocab ? t : 0;
+    rope_pos[b] = min(S.pos[slot] + i, max_pos - 1);   // a draft past the position limit is dropped by the verify tables anyway
     kv_pos[b] = i;
 }
-__global__ void slot_init_kernel(SlotState S, uint32_t slot, uint32_t row0, float *temp, uint32_t *top_k, float *top_p, uint64_t *seed,
-                                 float t, uint32_t k, float p, uint64_t sd) {
+// Caller-supplied drafts of a verify-only round (spec_verify): drafts [n, k], optional per-row counts, optional draft
+// distributions as compact lists [n, k, 64]; without lists a draft counts as drawn from a point mass (q = 1 on the draft).
+__global__ void import_drafts_kernel(const uint32_t *src, const uint32_t *src_nd, const uint32_t *src_q_ids, const float *src_q_probs,
+                                     const uint32_t *src_q_n, uint32_t n, uint32_t k, uint32_t k_max, uint32_t *drafts, uint32_t *nd_in,
+                                     uint32_t *q_ids, float *q_probs, uint32_t *q_n) {
+    PDL_ENTRY();
+    const uint32_t b = blockIdx.x, j = blockIdx.y, i = threadIdx.x;   // 64 threads
+    const uint32_t d = src[b * k + j];
+    const size_t di = (size_t)b * k_max + j, si = (size_t)b * k + j;
+    if (i == 0) {
+        drafts[di] = d;
+        if (j == 0) nd_in[b] = src_nd ? min(src_nd[b], k) : k;
+        q_n[di] = src_q_ids ? min(src_q_n[si], 64u) : 1u;
+    }
+    if (src_q_ids) { q_ids[di * 64 + i] = src_q_ids[si * 64 + i]; q_probs[di * 64 + i] = src_q_probs[si * 64 + i]; }
+    else { q_ids[di * 64 + i] = i == 0 ? d : 0xffffffffu; q_probs[di * 64 + i] = i == 0 ? 1.0f : 0.0f; }
+}
+__global__ void resume_kernel(SlotState S, uint32_t slot, uint32_t position, uint32_t pending) { PDL_ENTRY(); S.pos[slot] = position; S.pending[slot] = pending; }
+__global__ void set_kreq_kernel(uint32_t *kreq, uint32_t slot, uint32_t k) { PDL_ENTRY(); kreq[slot] = k; }
+__global__ void clear_status_kernel(uint32_t *status, uint32_t slot) { PDL_ENTRY(); status[slot] = 0; }
+__global__ void slot_init_kernel(SlotState S, uint32_t slot, uint32_t row0, uint32_t limit, float *temp, uint32_t *top_k, float *top_p,
+                                 uint64_t *seed, float t, uint32_t k, float p, uint64_t sd) {
     PDL_ENTRY();
     S.pos[slot] = 0; S.pending[slot] = 0; S.state_row[slot] = row0; S.bank[slot] = 0; S.out_count[slot] = 0; S.round[slot] = 0;
-    S.stats[slot * 3] = S.stats[slot * 3 + 1] = S.stats[slot * 3 + 2] = 0;
+    S.limit[slot] = limit; S.status[slot] = 0; S.kreq[slot] = 0xffffffffu;
+    for (uint32_t i = 0; i < STATS_WORDS; i++) S.stats[(size_t)slot * STATS_WORDS + i] = 0;
     temp[slot] = t; top_k[slot] = k; top_p[slot] = p; seed[slot] = sd;
 }
 
@@ -241,6 +296,7 @@ static SlotState slot_state(Engine *e) {
     SlotState s;
     s.pos = e->d_pos; s.pending = e->d_pending; s.state_row = e->d_state_row; s.bank = e->d_bank; s.out_count = e->d_out_count;
     s.ring = e->d_ring; s.round = e->d_round; s.stats = e->d_stats; s.hid = e->d_hid;
+    s.limit = e->d_limit; s.status = e->d_status; s.kreq = e->d_kreq;
     return s;
 }
 
@@ -255,6 +311,7 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
     WB_CHECK_ARG(cfg->lin_k_dim == 128 && cfg->lin_v_dim == 128 && cfg->conv_kernel == 4, "engine_create: DeltaNet heads must be 128x128 with conv width 4");
     WB_CHECK_ARG(cfg->q_heads % cfg->kv_heads == 0 && (cfg->q_heads / cfg->kv_heads) * (cfg->k_max + 1) <= 32,
                  "engine_create: (k_max+1) x GQA group exceeds 32 query rows");
+    WB_CHECK_ARG(cfg->max_pos >= cfg->k_max + 2, "engine_create: max_pos %u leaves no room for one round", cfg->max_pos);
     Engine *e = new Engine();
     e->cfg = *cfg; e->w = *weights;
     e->H = cfg->hidden; e->II = cfg->inter; e->V = cfg->vocab; e->P = cfg->k_max + 1; e->T_max = cfg->max_seqs * e->P;
@@ -263,6 +320,12 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
     e->lpn = e->cd + e->vald + 2 * cfg->lin_v_heads;
     e->fpn = 2 * cfg->q_heads * cfg->head_dim + 2 * cfg->kv_heads * cfg->head_dim;
     e->rows_per_slot = 2 * e->P;
+    // One GEMM kernel per engine: the skinny kernel and the tensor-memory kernel each keep a row's bits independent of the
+    // batch, but differ from each other, and greedy speculation is output-preserving only if the plain, draft and verify
+    // forwards of a sequence sum in one order.  An engine whose largest forward fits 32 rows runs the skinny kernel
+    // everywhere; any larger engine runs the tensor-memory kernel for every row count.
+    e->gemm_path = e->T_max > 32 ? WB_GEMM_TC : WB_GEMM_AUTO;
+    e->snapshots = cfg->state_snapshots != 0;
     // Pages per attention segment: fixed per engine, because it fixes the summation order (two engines agree bit for bit only
     // with the same value: pin cfg.attn_seg_pages to compare engines of different capacity).  A CTA reduces one segment of
     // one (chain, kv head): short segments cost a launch, a Q stage and a merge per 128 KB of KV, long ones leave SMs idle.
@@ -283,7 +346,7 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
     for (uint32_t l = 0; l < cfg->n_layers; l++) (cfg->layer_is_full[l] ? e->n_full : e->n_lin)++;
     *out = e;
     const uint32_t S = cfg->max_seqs, T = e->T_max, H = e->H;
-    TRY(wb_gemm_warmup());
+    TRY(wb_gemm_init());
     TRY(wb_attn_init(cfg->head_dim));
     // pools
     size_t st_elem = cfg->state_f32 ? 4 : 2;
@@ -295,7 +358,7 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
         e->lin_state.push_back(p); e->conv_state.push_back(c);
     }
     if (e->n_lin) TRY(dalloc(e, &e->gdn_kq, (size_t)T * cfg->lin_k_heads * 256, "gdn_kq", false));
-    if (e->P >= 3 && e->n_lin) {
+    if (e->P >= 3 && e->n_lin && !e->snapshots) {
         // from three positions per round on, a round logs its state updates instead of writing a snapshot per position
         for (uint32_t i = 0; i < e->n_lin; i++) {
             float *lg;
@@ -323,8 +386,9 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
     TRY(dalloc(e, &e->d_pos, S, "pos")); TRY(dalloc(e, &e->d_pending, S, "pending")); TRY(dalloc(e, &e->d_state_row, S, "state_row"));
     TRY(dalloc(e, &e->d_bank, S, "bank")); TRY(dalloc(e, &e->d_out_count, S, "out_count")); TRY(dalloc(e, &e->d_top_k, S, "top_k"));
     TRY(dalloc(e, &e->d_ring, (size_t)S * RING_CAP, "ring")); TRY(dalloc(e, &e->d_block_table, (size_t)S * e->bpr, "block_table"));
-    TRY(dalloc(e, &e->d_round, S, "round")); TRY(dalloc(e, &e->d_seed, S, "seed")); TRY(dalloc(e, &e->d_stats, (size_t)S * 3, "stats"));
+    TRY(dalloc(e, &e->d_round, S, "round")); TRY(dalloc(e, &e->d_seed, S, "seed")); TRY(dalloc(e, &e->d_stats, (size_t)S * STATS_WORDS, "stats"));
     TRY(dalloc(e, &e->d_temp, S, "temp")); TRY(dalloc(e, &e->d_top_p, S, "top_p")); TRY(dalloc(e, &e->d_hid, (size_t)S * H, "hid"));
+    TRY(dalloc(e, &e->d_limit, S, "limit")); TRY(dalloc(e, &e->d_status, S, "status")); TRY(dalloc(e, &e->d_kreq, S, "kreq"));
     // step tables
     TRY(dalloc(e, &e->d_slots, S, "slots")); TRY(dalloc(e, &e->d_tok, T, "tok")); TRY(dalloc(e, &e->d_pos_rows, T, "pos_rows"));
     TRY(dalloc(e, &e->d_seq_rows, T, "seq_rows")); TRY(dalloc(e, &e->d_row_start, S, "row_start")); TRY(dalloc(e, &e->d_row_count, S, "row_count"));
@@ -334,6 +398,7 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
     TRY(dalloc(e, &e->d_first_tok, S, "first_tok")); TRY(dalloc(e, &e->d_lg_of, S, "lg_of"));
     TRY(dalloc(e, &e->d_drafts, (size_t)S * (cfg->k_max ? cfg->k_max : 1), "drafts")); TRY(dalloc(e, &e->d_accept_len, S, "accept_len"));
     TRY(dalloc(e, &e->d_out_tokens, T, "out_tokens")); TRY(dalloc(e, &e->d_target, T, "target"));
+    TRY(dalloc(e, &e->d_nd, S, "n_drafts")); TRY(dalloc(e, &e->d_nd_in, S, "n_drafts_in"));
     TRY(dalloc(e, &e->d_mtp_tok, S, "mtp_tok")); TRY(dalloc(e, &e->d_mtp_rope, S, "mtp_rope")); TRY(dalloc(e, &e->d_mtp_kvpos, S, "mtp_kvpos"));
     {
         std::vector<uint32_t> iota(T), ones(T, 1);
@@ -377,10 +442,12 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
     TRY(dalloc(e, &e->p_ids, (size_t)T * 64, "p_ids")); TRY(dalloc(e, &e->p_probs, (size_t)T * 64, "p_probs")); TRY(dalloc(e, &e->p_n, T, "p_n"));
     TRY(dalloc(e, &e->q_ids, (size_t)T * 64, "q_ids")); TRY(dalloc(e, &e->q_probs, (size_t)T * 64, "q_probs")); TRY(dalloc(e, &e->q_n, T, "q_n"));
     e->h_temp.assign(S, 0.0f);
-    TRY(dalloc(e, &e->d_pack, (size_t)S * (3 + e->P), "round_pack"));
-    CUDA_TRY(cudaMallocHost((void **)&e->h_pack, (size_t)S * (3 + e->P) * 4));
+    e->h_limit.assign(S, 0);
+    TRY(dalloc(e, &e->d_pack, (size_t)S * (4 + e->P), "round_pack"));
+    CUDA_TRY(cudaMallocHost((void **)&e->h_pack, (size_t)S * (4 + e->P) * 4));
     e->h_stage_words = (size_t)T + 5 * S + 16;
     CUDA_TRY(cudaMallocHost((void **)&e->h_stage, e->h_stage_words * 4));
+    for (int i = 0; i < 4; i++) CUDA_TRY(cudaEventCreate(&e->ev[i]));
     CUDA_TRY(cudaDeviceSynchronize());
     return WB_OK;
 }
@@ -388,10 +455,11 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
 extern "C" void wein_b200_engine_destroy(wein_b200_engine *e) {
     if (!e) return;
     cudaDeviceSynchronize();
-    for (auto &g : e->graphs) cudaGraphExecDestroy(g.second);
+    for (auto &g : e->graphs) cudaGraphExecDestroy(g.second.first);
     for (void *p : e->allocs) cudaFree(p);
     if (e->h_stage) cudaFreeHost(e->h_stage);
     if (e->h_pack) cudaFreeHost(e->h_pack);
+    for (int i = 0; i < 4; i++) if (e->ev[i]) cudaEventDestroy(e->ev[i]);
     delete e;
 }
 extern "C" uint64_t wein_b200_engine_device_bytes(const wein_b200_engine *e) { return e ? e->bytes : 0; }
@@ -419,46 +487,49 @@ extern "C" int32_t wein_b200_engine_admit(wein_b200_engine *e, uint32_t slot, co
         CUDA_TRY(cudaMemsetAsync((char *)e->conv_state[i] + (size_t)row0 * conv_row, 0, conv_row, st));
     }
     CUDA_TRY(cudaMemcpyAsync(e->d_block_table + (size_t)slot * e->bpr, host_pages, (size_t)n_pages * 4, cudaMemcpyHostToDevice, st));
-    WB_LAUNCH((slot_init_kernel), 1, 1, 0, st, slot_state(e), slot, row0, e->d_temp, e->d_top_k, e->d_top_p, e->d_seed, temp, top_k, top_p, seed);
+    // positions the slot may occupy: what its pages hold, never more than the engine's tables (rotary table, block-table row)
+    const uint32_t limit = n_pages * 16 < e->cfg.max_pos ? n_pages * 16 : e->cfg.max_pos;
+    WB_LAUNCH((slot_init_kernel), 1, 1, 0, st, slot_state(e), slot, row0, limit, e->d_temp, e->d_top_k, e->d_top_p, e->d_seed, temp, top_k, top_p, seed);
     WB_LAUNCH_CHECK();
     CUDA_TRY(cudaStreamSynchronize(st));  // host_pages may be pageable memory
     e->h_temp[slot] = temp;
+    e->h_limit[slot] = limit;
+    return WB_OK;
+}
+
+// Per-request draft length (Qwen35Executor::set_spec, qwen.rs:2604-2647): rounds verify min(round k, this value) drafts for the
+// slot; 0 makes it a plain decode row inside a speculative round.  Admission resets it to "as many as the round drafts".
+extern "C" int32_t wein_b200_engine_set_spec(wein_b200_engine *e, uint32_t slot, uint32_t k, void *stream) {
+    WB_CHECK_ARG(e && slot < e->cfg.max_seqs, "engine_set_spec: slot out of range");
+    WB_LAUNCH((set_kreq_kernel), 1, 1, 0, (cudaStream_t)stream, e->d_kreq, slot, k);
+    WB_LAUNCH_CHECK();
+    return WB_OK;
+}
+
+// A sequence that does not start at position 0: its first `position` tokens are already in the KV pages it was admitted with
+// and its recurrent / conv state row (row 2 * (k_max + 1) * slot of every pool, see wein_b200_engine_buffer) holds the state
+// after them -- what a prefix-cache hit restores in the reference (radix snapshots, qwen.rs:3056-3100).  The caller writes
+// those buffers, then names the position and the token to feed next.  Call after admit, before the slot's first round.
+extern "C" int32_t wein_b200_engine_resume(wein_b200_engine *e, uint32_t slot, uint32_t position, uint32_t pending_token, void *stream) {
+    WB_CHECK_ARG(e && slot < e->cfg.max_seqs, "engine_resume: slot out of range");
+    WB_CHECK_ARG(position + 1 <= e->h_limit[slot], "engine_resume: position %u leaves no room below the slot's limit %u", position, e->h_limit[slot]);
+    WB_CHECK_ARG(pending_token < e->V, "engine_resume: token id %u outside the vocabulary", pending_token);
+    WB_LAUNCH((resume_kernel), 1, 1, 0, (cudaStream_t)stream, slot_state(e), slot, position, pending_token);
+    WB_LAUNCH_CHECK();
     return WB_OK;
 }
 
 // ------------------------------------------------------------------------------------------------ forward passes
-// Profiling hook (ablation, as the reference's WEIN_ABLATE): bit 0 skips every GEMM launch, bit 1 the residual-add+norm
-// kernels, bit 2 the DeltaNet layer kernel, bit 3 the attention kernels (q/k prep, attention, combine), bit 4 the draft
-// forwards (the verify forward then runs on stale draft tokens: this is how the verify step is timed alone), so timed
-// rounds attribute the in-graph cost of each class; results are then meaningless.  Never set outside measurements.
-static uint32_t g_ablate = 0;
-static bool g_fast_sampled = true;   // A/B switch, see spec_step
-extern "C" void wein_b200_engine_fast_sampled(uint32_t on) { g_fast_sampled = on != 0; }
-static bool g_lite = true;   // A/B switch: false writes a state snapshot per position in every round
-extern "C" void wein_b200_engine_lite(uint32_t on) { g_lite = on != 0; }
-extern "C" void wein_b200_engine_ablate(uint32_t mask) { g_ablate = mask; }
-
-// Tells the GEMM about to be launched which weights come after it in the round, if this launch is where the chain expects it.
-static void chain_hint(Engine *e, const void *w) {
-    if (e->chain.empty()) return;
-    if (e->chain[e->chain_pos % e->chain.size()].first != w) { e->chain.clear(); return; }  // order differs: stop hinting
-    const auto &nx = e->chain[(e->chain_pos + 1) % e->chain.size()];
-    wb_gemm_set_next(nx.first, nx.second);
-    e->chain_pos++;
-}
-
 static int32_t gemm(Engine *e, const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, cudaStream_t st) {
-    if (g_ablate & 1u) return WB_OK;
     e->launches++;
-    chain_hint(e, w);
-    return wb_gemm_wt(a, w, c, m, n, k, lda, ldc, e->gemm_scratch, e->gemm_scratch_bytes, st);
+    return wb_gemm_wt(a, w, c, m, n, k, lda, ldc, e->gemm_scratch, e->gemm_scratch_bytes, e->gemm_path, st);
 }
 
 // Full-attention block: projections -> fused q/k norm + rope + KV scatter -> paged verify attention (+ gate) -> o_proj.
 static int32_t full_attn_block(Engine *e, const wein_b200_layer_weights &w, void *kp, void *vp, uint32_t T, uint32_t n_spans,
                                uint32_t max_count, uint32_t max_ctx, uint32_t seg_pages, const uint32_t *rope_pos, const uint32_t *kv_pos,
                                const uint32_t *seq_ids, const uint32_t *bt, uint32_t bpr, const uint32_t *row_start,
-                               const uint32_t *row_count, cudaStream_t st) {
+                               const uint32_t *row_count, uint32_t *status, cudaStream_t st) {
     const wein_b200_model_cfg &c = e->cfg;
     uint32_t H = e->H, qd = c.q_heads * c.head_dim, he = c.kv_heads * c.head_dim;
     if (adjacent(w.qg, w.k, (size_t)2 * qd * H) && adjacent(w.k, w.v, (size_t)he * H)) {
@@ -468,13 +539,11 @@ static int32_t full_attn_block(Engine *e, const wein_b200_layer_weights &w, void
         TRY(gemm(e, e->n1, w.k, e->proj + 2 * qd, T, he, H, H, e->fpn, st));
         TRY(gemm(e, e->n1, w.v, e->proj + 2 * qd + he, T, he, H, H, e->fpn, st));
     }
-    if (!(g_ablate & 8u)) {
     TRY(wb_qk_prep(e->proj, e->fpn, w.qn, w.kn, e->cosv, e->sinv, rope_pos, kv_pos, seq_ids, bt, bpr, e->qh, e->gate, kp, vp, T, c.q_heads,
                    c.kv_heads, c.head_dim, c.rot_dim, c.rms_eps, st));
     float q_scale = 1.0f / sqrtf((float)c.head_dim);
     TRY(wb_attn_verify(e->qh, kp, vp, bt, seq_ids, kv_pos, row_start, row_count, e->gate, e->attn, q_scale, bpr, 16, c.q_heads, c.kv_heads,
-                       c.head_dim, n_spans, max_count, max_ctx, seg_pages, e->attn_scratch, e->attn_scratch_bytes, st));
-    }
+                       c.head_dim, n_spans, max_count, max_ctx, seg_pages, e->attn_scratch, e->attn_scratch_bytes, status, st));
     e->launches += 3;
     TRY(gemm(e, e->attn, w.o, e->o, T, H, qd, qd, H, st));
     return WB_OK;
@@ -482,21 +551,15 @@ static int32_t full_attn_block(Engine *e, const wein_b200_layer_weights &w, void
 
 static int32_t mlp_block(Engine *e, const wein_b200_layer_weights &w, uint32_t T, cudaStream_t st) {
     uint32_t H = e->H, II = e->II;
-    if (T <= wb_gemm_skinny_max() && adjacent(w.wg, w.wu, (size_t)II * H)) {
+    if (adjacent(w.wg, w.wu, (size_t)II * H)) {
         // gate|up projection with the SwiGLU activation in the epilogue: one launch, no [T, 2*inter] round trip
         e->launches++;
-        chain_hint(e, w.wg);
-        if (!(g_ablate & 1u))
-        TRY(wb_gemm_swiglu(e->n2, w.wg, e->m, T, II, H, H, II, e->gemm_scratch, e->gemm_scratch_bytes, st));
+        TRY(wb_gemm_swiglu(e->n2, w.wg, e->m, T, II, H, H, II, e->gemm_scratch, e->gemm_scratch_bytes, e->gemm_path, st));
         TRY(gemm(e, e->m, w.wd, e->d, T, H, II, II, H, st));
         return WB_OK;
     }
-    if (adjacent(w.wg, w.wu, (size_t)II * H)) {
-        TRY(gemm(e, e->n2, w.wg, e->gu, T, 2 * II, H, H, 2 * II, st));
-    } else {
-        TRY(gemm(e, e->n2, w.wg, e->gu, T, II, H, H, 2 * II, st));
-        TRY(gemm(e, e->n2, w.wu, e->gu + II, T, II, H, H, 2 * II, st));
-    }
+    TRY(gemm(e, e->n2, w.wg, e->gu, T, II, H, H, 2 * II, st));
+    TRY(gemm(e, e->n2, w.wu, e->gu + II, T, II, H, H, 2 * II, st));
     TRY(wb_silu_mul_rows(e->gu, 2 * II, e->m, T, II, st));
     e->launches++;
     TRY(gemm(e, e->m, w.wd, e->d, T, H, II, II, H, st));
@@ -516,7 +579,7 @@ static int32_t forward(Engine *e, uint32_t T, uint32_t n_spans, uint32_t max_cou
         const wein_b200_layer_weights &w = e->w.layers[l];
         if (c.layer_is_full[l]) {
             TRY(full_attn_block(e, w, e->k_pool[fi], e->v_pool[fi], T, n_spans, max_count, max_ctx, e->seg_pages, e->d_pos_rows, e->d_pos_rows,
-                                e->d_seq_rows, e->d_block_table, e->bpr, e->d_row_start, e->d_row_count, st));
+                                e->d_seq_rows, e->d_block_table, e->bpr, e->d_row_start, e->d_row_count, e->d_status, st));
             fi++;
         } else {
             uint32_t vh = c.lin_v_heads;
@@ -529,17 +592,17 @@ static int32_t forward(Engine *e, uint32_t T, uint32_t n_spans, uint32_t max_cou
                 TRY(gemm(e, e->n1, w.b, e->proj + e->cd + e->vald + vh, T, vh, H, H, e->lpn, st));
             }
             // conv + SiLU + conv rows + l2 norms + gates + chain recurrence + gated norm: one launch per layer
-            if (!(g_ablate & 4u)) TRY(wb_gdn_layer(e->proj, e->lpn, w.conv, e->conv_state[li], w.a_log, w.dt_bias, w.norm, e->lin_state[li], c.state_f32, e->normed,
+            TRY(wb_gdn_layer(e->proj, e->lpn, w.conv, e->conv_state[li], w.a_log, w.dt_bias, w.norm, e->lin_state[li], c.state_f32, e->normed,
                              e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base, n_spans, c.lin_k_heads, vh, c.l2_eps, c.rms_eps,
                              lite ? e->lin_log[li] : nullptr, e->gdn_kq, st));
             e->launches += 1;
             TRY(gemm(e, e->normed, w.out, e->o, T, H, e->vald, e->vald, H, st));
             li++;
         }
-        if (!(g_ablate & 2u)) TRY(wein_b200_add_norm_zc(e->x, e->o, w.ln2, e->h2, e->n2, T, H, c.rms_eps, st));
+        TRY(wein_b200_add_norm_zc(e->x, e->o, w.ln2, e->h2, e->n2, T, H, c.rms_eps, st));
         TRY(mlp_block(e, w, T, st));
         bool last = l + 1 == c.n_layers;
-        if (!(g_ablate & 2u)) TRY(wein_b200_add_norm_zc(e->h2, e->d, last ? e->w.norm_f : e->w.layers[l + 1].ln1, e->x, last ? e->n2 : e->n1, T, H, c.rms_eps, st));
+        TRY(wein_b200_add_norm_zc(e->h2, e->d, last ? e->w.norm_f : e->w.layers[l + 1].ln1, e->x, last ? e->n2 : e->n1, T, H, c.rms_eps, st));
         e->launches += 2;
     }
     if (n_lg == 0) return WB_OK;
@@ -561,7 +624,8 @@ static int32_t mtp_forward(Engine *e, uint32_t n, uint32_t i, bool sampled, cuda
     const wein_b200_model_cfg &c = e->cfg;
     uint32_t H = e->H, km = c.k_max;
     const wein_b200_layer_weights &w = e->w.mtp_layer;
-    WB_LAUNCH((mtp_prep_kernel), (n + 127) / 128, 128, 0, st, e->d_slots, slot_state(e), e->d_drafts, km, n, i, e->d_mtp_tok, e->d_mtp_rope, e->d_mtp_kvpos);
+    WB_LAUNCH((mtp_prep_kernel), (n + 127) / 128, 128, 0, st, e->d_slots, slot_state(e), e->d_drafts, km, n, i, e->V, c.max_pos, e->d_mtp_tok, e->d_mtp_rope,
+                                          e->d_mtp_kvpos);
     WB_LAUNCH_CHECK();
     // hidden: the stashed target hidden of position pos-1 for the first draft, then the head's own normalised output
     TRY(wb_mtp_cat(e->d_mtp_tok, 1, e->w.embed, i == 0 ? e->d_hid : e->n2, i == 0 ? e->d_slots : nullptr, e->w.mtp_pre_e, e->w.mtp_pre_h, e->cat,
@@ -571,7 +635,7 @@ static int32_t mtp_forward(Engine *e, uint32_t n, uint32_t i, bool sampled, cuda
     e->launches += 3;
     // each batch row is its own one-page chain: clean per round, chain-local KV slots, absolute rotary positions
     TRY(full_attn_block(e, w, e->k_pool[e->n_full], e->v_pool[e->n_full], n, n, 1, 16, 1, e->d_mtp_rope, e->d_mtp_kvpos, e->d_iota, e->d_iota, 1,
-                        e->d_iota, e->d_ones, st));
+                        e->d_iota, e->d_ones, nullptr, st));
     TRY(wein_b200_add_norm_zc(e->x, e->o, w.ln2, e->h2, e->n2, n, H, c.rms_eps, st));
     TRY(mlp_block(e, w, n, st));
     TRY(wein_b200_add_norm_zc(e->h2, e->d, e->w.mtp_norm, e->x, e->n2, n, H, c.rms_eps, st));
@@ -593,87 +657,30 @@ static int32_t mtp_forward(Engine *e, uint32_t n, uint32_t i, bool sampled, cuda
     return WB_OK;
 }
 
-// The order in which a round of k drafts + one verify forward multiplies its weight matrices (fused layouts only).
-static void build_chain(Engine *e, uint32_t k, uint32_t T) {
-    e->chain.clear();
-    e->chain_pos = 0;
-    const wein_b200_model_cfg &c = e->cfg;
-    const uint64_t H = e->H, II = e->II, qd = (uint64_t)c.q_heads * c.head_dim, he = (uint64_t)c.kv_heads * c.head_dim;
-    if (T > 32) return;
-    auto layer_ok = [&](const wein_b200_layer_weights &w, bool full) {
-        if (!adjacent(w.wg, w.wu, II * H)) return false;
-        if (full) return adjacent(w.qg, w.k, 2 * qd * H) && adjacent(w.k, w.v, he * H);
-        return adjacent(w.qkv, w.z, (uint64_t)e->cd * H) && adjacent(w.z, w.a, (uint64_t)e->vald * H) && adjacent(w.a, w.b, (uint64_t)c.lin_v_heads * H);
-    };
-    auto push_layer = [&](const wein_b200_layer_weights &w, bool full) {
-        if (full) { e->chain.push_back({w.qg, (uint64_t)e->fpn * H * 2}); e->chain.push_back({w.o, H * qd * 2}); }
-        else { e->chain.push_back({w.qkv, (uint64_t)e->lpn * H * 2}); e->chain.push_back({w.out, H * e->vald * 2}); }
-        e->chain.push_back({w.wg, 2 * II * H * 2});
-        e->chain.push_back({w.wd, H * II * 2});
-    };
-    for (uint32_t l = 0; l < c.n_layers; l++) if (!layer_ok(e->w.layers[l], c.layer_is_full[l])) return;
-    if (k && !layer_ok(e->w.mtp_layer, true)) return;
-    for (uint32_t i = 0; i < k; i++) {
-        e->chain.push_back({e->w.mtp_fc, 2 * H * H * 2});
-        push_layer(e->w.mtp_layer, true);
-        e->chain.push_back({e->w.embed, (uint64_t)e->V * H * 2});
-    }
-    for (uint32_t l = 0; l < c.n_layers; l++) push_layer(e->w.layers[l], c.layer_is_full[l]);
-    e->chain.push_back({e->w.embed, (uint64_t)e->V * H * 2});
-}
-
-// Forwards of more than 32 rows multiply through cuBLASLt.  Its first heuristic answer is rarely the fastest for these
-// skinny weight-streaming shapes, so the first time a row count is seen every product shape of the forward is timed once
-// on the engine's own buffers (activations are scratch between rounds) and the winner is kept.  Not capturable: called
-// before a round is captured or run.
-static int32_t tune_rows(Engine *e, uint32_t m, bool mtp, cudaStream_t st) {
-    if (m <= wb_gemm_skinny_max() || e->lt_tuned.count(m | (mtp ? 0x80000000u : 0u))) return WB_OK;
-    const wein_b200_model_cfg &c = e->cfg;
-    const uint32_t H = e->H, II = e->II, qd = c.q_heads * c.head_dim;
-    auto tune_layer = [&](const wein_b200_layer_weights &w, bool full) -> int32_t {
-        if (full) {
-            TRY(wb_gemm_lt_autotune(e->n1, w.qg, e->proj, m, e->fpn, H, H, e->fpn, st));
-            TRY(wb_gemm_lt_autotune(e->attn, w.o, e->o, m, H, qd, qd, H, st));
-        } else {
-            TRY(wb_gemm_lt_autotune(e->n1, w.qkv, e->proj, m, e->lpn, H, H, e->lpn, st));
-            TRY(wb_gemm_lt_autotune(e->normed, w.out, e->o, m, H, e->vald, e->vald, H, st));
-        }
-        TRY(wb_gemm_lt_autotune(e->n2, w.wg, e->gu, m, 2 * II, H, H, 2 * II, st));
-        TRY(wb_gemm_lt_autotune(e->m, w.wd, e->d, m, H, II, II, H, st));
-        return WB_OK;
-    };
-    if (mtp) {
-        TRY(wb_gemm_lt_autotune(e->cat, e->w.mtp_fc, e->x, m, H, 2 * H, 2 * H, H, st));
-        TRY(tune_layer(e->w.mtp_layer, true));
-    } else {
-        bool seen_full = false, seen_lin = false;
-        for (uint32_t l = 0; l < c.n_layers; l++) {
-            const bool full = c.layer_is_full[l] != 0;
-            if (full ? seen_full : seen_lin) continue;
-            (full ? seen_full : seen_lin) = true;
-            TRY(tune_layer(e->w.layers[l], full));
-        }
-    }
-    TRY(wb_gemm_lt_autotune(e->n2, e->w.embed, e->logits, m, e->V, H, H, e->V, st));
-    e->lt_tuned.insert(m | (mtp ? 0x80000000u : 0u));
+// The draft phase of a round (spec_draft_batch, qwen.rs:2748-2853): k MTP forwards, drafts and their distributions stay on the device.
+static int32_t run_draft(Engine *e, uint32_t n, uint32_t k, bool sampled, cudaStream_t st) {
+    for (uint32_t i = 0; i < k; i++) TRY(mtp_forward(e, n, i, sampled, st));
+    e->launches += k;
     return WB_OK;
 }
 
-static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32_t max_ctx, cudaStream_t st) {
+// Verify forward + acceptance + commit (forward_batch_mixed + spec_finish) over the drafts in the engine's draft buffer.
+// caller_nd: per-row draft counts were imported (spec_verify); dry: decide but commit nothing.
+static int32_t run_verify(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32_t max_ctx, bool caller_nd, bool dry, cudaEvent_t after_forward,
+                          cudaStream_t st) {
     const uint32_t P = k + 1, T = n * P, km = e->cfg.k_max ? e->cfg.k_max : 1;
-    build_chain(e, k, T);
-    if (!(g_ablate & 16u))
-        for (uint32_t i = 0; i < k; i++) TRY(mtp_forward(e, n, i, sampled, st));
-    WB_LAUNCH((verify_prep_kernel), (n + 127) / 128, 128, 0, st, e->d_slots, slot_state(e), e->d_drafts, km, n, P, e->rows_per_slot, e->P, e->d_tok,
-                                                      e->d_pos_rows, e->d_seq_rows, e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base,
-                                                      e->d_lg_rows);
+    WB_LAUNCH((verify_prep_kernel), (n + 127) / 128, 128, 0, st, e->d_slots, slot_state(e), e->d_drafts, km, caller_nd ? e->d_nd_in : nullptr, n, P, e->V,
+                                                      e->rows_per_slot, e->P, e->d_tok, e->d_pos_rows, e->d_seq_rows, e->d_row_start, e->d_row_count,
+                                                      e->d_in_row, e->d_out_base, e->d_lg_rows, e->d_nd);
     WB_LAUNCH_CHECK();
-    e->launches += 1 + k;
+    e->launches += 1;
     // three positions or more: log the state updates, materialise the accepted state once after acceptance (below)
-    const bool lite = g_lite && P >= 3 && !e->lin_log.empty();
+    const bool lite = P >= 3 && !e->lin_log.empty();
     TRY(forward(e, T, n, P, max_ctx, T, true, lite, st));
+    if (after_forward) cudaEventRecord(after_forward, st);
     AcceptArgs a{};
-    a.drafts = e->d_drafts; a.draft_stride = km; a.B = n; a.k = k; a.accept_len = e->d_accept_len; a.out_tokens = e->d_out_tokens; a.target = e->d_target;
+    a.drafts = e->d_drafts; a.draft_stride = km; a.n_drafts = e->d_nd; a.B = n; a.k = k; a.accept_len = e->d_accept_len; a.out_tokens = e->d_out_tokens;
+    a.target = e->d_target;
     if (!sampled) {
         const uint32_t split = am_split(T);
         TRY(wein_b200_argmax_partials(e->logits, e->d_lg_rows, e->am_part, e->V, T, split, st));
@@ -687,14 +694,16 @@ static int32_t run_round(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32
         a.temp = e->d_temp; a.seed = e->d_seed; a.round = e->d_round; a.slot_of = e->d_slots;
     }
     TRY(wb_accept_args(a, st));
-    if (lite && !(g_ablate & 4u)) {
+    e->launches += 2;
+    if (dry) return WB_OK;
+    if (lite) {
         TRY(wb_gdn_commit(e->d_state_ptrs, e->d_log_ptrs, e->n_lin, e->cfg.state_f32, e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base,
                           e->d_accept_len, n, e->cfg.lin_v_heads, st));
         e->launches++;
     }
-    WB_LAUNCH((commit_kernel), n, 128, 0, st, e->d_slots, slot_state(e), e->d_accept_len, e->d_out_tokens, e->d_out_base, e->x, P, k, e->H);
+    WB_LAUNCH((commit_kernel), n, 128, 0, st, e->d_slots, slot_state(e), e->d_accept_len, e->d_row_count, e->d_nd, e->d_out_tokens, e->d_out_base, e->x, P, k, e->H);
     WB_LAUNCH_CHECK();
-    e->launches += 3;
+    e->launches += 1;
     return WB_OK;
 }
 
@@ -713,55 +722,165 @@ static int32_t set_slots(Engine *e, uint32_t n, const uint32_t *host_slots, cuda
     return WB_OK;
 }
 
-extern "C" int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, uint32_t ctx_bound,
-                                              uint32_t use_graph, void *stream) {
-    WB_CHECK_ARG(e && host_slots && n >= 1 && n <= e->cfg.max_seqs, "spec_step: batch of %u outside 1..max_seqs", n);
-    WB_CHECK_ARG(k <= e->cfg.k_max, "spec_step: k = %u exceeds k_max = %u", k, e->cfg.k_max);
-    WB_CHECK_ARG(k == 0 || e->cfg.has_mtp, "spec_step: drafting needs the MTP head");
-    WB_CHECK_ARG(ctx_bound >= k + 1 && ctx_bound <= e->cfg.max_pos, "spec_step: ctx_bound %u outside k+1..max_pos", ctx_bound);
-    cudaStream_t st = (cudaStream_t)stream;
-    WB_CHECK_ARG(!use_graph || st != nullptr, "spec_step: a CUDA graph cannot be captured on the default stream; pass a created stream");
-    TRY(set_slots(e, n, host_slots, st, (use_graph & 2u) != 0));
-    use_graph &= 1u;
-    e->last_n = n; e->last_P = k + 1;
-    bool sampled = false;
-    for (uint32_t i = 0; i < n; i++) sampled |= e->h_temp[host_slots[i]] > 0.0f;
+// What a call runs: the draft phase, the verify phase, or both (one round).
+enum { PH_DRAFT = 1, PH_VERIFY = 2, PH_CALLER_ND = 4, PH_DRY = 8 };
+
+static int32_t run_phases(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32_t bucket, uint32_t phases, cudaStream_t st, bool timed) {
+    const bool t = timed && e->timing;
+    if (t) cudaEventRecord(e->ev[0], st);
+    if (phases & PH_DRAFT) TRY(run_draft(e, n, k, sampled, st));
+    if (t) cudaEventRecord(e->ev[1], st);
+    if (phases & PH_VERIFY) TRY(run_verify(e, n, k, sampled, bucket, (phases & PH_CALLER_ND) != 0, (phases & PH_DRY) != 0, t ? e->ev[2] : nullptr, st));
+    if (t) {
+        if (!(phases & PH_VERIFY)) cudaEventRecord(e->ev[2], st);
+        cudaEventRecord(e->ev[3], st);
+        e->ev_pending = true;
+    }
+    return WB_OK;
+}
+
+// Folds the phase events of the last eager round into the totals (spec_timing_ms, qwen.rs:4277-4279); synchronises on them.
+static void fold_timing(Engine *e) {
+    if (!e->ev_pending) return;
+    e->ev_pending = false;
+    if (cudaEventSynchronize(e->ev[3]) != cudaSuccess) { cudaGetLastError(); return; }
+    for (int i = 0; i < 3; i++) {
+        float ms = 0.0f;
+        if (cudaEventElapsedTime(&ms, e->ev[i], e->ev[i + 1]) == cudaSuccess) e->ms_phase[i] += ms;
+        else cudaGetLastError();
+    }
+}
+
+static uint32_t ctx_bucket(const Engine *e, uint32_t ctx_bound) {
     // the context bound only sizes the attention grid: round it up to a bucket so graphs are reused
     uint32_t bucket = 256;
     while (bucket < ctx_bound) bucket *= 2;
     if (bucket > e->bpr * 16) bucket = e->bpr * 16;
-    // Rounds with sampled chains give up the batch-independent bits of the skinny GEMM between 17 and 32 rows for the
-    // library's speed there (acceptance is then exact in distribution, not bitwise against a plain decode run)
-    struct SkinnyScope { SkinnyScope(uint32_t m) { wb_gemm_set_skinny_max(m); } ~SkinnyScope() { wb_gemm_set_skinny_max(32); } } skinny(sampled && g_fast_sampled ? 16 : 32);
-    TRY(tune_rows(e, n * (k + 1), false, st));
-    if (k) TRY(tune_rows(e, n, true, st));
-    if (!use_graph) {
-        e->launches = 0;
-        TRY(run_round(e, n, k, sampled, bucket, st));
-        e->last_launches = e->launches;
-        return WB_OK;
-    }
-    auto key = std::make_tuple(n, k, (uint32_t)sampled, bucket, g_ablate | (g_lite ? 0u : 0x8000u) | (g_fast_sampled ? 0u : 0x4000u));
-    const std::string gname = "graph_launches:" + std::to_string(n) + ":" + std::to_string(k) + ":" + std::to_string((int)sampled) + ":" +
-                              std::to_string(bucket) + ":" + std::to_string(g_ablate);
+    return bucket;
+}
+
+// Captures (once) and returns the graph of the given phases; graph == nullptr only on error.
+static int32_t get_graph(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32_t bucket, uint32_t phases, cudaStream_t st,
+                         std::pair<cudaGraphExec_t, uint32_t> **out) {
+    auto key = std::make_tuple(phases, n, k, (uint32_t)sampled, bucket, 0u);
     auto it = e->graphs.find(key);
     if (it == e->graphs.end()) {
         cudaGraph_t g = nullptr;
         e->launches = 0;
         CUDA_TRY(cudaStreamBeginCapture(st, cudaStreamCaptureModeThreadLocal));
-        int32_t rc = run_round(e, n, k, sampled, bucket, st);
+        int32_t rc = run_phases(e, n, k, sampled, bucket, phases, st, false);
         cudaError_t ce = cudaStreamEndCapture(st, &g);
         if (rc != WB_OK) { if (g) cudaGraphDestroy(g); return rc; }
-        if (ce != cudaSuccess) { wb_set_error("spec_step: stream capture failed: %s", cudaGetErrorString(ce)); return WB_ERR_CUDA; }
+        if (ce != cudaSuccess) { wb_set_error("engine: stream capture failed: %s", cudaGetErrorString(ce)); return WB_ERR_CUDA; }
         cudaGraphExec_t ge = nullptr;
         ce = cudaGraphInstantiate(&ge, g, 0);
         cudaGraphDestroy(g);
-        if (ce != cudaSuccess) { wb_set_error("spec_step: graph instantiation failed: %s", cudaGetErrorString(ce)); return WB_ERR_CUDA; }
-        it = e->graphs.emplace(key, ge).first;
-        e->named[gname] = {nullptr, e->launches};
+        if (ce != cudaSuccess) { wb_set_error("engine: graph instantiation failed: %s", cudaGetErrorString(ce)); return WB_ERR_CUDA; }
+        cudaGraphUpload(ge, st);   // so that the first replay does not allocate either
+        cudaGetLastError();
+        it = e->graphs.emplace(key, std::make_pair(ge, e->launches)).first;
     }
-    e->last_launches = (uint32_t)e->named[gname].second;
-    CUDA_TRY(cudaGraphLaunch(it->second, st));
+    *out = &it->second;
+    return WB_OK;
+}
+
+static int32_t check_round_args(Engine *e, const char *who, uint32_t n, const uint32_t *host_slots, uint32_t k, uint32_t ctx_bound, bool graph, cudaStream_t st) {
+    WB_CHECK_ARG(e && host_slots && n >= 1 && n <= e->cfg.max_seqs, "%s: batch of %u outside 1..max_seqs", who, n);
+    WB_CHECK_ARG(k <= e->cfg.k_max, "%s: k = %u exceeds k_max = %u", who, k, e->cfg.k_max);
+    WB_CHECK_ARG(ctx_bound >= 1 && ctx_bound <= e->cfg.max_pos, "%s: ctx_bound %u outside 1..max_pos", who, ctx_bound);
+    WB_CHECK_ARG(!graph || st != nullptr, "%s: a CUDA graph cannot be captured on the default stream; pass a created stream", who);
+    return WB_OK;
+}
+
+static bool any_sampled(const Engine *e, uint32_t n, const uint32_t *host_slots) {
+    bool sampled = false;
+    for (uint32_t i = 0; i < n; i++) sampled |= e->h_temp[host_slots[i]] > 0.0f;
+    return sampled;
+}
+
+static int32_t launch_phases(Engine *e, uint32_t n, uint32_t k, bool sampled, uint32_t bucket, uint32_t phases, bool graph, cudaStream_t st) {
+    if (!graph) {
+        fold_timing(e);
+        e->launches = 0;
+        TRY(run_phases(e, n, k, sampled, bucket, phases, st, true));
+        e->last_launches = e->launches;
+        return WB_OK;
+    }
+    std::pair<cudaGraphExec_t, uint32_t> *g = nullptr;
+    TRY(get_graph(e, n, k, sampled, bucket, phases, st, &g));
+    e->last_launches = g->second;
+    CUDA_TRY(cudaGraphLaunch(g->first, st));
+    return WB_OK;
+}
+
+extern "C" int32_t wein_b200_engine_spec_step(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, uint32_t ctx_bound,
+                                              uint32_t use_graph, void *stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    TRY(check_round_args(e, "spec_step", n, host_slots, k, ctx_bound, (use_graph & 1u) != 0, st));
+    WB_CHECK_ARG(k == 0 || e->cfg.has_mtp, "spec_step: drafting needs the MTP head");
+    TRY(set_slots(e, n, host_slots, st, (use_graph & 2u) != 0));
+    e->last_n = n; e->last_P = k + 1;
+    return launch_phases(e, n, k, any_sampled(e, n, host_slots), ctx_bucket(e, ctx_bound), PH_DRAFT | PH_VERIFY, (use_graph & 1u) != 0, st);
+}
+
+// The draft phase alone (Qwen35Executor::spec_draft_batch, qwen.rs:2748): k MTP forwards for the listed slots; drafts_out
+// (optional, device, [n, k]) receives the draft tokens, which also stay in the engine for a following spec_verify.
+__global__ void export_drafts_kernel(const uint32_t *drafts, uint32_t k_max, uint32_t k, uint32_t *out) {
+    PDL_ENTRY();
+    if (threadIdx.x < k) out[blockIdx.x * k + threadIdx.x] = drafts[blockIdx.x * k_max + threadIdx.x];
+}
+extern "C" int32_t wein_b200_engine_draft(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, void *drafts_out,
+                                          uint32_t use_graph, void *stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    TRY(check_round_args(e, "engine_draft", n, host_slots, k, 1, (use_graph & 1u) != 0, st));
+    WB_CHECK_ARG(k >= 1 && e->cfg.has_mtp, "engine_draft: needs k >= 1 and the MTP head");
+    TRY(set_slots(e, n, host_slots, st, (use_graph & 2u) != 0));
+    TRY(launch_phases(e, n, k, any_sampled(e, n, host_slots), 0, PH_DRAFT, (use_graph & 1u) != 0, st));
+    if (drafts_out) {
+        WB_LAUNCH((export_drafts_kernel), n, 32, 0, st, e->d_drafts, e->cfg.k_max, k, (uint32_t *)drafts_out);
+        WB_LAUNCH_CHECK();
+    }
+    return WB_OK;
+}
+
+// Verify + accept + commit with the caller's drafts (Qwen35Executor::spec_verify / spec_commit_batch, qwen.rs:2261-2303).
+extern "C" int32_t wein_b200_engine_spec_verify(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, const void *drafts,
+                                                const void *n_drafts, const void *q_ids, const void *q_probs, const void *q_n,
+                                                uint32_t ctx_bound, uint32_t flags, void *stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    const bool graph = (flags & WEIN_B200_VERIFY_GRAPH) != 0, dry = (flags & WEIN_B200_VERIFY_DRY_RUN) != 0;
+    TRY(check_round_args(e, "spec_verify", n, host_slots, k, ctx_bound, graph, st));
+    WB_CHECK_ARG(k == 0 || drafts || (flags & WEIN_B200_VERIFY_ENGINE_DRAFTS), "spec_verify: drafts are required for k > 0");
+    WB_CHECK_ARG((q_ids == nullptr) == (q_probs == nullptr) && (q_ids == nullptr) == (q_n == nullptr), "spec_verify: q_ids, q_probs and q_n go together");
+    TRY(set_slots(e, n, host_slots, st, (flags & WEIN_B200_VERIFY_FORCE_SLOTS) != 0));
+    e->last_n = n; e->last_P = k + 1;
+    uint32_t phases = PH_VERIFY | (dry ? PH_DRY : 0u);
+    if (k && !(flags & WEIN_B200_VERIFY_ENGINE_DRAFTS)) {
+        // outside the graph: the caller's pointers may change from call to call
+        WB_LAUNCH((import_drafts_kernel), dim3(n, k), 64, 0, st, (const uint32_t *)drafts, (const uint32_t *)n_drafts, (const uint32_t *)q_ids,
+                                                   (const float *)q_probs, (const uint32_t *)q_n, n, k, e->cfg.k_max, e->d_drafts, e->d_nd_in,
+                                                   e->q_ids, e->q_probs, e->q_n);
+        WB_LAUNCH_CHECK();
+        phases |= PH_CALLER_ND;
+    }
+    return launch_phases(e, n, k, any_sampled(e, n, host_slots), ctx_bucket(e, ctx_bound), phases, graph, st);
+}
+
+// Everything a later call with the same (n, k, sampling mode, context bucket) would otherwise do lazily: capture and
+// instantiate its graphs (the reference warms its graphs at open_graph, qwen.rs:1994-2034).  `what` = bit 0: spec_step,
+// bit 1: spec_verify, bit 2: spec_verify as a dry run, bit 3: engine_draft.  The slots named must be admitted.
+extern "C" int32_t wein_b200_engine_warm(wein_b200_engine *e, uint32_t n, const uint32_t *host_slots, uint32_t k, uint32_t ctx_bound,
+                                         uint32_t what, void *stream) {
+    cudaStream_t st = (cudaStream_t)stream;
+    TRY(check_round_args(e, "engine_warm", n, host_slots, k, ctx_bound, true, st));
+    TRY(set_slots(e, n, host_slots, st));
+    const bool sampled = any_sampled(e, n, host_slots);
+    const uint32_t bucket = ctx_bucket(e, ctx_bound);
+    std::pair<cudaGraphExec_t, uint32_t> *g = nullptr;
+    if ((what & 1u) && (k == 0 || e->cfg.has_mtp)) TRY(get_graph(e, n, k, sampled, bucket, PH_DRAFT | PH_VERIFY, st, &g));
+    if (what & 2u) { TRY(get_graph(e, n, k, sampled, bucket, PH_VERIFY | (k ? PH_CALLER_ND : 0u), st, &g)); TRY(get_graph(e, n, k, sampled, bucket, PH_VERIFY, st, &g)); }
+    if (what & 4u) TRY(get_graph(e, n, k, sampled, bucket, PH_VERIFY | PH_DRY | (k ? PH_CALLER_ND : 0u), st, &g));
+    if ((what & 8u) && k && e->cfg.has_mtp) TRY(get_graph(e, n, k, sampled, 0, PH_DRAFT, st, &g));
     return WB_OK;
 }
 
@@ -770,11 +889,20 @@ extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, con
     WB_CHECK_ARG(e && host_slots && host_tokens && host_lens && n >= 1 && n <= e->cfg.max_seqs, "prefill: bad batch");
     cudaStream_t st = (cudaStream_t)stream;
     TRY(set_slots(e, n, host_slots, st));
+    // where every slot stands now (a slot may be prefilled again, or after rounds): sizes the attention grid and the limit check
+    std::vector<uint32_t> pos0(n, 0);
+    CUDA_TRY(cudaStreamSynchronize(st));
+    for (uint32_t i = 0; i < n; i++) CUDA_TRY(cudaMemcpy(&pos0[i], e->d_pos + host_slots[i], 4, cudaMemcpyDeviceToHost));
     std::vector<uint64_t> off(n + 1, 0);
     uint32_t max_len = 0;
     bool sampled = false;
     for (uint32_t i = 0; i < n; i++) {
-        WB_CHECK_ARG(host_lens[i] >= 1 && host_lens[i] < e->cfg.max_pos, "prefill: prompt of %u tokens outside 1..max_pos-1", host_lens[i]);
+        WB_CHECK_ARG(host_lens[i] >= 1, "prefill: empty prompt for slot %u", host_slots[i]);
+        if ((uint64_t)pos0[i] + host_lens[i] + 1 > e->h_limit[host_slots[i]]) {
+            wb_set_error("prefill: slot %u at position %u cannot take %u more tokens (limit %u from its admitted pages)", host_slots[i], pos0[i],
+                         host_lens[i], e->h_limit[host_slots[i]]);
+            return WB_ERR_CAPACITY;
+        }
         off[i + 1] = off[i] + host_lens[i];
         max_len = host_lens[i] > max_len ? host_lens[i] : max_len;
         sampled |= e->h_temp[host_slots[i]] > 0.0f;
@@ -784,7 +912,7 @@ extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, con
     std::vector<uint32_t> done(n, 0);
     uint32_t *h_cnt = e->h_stage, *h_last = e->h_stage + n, *h_tok = e->h_stage + 2 * n;
     for (uint32_t base = 0; base < max_len; base += P) {
-        uint32_t T = 0, n_lg = 0;
+        uint32_t T = 0, n_lg = 0, max_ctx = 1;
         CUDA_TRY(cudaStreamSynchronize(st));
         for (uint32_t i = 0; i < n; i++) {
             uint32_t rem = host_lens[i] - done[i], c = rem < P ? rem : P;
@@ -793,6 +921,7 @@ extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, con
             n_lg += h_last[i];
             for (uint32_t j = 0; j < c; j++) h_tok[T++] = host_tokens[off[i] + done[i] + j];
             done[i] += c;
+            if (c && pos0[i] + done[i] > max_ctx) max_ctx = pos0[i] + done[i];
         }
         uint32_t *h_lgslot = h_tok + T;
         for (uint32_t i = 0, q = 0; i < n; i++) if (h_last[i]) h_lgslot[q++] = host_slots[i];
@@ -804,8 +933,7 @@ extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, con
                                              e->d_pos_rows, e->d_seq_rows, e->d_row_start, e->d_row_count, e->d_in_row, e->d_out_base,
                                              e->d_lg_rows, e->d_lg_of);
         WB_LAUNCH_CHECK();
-        uint32_t max_ctx = base + P < e->bpr * 16 ? base + P : e->bpr * 16;
-        e->chain.clear();
+        if (max_ctx > e->bpr * 16) max_ctx = e->bpr * 16;
         TRY(forward(e, T, n, P, max_ctx, n_lg, false, false, st));
         if (n_lg > 0) {
             if (!sampled) {
@@ -830,16 +958,17 @@ extern "C" int32_t wein_b200_engine_prefill(wein_b200_engine *e, uint32_t n, con
     return WB_OK;
 }
 
-// One readback for the whole batch of the most recent spec_step: host_out [n, 3 + k_max + 1] = per batch row the accept
-// length a, the position, the tokens emitted since admission, and the round's a+1 tokens (unused words 0xFFFFFFFF).  One small
-// kernel, one copy to pinned memory, one synchronisation.
+// One readback for the whole batch of the most recent round: host_out [n, 4 + k_max + 1] = per batch row the accept
+// length a, the position, the tokens emitted since admission, the round's a+1 tokens (unused words 0xFFFFFFFF) and the slot's
+// status word.  One small kernel, one copy to pinned memory, one synchronisation.
 extern "C" int32_t wein_b200_engine_read_round(wein_b200_engine *e, uint32_t *host_out, uint32_t host_words, void *stream) {
     WB_CHECK_ARG(e && host_out, "engine_read_round: null pointer");
     WB_CHECK_ARG(e->last_n > 0, "engine_read_round: no round has run yet");
-    const uint32_t n = e->last_n, stride = 3 + e->P;
+    const uint32_t n = e->last_n, stride = 4 + e->P;
     WB_CHECK_ARG(host_words >= n * stride, "engine_read_round: %u words given, %u needed", host_words, n * stride);
     cudaStream_t st = (cudaStream_t)stream;
-    WB_LAUNCH((round_pack_kernel), (n + 127) / 128, 128, 0, st, e->d_slots, slot_state(e), e->d_accept_len, e->d_out_tokens, n, e->last_P, e->P, e->d_pack);
+    WB_LAUNCH((round_pack_kernel), (n + 127) / 128, 128, 0, st, e->d_slots, slot_state(e), e->d_accept_len, e->d_row_count, e->d_out_tokens, n, e->last_P, e->P,
+                                            e->d_pack);
     WB_LAUNCH_CHECK();
     CUDA_TRY(cudaMemcpyAsync(e->h_pack, e->d_pack, (size_t)n * stride * 4, cudaMemcpyDeviceToHost, st));
     CUDA_TRY(cudaStreamSynchronize(st));
@@ -857,7 +986,7 @@ extern "C" int32_t wein_b200_engine_read(wein_b200_engine *e, uint32_t slot, uin
     CUDA_TRY(cudaMemcpy(&pos, e->d_pos + slot, 4, cudaMemcpyDeviceToHost));
     if (host_n_tokens) *host_n_tokens = oc;
     if (host_pos) *host_pos = pos;
-    if (host_stats3) CUDA_TRY(cudaMemcpy(host_stats3, e->d_stats + (size_t)slot * 3, 24, cudaMemcpyDeviceToHost));
+    if (host_stats3) CUDA_TRY(cudaMemcpy(host_stats3, e->d_stats + (size_t)slot * STATS_WORDS, 24, cudaMemcpyDeviceToHost));
     if (host_tokens && cap) {
         // the most recent min(cap, emitted, ring size) tokens, oldest first
         uint32_t nread = oc < cap ? oc : cap;
@@ -870,4 +999,37 @@ extern "C" int32_t wein_b200_engine_read(wein_b200_engine *e, uint32_t slot, uin
     return WB_OK;
 }
 
-WB_TRACE_SETTER(engine)   // diagnostic builds only (see common.cuh); expands to nothing otherwise
+// The speculation counters of a slot (spec_stats / spec_k_stats of the reference, qwen.rs:4257-4259, :2670), WEIN_B200_STATS_WORDS
+// words: rounds, drafts, accepted, fallbacks, draft-length switches, rounds by draft count [8], rounds by accept length [9],
+// the last draft count, one spare.  Synchronises the stream.
+extern "C" int32_t wein_b200_engine_stats(wein_b200_engine *e, uint32_t slot, uint64_t *host_stats, void *stream) {
+    WB_CHECK_ARG(e && slot < e->cfg.max_seqs && host_stats, "engine_stats: bad argument");
+    CUDA_TRY(cudaStreamSynchronize((cudaStream_t)stream));
+    CUDA_TRY(cudaMemcpy(host_stats, e->d_stats + (size_t)slot * STATS_WORDS, STATS_WORDS * 8, cudaMemcpyDeviceToHost));
+    return WB_OK;
+}
+
+// Device status word of a slot (WEIN_B200_STATUS_* bits); clear != 0 resets it after the read.  Synchronises the stream.
+extern "C" int32_t wein_b200_engine_status(wein_b200_engine *e, uint32_t slot, uint32_t *host_status, uint32_t clear, void *stream) {
+    WB_CHECK_ARG(e && slot < e->cfg.max_seqs && host_status, "engine_status: bad argument");
+    cudaStream_t st = (cudaStream_t)stream;
+    CUDA_TRY(cudaStreamSynchronize(st));
+    CUDA_TRY(cudaMemcpy(host_status, e->d_status + slot, 4, cudaMemcpyDeviceToHost));
+    if (clear) {
+        WB_LAUNCH((clear_status_kernel), 1, 1, 0, st, e->d_status, slot);
+        WB_LAUNCH_CHECK();
+    }
+    return WB_OK;
+}
+
+// Phase timers (spec_timing_ms of the reference, qwen.rs:4277-4279): with on != 0, rounds run eagerly (use_graph = 0) record
+// events around the draft phase, the verify forward and acceptance + commit; host_ms3 (optional) receives the totals in
+// milliseconds since the timers were last switched on.  Graph replays are not broken down.
+extern "C" int32_t wein_b200_engine_timing(wein_b200_engine *e, uint32_t on, double *host_ms3) {
+    WB_CHECK_ARG(e != nullptr, "engine_timing: null engine");
+    fold_timing(e);
+    if (host_ms3) for (int i = 0; i < 3; i++) host_ms3[i] = e->ms_phase[i];
+    if (on && !e->timing) for (int i = 0; i < 3; i++) e->ms_phase[i] = 0.0;
+    e->timing = on != 0;
+    return WB_OK;
+}

@@ -21,10 +21,13 @@ __global__ void qk_prep_kernel(const bf16_t *qgkv, uint32_t ld, const bf16_t *qn
     const bf16_t *row = qgkv + (size_t)t * ld;
     const uint32_t he = kv_heads * hd;
     const bool is_q = unit < q_heads, is_k = !is_q && unit < q_heads + kv_heads;
+    // a row whose cache position is 0xFFFFFFFF belongs to no live chain position: it writes no K / V and rotates by position 0
+    const uint32_t kvp = kv_pos[t];
+    const bool dead = kvp == 0xffffffffu;
     size_t slot = 0;
     if (!is_q) {
-        uint32_t p = kv_pos[t];
-        slot = (size_t)block_table[(size_t)seq_ids[t] * bpr + p / 16] * 16 + p % 16;
+        if (dead) return;
+        slot = (size_t)block_table[(size_t)seq_ids[t] * bpr + kvp / 16] * 16 + kvp % 16;
     }
     if (!is_q && !is_k) {  // v head: plain copy into the page
         uint32_t h = unit - q_heads - kv_heads;
@@ -42,7 +45,8 @@ __global__ void qk_prep_kernel(const bf16_t *qgkv, uint32_t ld, const bf16_t *qn
     float rc = 0.0f, rs = 0.0f;
     if (i < rot_dim) {
         uint32_t p = i < half ? i : i - half;
-        size_t ci = (size_t)rope_pos[t] * half + p;
+        const uint32_t rp = rope_pos[t];
+        size_t ci = (size_t)(rp == 0xffffffffu ? 0u : rp) * half + p;
         rc = cosv[ci]; rs = sinv[ci];
     }
     if (is_q) gate[((size_t)t * q_heads + unit) * hd + i] = gv;
@@ -185,4 +189,29 @@ int32_t wb_rms_norm_gated_rows(const void *x, const void *z, uint32_t z_tok_stri
     return WB_OK;
 }
 
-WB_TRACE_SETTER(fused_glue)   // diagnostic builds only (see common.cuh); expands to nothing otherwise
+
+// ---- C-ABI of the fused forms, so that each one is checked on its own against the operator chain it replaces ----
+extern "C" {
+int32_t wein_b200_qk_prep(const void *qgkv, uint32_t ld, const void *qn, const void *kn, const void *cosv, const void *sinv,
+                          const void *rope_pos, const void *kv_pos, const void *seq_ids, const void *block_table, uint32_t bpr,
+                          void *qh, void *gate, void *k_pool, void *v_pool, uint32_t tokens, uint32_t q_heads, uint32_t kv_heads,
+                          uint32_t head_dim, uint32_t rot_dim, float eps, void *stream) {
+    WB_CHECK_ARG(qgkv && qn && kn && cosv && sinv && rope_pos && kv_pos && seq_ids && block_table && qh && gate && k_pool && v_pool,
+                 "qk_prep: null pointer");
+    WB_CHECK_ARG(ld >= 2 * q_heads * head_dim + 2 * kv_heads * head_dim, "qk_prep: row stride %u shorter than q|gate|k|v", ld);
+    return wb_qk_prep(qgkv, ld, qn, kn, (const float *)cosv, (const float *)sinv, (const uint32_t *)rope_pos, (const uint32_t *)kv_pos,
+                      (const uint32_t *)seq_ids, (const uint32_t *)block_table, bpr, qh, gate, k_pool, v_pool, tokens, q_heads, kv_heads,
+                      head_dim, rot_dim, eps, (cudaStream_t)stream);
+}
+int32_t wein_b200_mtp_cat(const void *tok, const void *embed, const void *hid, const void *hid_rows, const void *pre_e,
+                          const void *pre_h, void *cat, uint32_t rows, uint32_t hidden, float eps, void *stream) {
+    WB_CHECK_ARG(tok && embed && hid && pre_e && pre_h && cat, "mtp_cat: null pointer");
+    return wb_mtp_cat((const uint32_t *)tok, 1, embed, hid, (const uint32_t *)hid_rows, pre_e, pre_h, cat, rows, hidden, eps,
+                      (cudaStream_t)stream);
+}
+int32_t wein_b200_silu_mul_rows(const void *gu, uint32_t ld, void *out, uint32_t rows, uint32_t inter, void *stream) {
+    WB_CHECK_ARG(gu && out && ld >= 2 * inter, "silu_mul_rows: null pointer or row stride %u shorter than gate|up", ld);
+    return wb_silu_mul_rows(gu, ld, out, rows, inter, (cudaStream_t)stream);
+}
+}  // extern "C"
+

@@ -585,10 +585,6 @@ __global__ void __launch_bounds__(256) gdn_qk_kernel(const GdnLayerParams P) {
     }
 }
 
-// A/B switch: 0 keeps the one-launch layer at every grid size
-static bool g_gdn_split = true;
-extern "C" void wein_b200_gdn_split(uint32_t on) { g_gdn_split = on != 0; }
-
 int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log, const void *dt_bias,
                      const void *norm_w, void *state, uint32_t state_f32, void *out, const void *row_start, const void *row_count,
                      const void *in_row, const void *out_base, uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps,
@@ -605,7 +601,7 @@ int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *co
     p.n_rows = n_rows; p.k_heads = k_heads; p.v_heads = v_heads; p.l2_eps = l2_eps; p.rms_eps = rms_eps; p.log = (float *)log;
     WB_CHECK_ARG(((uintptr_t)log & 15u) == 0, "gdn_layer: the update log must be 16-byte aligned");
     const bool big = (uint64_t)n_rows * v_heads >= 296;
-    if (big && kq_scratch && g_gdn_split) {
+    if (big && kq_scratch) {
         // large grid: k-hat / q-hat once per k-head in a launch of their own
         WB_CHECK_ARG(((uintptr_t)kq_scratch & 15u) == 0, "gdn_layer: the k-hat / q-hat scratch must be 16-byte aligned");
         p.kq = (float *)kq_scratch;
@@ -737,4 +733,3 @@ extern "C" int32_t wein_b200_gdn_commit(const void *states, const void *logs, ui
                          accept_len, n_rows, v_heads, (cudaStream_t)stream);
 }
 
-WB_TRACE_SETTER(gdn)   // diagnostic builds only (see common.cuh); expands to nothing otherwise

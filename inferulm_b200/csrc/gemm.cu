@@ -18,11 +18,7 @@
 //    (batch-shape invariance: a verify row equals the same row of a plain decode step bit for bit);
 //  * small n with large k (the 2560-wide output projections) additionally split k over CTAs; partials go
 //    to a scratch buffer and the last CTA of a tile to arrive adds them in slice order (deterministic).
-// Larger m falls through to cuBLASLt, as in the reference.
-#include <cublasLt.h>
-#include <map>
-#include <mutex>
-#include <tuple>
+// Larger m runs the tensor-memory kernel of gemm_umma.cu (the reference hands those shapes to cuBLASLt).
 #include "common.cuh"
 #include "internal.h"
 
@@ -49,8 +45,6 @@ struct WgemmParams {
     float *partial;       // [ksplit][ctas][8/KW tiles * MT*128] when ksplit > 1
     uint32_t *counters;   // [ctas], zero on entry, left zero
     uint32_t m, n, k, lda, ldc, ksplit, kslice;  // kslice: k elements per CTA slice (multiple of 32)
-    const void *next_w;   // weights of the stream's next product (or null): their head is pulled into L2 by this kernel's
-    uint32_t next_lines;  //   CTAs as they finish, so HBM keeps streaming through the kernels in between; count of 128-byte lines
     uint32_t pf_row_bytes; // per weight row of a warp's slab: how far ahead of the register window the pre-wait L2 prefetch reaches
     uint32_t swiglu;      // 1: W = [gate; up] (n = 2*inter rows); tile rows 0-7 are gate rows, 8-15 the matching up rows, and
                           //    the epilogue writes bf16(bf16(silu(bf16 g)) * bf16 u) into C[m, inter]
@@ -154,11 +148,6 @@ __global__ void __launch_bounds__(256, (MT == 1 && UNR <= 4) ? 3 : 2) wgemm_kern
             }
         }
     }
-    if (P.next_lines) {
-        const char *nb = reinterpret_cast<const char *>(P.next_w);
-        const uint32_t nthreads = gridDim.x * gridDim.y * 256, me = (blockIdx.y * gridDim.x + blockIdx.x) * 256 + threadIdx.x;
-        for (uint32_t ln = me; ln < P.next_lines; ln += nthreads) asm volatile("prefetch.global.L2 [%0];" ::"l"(nb + (size_t)ln * 128));
-    }
 #pragma unroll
     for (int mt = 0; mt < MT; mt++)
 #pragma unroll
@@ -228,9 +217,7 @@ struct WgemmPlan { uint32_t kw, ksplit; };
 // kernel in front of this GEMM (a residual norm of 40 KB) is on the critical path -- its interval grows from ~2.4 to 4.8 us.
 // Whole slab 2.714 ms per round, nothing 2.705, 512 B 2.663, 640-768 B 2.612-2.622, 1024 B 2.66, 2048 B 2.68.  Loading fewer slots
 // of the register window before the wait was worse (none 2.78, half 2.64).
-static uint32_t g_force_kw = 0, g_force_ks = 0, g_force_unr = 0, g_pf_row_bytes = 768;
-extern "C" void wein_b200_gemm_prefetch_row_bytes(uint32_t b) { g_pf_row_bytes = b; }
-extern "C" void wein_b200_gemm_tune(uint32_t kw, uint32_t ksplit, uint32_t unr) { g_force_kw = kw; g_force_ks = ksplit; g_force_unr = unr; }
+constexpr uint32_t WG_PF_ROW_BYTES = 768;
 
 static WgemmPlan plan_for(uint32_t n_tiles, uint32_t k, bool has_scratch) {
     // Measured on B200 (graph replay, weights rotated through 3 GB, m = 4): the fewest warps per tile that still give
@@ -239,8 +226,7 @@ static WgemmPlan plan_for(uint32_t n_tiles, uint32_t k, bool has_scratch) {
     uint32_t kb = k / 32, kw = 1, ks = 1;
     while (kw < 8 && (n_tiles * kw + 7) / 8 < 280 && kb / (kw * 2) >= 4) kw *= 2;
     if (n_tiles >= 4096 && kb >= 32) kw = 4;
-    if (g_force_kw) kw = g_force_kw;
-    if (g_force_ks) ks = has_scratch ? g_force_ks : 1;
+    (void)has_scratch;
     return {kw, ks};
 }
 
@@ -250,18 +236,15 @@ extern "C" uint64_t wein_b200_gemm_scratch_bytes(uint32_t n_max) {
     return 8ull * 592 * (8 * 4 * 128) * 4 + 4096 * 4;
 }
 
-extern bool g_wb_pdl_gemm;
-struct PdlScope { bool saved; PdlScope() : saved(g_wb_pdl) { g_wb_pdl = g_wb_pdl && g_wb_pdl_gemm; } ~PdlScope() { g_wb_pdl = saved; } };
 template <int MT, int KW>
 static void wgemm_go(const WgemmParams &p, dim3 grid, uint32_t unr, cudaStream_t st) {
-    PdlScope scope;
     if constexpr (MT == 1) {
         if (unr == 8) { WB_LAUNCH((wgemm_kernel<MT, KW, 8, 8>), grid, 256, 0, st, p); return; }
         if (unr == 6) { WB_LAUNCH((wgemm_kernel<MT, KW, 6, 6>), grid, 256, 0, st, p); return; }
     }
     if constexpr (MT == 4) {
         // 25..32 rows: a 6-deep weight window with activations fetched 2 blocks ahead is what fits 128 registers
-        if (g_force_unr != 4) { WB_LAUNCH((wgemm_kernel<MT, KW, 6, 2>), grid, 256, 0, st, p); return; }
+        WB_LAUNCH((wgemm_kernel<MT, KW, 6, 2>), grid, 256, 0, st, p); return;
     }
     WB_LAUNCH((wgemm_kernel<MT, KW, 4, 4>), grid, 256, 0, st, p);
 }
@@ -275,37 +258,11 @@ static void wgemm_go_kw(const WgemmParams &p, dim3 grid, uint32_t kw, uint32_t u
     }
 }
 
-// One-shot hint consumed by the next skinny-GEMM launch of this thread: the weights the stream multiplies next.
-static thread_local const void *t_next_w = nullptr;
-static thread_local uint64_t t_next_bytes = 0;
-static uint64_t g_prefetch_cap = 0;  // measured on B200: a prefetch issued from a bandwidth-bound kernel's tail only moves time around (off)
-void wb_gemm_set_next(const void *w, uint64_t bytes) { t_next_w = w; t_next_bytes = bytes; }
-extern "C" void wein_b200_gemm_prefetch_cap(uint64_t bytes) { g_prefetch_cap = bytes; }
-
-// 0: register-streaming kernel of this file (default); 1: the TMA-staged kernel (gemm_stream.cu).  Measured on B200 at m = 4
-// (graph replay, weights rotated through 3 GB): staged wins on the largest product (gate|up 94 MB: 16.1 vs 17.9 us, 5.86 vs
-// 5.26 TB/s), ties on the vocabulary projection (6.39 vs 6.32 TB/s) and loses on the 2560-row projections (160 row tiles
-// on 148 SMs: 7.1 vs 5.0 us); a whole round is 2.89 vs 2.77 ms.  Mixing the two inside a round costs far more (3.4 ms): one
-// wants the SM's memory array as shared memory, the other as L1 (it lands its loads in flight there: at a 75 % shared
-// carve-out the register-streaming kernel drops from 5.3 to 3.5 TB/s), and an SM drains before it changes the split.
-static uint32_t g_gemm_impl = 0;
-extern "C" void wein_b200_gemm_impl(uint32_t impl) { g_gemm_impl = impl & 1; }
-
 static int32_t wgemm_launch(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc,
                             void *scratch, uint64_t scratch_bytes, bool swiglu, cudaStream_t st) {
-    if (g_gemm_impl == 1 && wb_tgemm_supports(n, k, swiglu)) {
-        t_next_w = nullptr; t_next_bytes = 0;
-        PdlScope scope;
-        return wb_tgemm(a, w, c, m, n, k, lda, ldc, swiglu, st);
-    }
     WgemmParams p{};
     p.A = (const bf16_t *)a; p.W = (const bf16_t *)w; p.C = (bf16_t *)c;
-    p.m = m; p.n = n; p.k = k; p.lda = lda; p.ldc = ldc; p.swiglu = swiglu ? 1 : 0; p.pf_row_bytes = g_pf_row_bytes;
-    if (t_next_w && g_prefetch_cap) {
-        uint64_t nbytes = t_next_bytes < g_prefetch_cap ? t_next_bytes : g_prefetch_cap;
-        p.next_w = t_next_w; p.next_lines = (uint32_t)(nbytes / 128);
-    }
-    t_next_w = nullptr; t_next_bytes = 0;
+    p.m = m; p.n = n; p.k = k; p.lda = lda; p.ldc = ldc; p.swiglu = swiglu ? 1 : 0; p.pf_row_bytes = WG_PF_ROW_BYTES;
     uint32_t tiles = swiglu ? (n / 2 + 7) / 8 : (n + 15) / 16;
     int mt = (m + 7) / 8;
     WgemmPlan pl = plan_for(tiles, k, scratch != nullptr);
@@ -320,7 +277,7 @@ static int32_t wgemm_launch(const void *a, const void *w, void *c, uint32_t m, u
     p.counters = (uint32_t *)scratch;
     p.partial = scratch ? (float *)((char *)scratch + 4096 * 4) : nullptr;
     dim3 grid(ctas, pl.ksplit);
-    uint32_t unr = g_force_unr ? g_force_unr : (ctas * pl.ksplit <= 296 ? 8 : 4);
+    uint32_t unr = ctas * pl.ksplit <= 296 ? 8 : 4;
     switch (mt) {
         case 1: wgemm_go_kw<1>(p, grid, pl.kw, unr, st); break;
         case 2: wgemm_go_kw<2>(p, grid, pl.kw, unr, st); break;
@@ -331,176 +288,51 @@ static int32_t wgemm_launch(const void *a, const void *w, void *c, uint32_t m, u
     return WB_OK;
 }
 
-// ---------------------------------------------------------------- cuBLASLt path (m > 32)
-struct LtState {
-    cublasLtHandle_t h = nullptr;
-    void *ws = nullptr;
-    size_t ws_bytes = 32u << 20;
-    std::mutex mu;
-};
-static LtState g_lt;
-
-static int32_t lt_init() {
-    if (!g_lt.h) {
-        if (cublasLtCreate(&g_lt.h) != CUBLAS_STATUS_SUCCESS) { wb_set_error("cublasLtCreate failed"); return WB_ERR_CUDA; }
-        if (cudaMalloc(&g_lt.ws, g_lt.ws_bytes) != cudaSuccess) { wb_set_error("cuBLASLt workspace allocation failed"); return WB_ERR_CUDA; }
-    }
-    return WB_OK;
-}
-int32_t wb_gemm_warmup() {
-    if (int32_t rc = wb_tgemm_init()) return rc;
-    std::lock_guard<std::mutex> lk(g_lt.mu);
-    return lt_init();
-}
-
-// Largest row count the skinny kernel takes; above it the product goes to cuBLASLt.  32 by default.  The skinny kernel
-// keeps a row's bits independent of the batch, which greedy speculation needs (a verify row must equal the same row of a
-// plain decode step), but from 17 rows on it streams at only ~3 TB/s where the library reaches ~5 TB/s: a caller that does
-// not need that property (a round of sampled chains) may lower the limit to 16 for the duration of its launches.
-static uint32_t g_skinny_max = 32;
-void wb_gemm_set_skinny_max(uint32_t m) { g_skinny_max = m < 32 ? m : 32; }
-uint32_t wb_gemm_skinny_max() { return g_skinny_max; }
-
-// Shape -> algorithm chosen for it: the heuristic's first answer, or the fastest of its first 16 answers once the
-// shape has been tuned (wb_gemm_lt_autotune: timed on the device, outside any capture).
-struct LtKey {
-    uint32_t m, n, k, lda, ldc;
-    bool operator<(const LtKey &o) const { return std::tie(m, n, k, lda, ldc) < std::tie(o.m, o.n, o.k, o.lda, o.ldc); }
-};
-struct LtPlan { cublasLtMatmulAlgo_t algo; bool tuned; };
-static std::map<LtKey, LtPlan> g_lt_plans;
-
-struct LtDesc {
-    cublasLtMatmulDesc_t desc = nullptr;
-    cublasLtMatrixLayout_t la = nullptr, lb = nullptr, lc = nullptr;
-    ~LtDesc() {
-        if (lc) cublasLtMatrixLayoutDestroy(lc);
-        if (lb) cublasLtMatrixLayoutDestroy(lb);
-        if (la) cublasLtMatrixLayoutDestroy(la);
-        if (desc) cublasLtMatmulDescDestroy(desc);
-    }
-    // column-major view: C^T [n x m] = W [n x k] * A^T [k x m]  ->  op(W) = T on the stored k x n, op(A) = N on k x m
-    bool init(uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc) {
-        cublasOperation_t ta = CUBLAS_OP_T, tb = CUBLAS_OP_N;
-        if (cublasLtMatmulDescCreate(&desc, CUBLAS_COMPUTE_32F, CUDA_R_32F) != CUBLAS_STATUS_SUCCESS) return false;
-        cublasLtMatmulDescSetAttribute(desc, CUBLASLT_MATMUL_DESC_TRANSA, &ta, sizeof ta);
-        cublasLtMatmulDescSetAttribute(desc, CUBLASLT_MATMUL_DESC_TRANSB, &tb, sizeof tb);
-        return cublasLtMatrixLayoutCreate(&la, CUDA_R_16BF, k, n, k) == CUBLAS_STATUS_SUCCESS &&
-               cublasLtMatrixLayoutCreate(&lb, CUDA_R_16BF, k, m, lda) == CUBLAS_STATUS_SUCCESS &&
-               cublasLtMatrixLayoutCreate(&lc, CUDA_R_16BF, n, m, ldc) == CUBLAS_STATUS_SUCCESS;
-    }
-};
-
-static int lt_candidates(const LtDesc &d, cublasLtMatmulHeuristicResult_t *out, int want) {
-    cublasLtMatmulPreference_t pref = nullptr;
-    int found = 0;
-    if (cublasLtMatmulPreferenceCreate(&pref) != CUBLAS_STATUS_SUCCESS) return 0;
-    cublasLtMatmulPreferenceSetAttribute(pref, CUBLASLT_MATMUL_PREF_MAX_WORKSPACE_BYTES, &g_lt.ws_bytes, sizeof g_lt.ws_bytes);
-    if (cublasLtMatmulAlgoGetHeuristic(g_lt.h, d.desc, d.la, d.lb, d.lc, d.lc, pref, want, out, &found) != CUBLAS_STATUS_SUCCESS) found = 0;
-    cublasLtMatmulPreferenceDestroy(pref);
-    return found;
-}
-
-static int32_t lt_gemm(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, cudaStream_t st) {
-    std::lock_guard<std::mutex> lk(g_lt.mu);
-    if (lt_init() != WB_OK) return WB_ERR_CUDA;
-    LtDesc d;
-    if (!d.init(m, n, k, lda, ldc)) { wb_set_error("cuBLASLt descriptor setup failed"); return WB_ERR_CUDA; }
-    const LtKey key{m, n, k, lda, ldc};
-    auto it = g_lt_plans.find(key);
-    if (it == g_lt_plans.end()) {
-        cublasLtMatmulHeuristicResult_t heur;
-        if (lt_candidates(d, &heur, 1) < 1) { wb_set_error("cuBLASLt: no algorithm for m=%u n=%u k=%u", m, n, k); return WB_ERR_CUDA; }
-        it = g_lt_plans.insert({key, LtPlan{heur.algo, false}}).first;
-    }
-    const float alpha = 1.0f, beta = 0.0f;
-    if (cublasLtMatmul(g_lt.h, d.desc, &alpha, w, d.la, a, d.lb, &beta, c, d.lc, c, d.lc, &it->second.algo, g_lt.ws, g_lt.ws_bytes, st) != CUBLAS_STATUS_SUCCESS) {
-        wb_set_error("cublasLtMatmul failed for m=%u n=%u k=%u", m, n, k);
-        return WB_ERR_CUDA;
-    }
-    return WB_OK;
-}
-
-// Times the library's first 16 candidate algorithms for one shape on the caller's operands (c is overwritten) and keeps the
-// fastest for later calls.  A 256 MB buffer is rewritten between runs so every run streams its weights from HBM, as in a
-// round.  Synchronises the stream: never call under capture.  No-op for shapes the skinny kernel serves or already tuned.
-static bool g_lt_tune_on = true;
-extern "C" void wein_b200_gemm_lt_tune(uint32_t on) { g_lt_tune_on = on != 0; }   // A/B switch: 0 keeps the heuristic's first answer
-int32_t wb_gemm_lt_autotune(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, cudaStream_t st) {
-    if (m <= g_skinny_max || !g_lt_tune_on) return WB_OK;
-    std::lock_guard<std::mutex> lk(g_lt.mu);
-    if (lt_init() != WB_OK) return WB_ERR_CUDA;
-    const LtKey key{m, n, k, lda, ldc};
-    auto it = g_lt_plans.find(key);
-    if (it != g_lt_plans.end() && it->second.tuned) return WB_OK;
-    LtDesc d;
-    if (!d.init(m, n, k, lda, ldc)) { wb_set_error("cuBLASLt descriptor setup failed"); return WB_ERR_CUDA; }
-    cublasLtMatmulHeuristicResult_t cand[16];
-    const int found = lt_candidates(d, cand, 16);
-    if (found < 1) { wb_set_error("cuBLASLt: no algorithm for m=%u n=%u k=%u", m, n, k); return WB_ERR_CUDA; }
-    void *flush = nullptr;
-    const size_t flush_bytes = 256u << 20;
-    cudaEvent_t e0 = nullptr, e1 = nullptr;
-    if (cudaMalloc(&flush, flush_bytes) != cudaSuccess) { cudaGetLastError(); flush = nullptr; }
-    cudaEventCreate(&e0); cudaEventCreate(&e1);
-    const float alpha = 1.0f, beta = 0.0f;
-    int best = 0;
-    float best_ms = 1e30f;
-    for (int i = 0; i < found; i++) {
-        if (cand[i].state != CUBLAS_STATUS_SUCCESS || cand[i].workspaceSize > g_lt.ws_bytes) continue;
-        float total = 0.0f;
-        bool ok = true;
-        for (int rep = 0; rep < 4 && ok; rep++) {
-            if (flush) cudaMemsetAsync(flush, rep, flush_bytes, st);
-            cudaEventRecord(e0, st);
-            ok = cublasLtMatmul(g_lt.h, d.desc, &alpha, w, d.la, a, d.lb, &beta, c, d.lc, c, d.lc, &cand[i].algo, g_lt.ws, g_lt.ws_bytes, st) == CUBLAS_STATUS_SUCCESS;
-            cudaEventRecord(e1, st);
-            if (cudaEventSynchronize(e1) != cudaSuccess) ok = false;
-            float ms = 0.0f;
-            cudaEventElapsedTime(&ms, e0, e1);
-            if (rep > 0) total += ms;   // the first run of an algorithm loads its kernel
-        }
-        if (ok && total < best_ms) { best_ms = total; best = i; }
-    }
-    cudaEventDestroy(e0); cudaEventDestroy(e1);
-    if (flush) cudaFree(flush);
-    cudaGetLastError();
-    g_lt_plans[key] = LtPlan{cand[best].algo, true};
-    return WB_OK;
-}
+// Which kernel multiplies.  The skinny kernel and the tensor-memory kernel each keep a token's sum independent of the batch,
+// but they do not agree with each other bit for bit, so a caller that compares forwards of different row counts (a verify
+// forward against a plain decode step) must run all of them on one kernel: WB_GEMM_TC for every m when any of them exceeds
+// 32 rows.  WB_GEMM_AUTO picks by m alone.
+int32_t wb_gemm_init() { return wb_ugemm_init(); }
 
 // Shared by the engine: strided rows (lda / ldc in elements) so a GEMM can write into a wider buffer.
 int32_t wb_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc,
-                   void *scratch, uint64_t scratch_bytes, cudaStream_t st) {
+                   void *scratch, uint64_t scratch_bytes, uint32_t path, cudaStream_t st) {
     WB_CHECK_ARG(a && w && c, "gemm_wt: null pointer");
     WB_CHECK_ARG(n > 0 && k > 0 && k % 32 == 0, "gemm_wt: k = %u must be a positive multiple of 32", k);
     WB_CHECK_ARG(lda >= k && ldc >= n && lda % 8 == 0, "gemm_wt: bad leading dimensions");
     WB_CHECK_ARG(((((uintptr_t)a) | ((uintptr_t)w)) & 15u) == 0, "gemm_wt: operands must be 16-byte aligned");
     if (m == 0) return WB_OK;
-    if (m <= g_skinny_max) return wgemm_launch(a, w, c, m, n, k, lda, ldc, scratch, scratch_bytes, false, st);
-    return lt_gemm(a, w, c, m, n, k, lda, ldc, st);
+    if (m <= 32 && path != WB_GEMM_TC) return wgemm_launch(a, w, c, m, n, k, lda, ldc, scratch, scratch_bytes, false, st);
+    return wb_ugemm(a, w, c, m, n, k, lda, ldc, false, st);
 }
 
 // Fused gate|up projection + SwiGLU activation: W = [gate; up] of shape [2*inter, k]; out[m, inter] =
 // bf16(bf16(silu(bf16(a.gate_j))) * bf16(a.up_j)) -- the values silu_mul produces from the separately rounded
-// projections (kernels/src/lib.rs:576-584 of the reference), without materialising them.  m <= 32 only.
+// projections (kernels/src/lib.rs:576-584 of the reference), without materialising them.
 int32_t wb_gemm_swiglu(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k, uint32_t lda,
-                       uint32_t ldc, void *scratch, uint64_t scratch_bytes, cudaStream_t st) {
+                       uint32_t ldc, void *scratch, uint64_t scratch_bytes, uint32_t path, cudaStream_t st) {
     WB_CHECK_ARG(a && w_gate_up && out, "gemm_swiglu: null pointer");
-    WB_CHECK_ARG(inter > 0 && k > 0 && k % 32 == 0 && m <= 32, "gemm_swiglu: k = %u must be a multiple of 32 and m = %u at most 32", k, m);
+    WB_CHECK_ARG(inter > 0 && k > 0 && k % 32 == 0, "gemm_swiglu: k = %u must be a positive multiple of 32", k);
     WB_CHECK_ARG(lda >= k && ldc >= inter && lda % 8 == 0, "gemm_swiglu: bad leading dimensions");
+    WB_CHECK_ARG(((((uintptr_t)a) | ((uintptr_t)w_gate_up)) & 15u) == 0, "gemm_swiglu: operands must be 16-byte aligned");
     if (m == 0) return WB_OK;
-    return wgemm_launch(a, w_gate_up, out, m, 2 * inter, k, lda, ldc, scratch, scratch_bytes, true, st);
+    if (m <= 32 && path != WB_GEMM_TC) return wgemm_launch(a, w_gate_up, out, m, 2 * inter, k, lda, ldc, scratch, scratch_bytes, true, st);
+    return wb_ugemm(a, w_gate_up, out, m, 2 * inter, k, lda, ldc, true, st);
 }
 
 extern "C" int32_t wein_b200_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, void *scratch,
                                      uint64_t scratch_bytes, void *stream) {
-    return wb_gemm_wt(a, w, c, m, n, k, k, n, scratch, scratch_bytes, (cudaStream_t)stream);
+    return wb_gemm_wt(a, w, c, m, n, k, k, n, scratch, scratch_bytes, WB_GEMM_AUTO, (cudaStream_t)stream);
+}
+extern "C" int32_t wein_b200_gemm_wt_tc(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, void *stream) {
+    return wb_gemm_wt(a, w, c, m, n, k, k, n, nullptr, 0, WB_GEMM_TC, (cudaStream_t)stream);
 }
 
 extern "C" int32_t wein_b200_gemm_swiglu(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k,
                                          void *scratch, uint64_t scratch_bytes, void *stream) {
-    return wb_gemm_swiglu(a, w_gate_up, out, m, inter, k, k, inter, scratch, scratch_bytes, (cudaStream_t)stream);
+    return wb_gemm_swiglu(a, w_gate_up, out, m, inter, k, k, inter, scratch, scratch_bytes, WB_GEMM_AUTO, (cudaStream_t)stream);
 }
-
-WB_TRACE_SETTER(gemm)   // diagnostic builds only (see common.cuh); expands to nothing otherwise
+extern "C" int32_t wein_b200_gemm_swiglu_tc(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k,
+                                            void *stream) {
+    return wb_gemm_swiglu(a, w_gate_up, out, m, inter, k, k, inter, nullptr, 0, WB_GEMM_TC, (cudaStream_t)stream);
+}

@@ -3,25 +3,20 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+enum { WB_GEMM_AUTO = 0, WB_GEMM_TC = 1 };  // kernel choice of a product: by row count (<= 32: skinny), or the tensor-memory kernel always
 int32_t wb_gemm_wt(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc,
-                   void *scratch, uint64_t scratch_bytes, cudaStream_t st);
+                   void *scratch, uint64_t scratch_bytes, uint32_t path, cudaStream_t st);
 int32_t wb_gemm_swiglu(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k, uint32_t lda,
-                       uint32_t ldc, void *scratch, uint64_t scratch_bytes, cudaStream_t st);
-void wb_gemm_set_next(const void *w, uint64_t bytes);  // hint for the next skinny GEMM launch: what the stream multiplies after it
-int32_t wb_tgemm(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, bool swiglu,
-                 cudaStream_t st);  // bulk-copy staged skinny GEMM (m <= 32), arguments already validated
-bool wb_tgemm_supports(uint32_t n, uint32_t k, bool swiglu);
-int32_t wb_tgemm_init();  // its one-time shared-memory opt-in, outside any stream capture
-int32_t wb_gemm_lt_autotune(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc,
-                            cudaStream_t st);  // picks the fastest library algorithm for a shape with m > 32; synchronises, not capturable
-void wb_gemm_set_skinny_max(uint32_t m);  // rows up to which the batch-invariant skinny kernel is used (<= 32, default 32)
-uint32_t wb_gemm_skinny_max();
-int32_t wb_gemm_warmup();  // creates the cuBLASLt handle and workspace outside any stream capture
+                       uint32_t ldc, void *scratch, uint64_t scratch_bytes, uint32_t path, cudaStream_t st);
+int32_t wb_ugemm(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, bool swiglu,
+                 cudaStream_t st);  // tensor-memory GEMM (gemm_umma.cu), arguments already validated
+int32_t wb_ugemm_init();  // driver entry point and shared-memory opt-in of the current device, outside any stream capture
+int32_t wb_gemm_init();
 int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, const void *block_table, const void *seq_ids,
                        const void *positions, const void *row_start, const void *row_count, const void *gate, void *out,
                        float q_scale, uint32_t bpr, uint32_t block_size, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
                        uint32_t n_spans, uint32_t max_count, uint32_t max_ctx, uint32_t seg_pages, void *scratch,
-                       uint64_t scratch_bytes, cudaStream_t st);
+                       uint64_t scratch_bytes, uint32_t *status, cudaStream_t st);  // status: optional, indexed by sequence id
 int32_t wb_attn_init(uint32_t head_dim);  // one-time shared-memory opt-in, outside any stream capture
 int32_t wein_b200_argmax_partials(const void *x, const void *rows, void *part, uint32_t n, uint32_t s, uint32_t split, cudaStream_t st);
 

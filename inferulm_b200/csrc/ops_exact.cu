@@ -569,4 +569,3 @@ int32_t wein_b200_argmax_rows_noalloc(const void *x, const void *rows, void *out
 
 }  // extern "C"
 
-WB_TRACE_SETTER(ops_exact)   // diagnostic builds only (see common.cuh); expands to nothing otherwise

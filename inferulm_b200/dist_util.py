@@ -14,6 +14,21 @@ def shard_sequences(n_total, rank, world):
     return [i for i in range(n_total) if i % world == rank]
 
 
+def pack_sequences(costs, world):
+    """Longest-first greedy bin packing: sequences sorted by cost (prompt + output tokens), largest first, each to the rank
+    with the least cost so far (ties to the lowest rank).  Returns one list of sequence indices per rank, in the order the
+    rank runs them.  Deterministic, so every rank computes the same assignment without communicating."""
+    costs = np.asarray(costs, dtype=np.int64)
+    order = sorted(range(costs.size), key=lambda i: (-int(costs[i]), i))
+    load = [0] * world
+    bins = [[] for _ in range(world)]
+    for i in order:
+        r = min(range(world), key=lambda j: (load[j], j))
+        bins[r].append(i)
+        load[r] += int(costs[i])
+    return bins
+
+
 def rank_prompts(rank, batch, prompt_len, vocab, base_seed=1000):
     """The prompts of one rank: seeded by the rank so that ranks run different sequences."""
     rs = np.random.default_rng(base_seed + rank)

@@ -6,7 +6,6 @@ sequences, prefill, run speculative rounds, read tokens and counters.  torch is
 used only to own device memory (the synthetic weights) and the CUDA stream.
 """
 import ctypes as C
-import os
 from dataclasses import dataclass, field
 
 import numpy as np
@@ -22,7 +21,7 @@ class ModelCfg(C.Structure):
                                           "lin_k_heads", "lin_v_heads", "lin_k_dim", "lin_v_dim", "conv_kernel")] + [
         ("rms_eps", C.c_float), ("l2_eps", C.c_float), ("rope_theta", C.c_double), ("layer_is_full", C.c_uint8 * MAX_LAYERS),
         ("has_mtp", C.c_uint32), ("max_seqs", C.c_uint32), ("k_max", C.c_uint32), ("max_pos", C.c_uint32), ("n_pages", C.c_uint32),
-        ("state_f32", C.c_uint32), ("attn_seg_pages", C.c_uint32)]
+        ("state_f32", C.c_uint32), ("attn_seg_pages", C.c_uint32), ("state_snapshots", C.c_uint32)]
 
 
 _LAYER_FIELDS = ("ln1", "ln2", "wg", "wu", "wd", "qg", "k", "v", "qn", "kn", "o", "qkv", "z", "a", "b", "conv", "a_log", "dt_bias",
@@ -148,7 +147,8 @@ class SyntheticWeights:
 
 
 class Engine:
-    def __init__(self, weights: SyntheticWeights, max_seqs=1, k_max=3, max_pos=4096, n_pages=None, state_f32=True, attn_seg_pages=0):
+    def __init__(self, weights: SyntheticWeights, max_seqs=1, k_max=3, max_pos=4096, n_pages=None, state_f32=True, attn_seg_pages=0,
+                 state_snapshots=False):
         s = weights.shape
         self.weights, self.shape = weights, s
         self.lib = load()
@@ -163,14 +163,14 @@ class Engine:
         self.bpr = (max_pos + 15) // 16
         self.n_pages = n_pages if n_pages is not None else max_seqs * self.bpr
         cfg.has_mtp, cfg.max_seqs, cfg.k_max, cfg.max_pos, cfg.n_pages = int(s.has_mtp), max_seqs, k_max, max_pos, self.n_pages
-        # A/B switch for measurements: WEIN_B200_SEG_PAGES overrides the automatic attention segment size
-        cfg.state_f32, cfg.attn_seg_pages = int(state_f32), attn_seg_pages or int(os.environ.get("WEIN_B200_SEG_PAGES", "0"))
+        cfg.state_f32, cfg.attn_seg_pages, cfg.state_snapshots = int(state_f32), attn_seg_pages, int(state_snapshots)
         self.cfg, self.max_seqs, self.k_max, self.max_pos = cfg, max_seqs, k_max, max_pos
         # rounds are replayed as CUDA graphs, which cannot be captured on the legacy default stream
         self.stream = torch.cuda.Stream()
         self.h = C.c_void_p()
         check(self.lib.wein_b200_engine_create(C.byref(cfg), C.byref(weights.c), C.byref(self.h)))
         self._free_pages = list(range(self.n_pages))
+        self._cap = {}   # slot -> position limit (16 x admitted pages, at most max_pos)
 
     def close(self):
         if self.h:
@@ -200,7 +200,16 @@ class Engine:
         arr = (C.c_uint32 * len(pages))(*pages)
         check(self.lib.wein_b200_engine_admit(self.h, C.c_uint32(slot), arr, C.c_uint32(len(pages)), C.c_float(temp), C.c_uint32(top_k),
                                               C.c_float(top_p), C.c_uint64(seed), self._stream()))
+        self._cap[slot] = min(self.max_pos, 16 * len(pages))
         return pages
+
+    def resume(self, slot, position, pending_token):
+        """Starts an admitted slot at `position` (KV pages and state row written by the caller: a prefix-cache hit)."""
+        check(self.lib.wein_b200_engine_resume(self.h, C.c_uint32(slot), C.c_uint32(position), C.c_uint32(pending_token), self._stream()))
+
+    def set_spec(self, slot, k):
+        """Per-request draft length: later rounds verify min(round k, k) drafts for the slot (0 = plain decode row)."""
+        check(self.lib.wein_b200_engine_set_spec(self.h, C.c_uint32(slot), C.c_uint32(k), self._stream()))
 
     def prefill(self, slots, prompts):
         slots = list(slots)
@@ -215,6 +224,51 @@ class Engine:
         check(self.lib.wein_b200_engine_spec_step(self.h, C.c_uint32(sl.size), sl.ctypes.data_as(C.c_void_p), C.c_uint32(k),
                                                   C.c_uint32(min(ctx_bound, self.max_pos)), C.c_uint32(int(use_graph)), self._stream()))
 
+    def draft(self, slots, k, out=None, use_graph=True):
+        """The draft phase alone: k MTP forwards; `out` (int32 CUDA tensor [n, k], optional) receives the drafts."""
+        sl = np.asarray(slots, np.uint32)
+        check(self.lib.wein_b200_engine_draft(self.h, C.c_uint32(sl.size), sl.ctypes.data_as(C.c_void_p), C.c_uint32(k),
+                                              C.c_void_p(out.data_ptr() if out is not None else 0), C.c_uint32(int(use_graph)), self._stream()))
+
+    VERIFY_GRAPH, VERIFY_FORCE_SLOTS, VERIFY_DRY_RUN, VERIFY_ENGINE_DRAFTS = 1, 2, 4, 8
+
+    def spec_verify(self, slots, k, drafts, ctx_bound, n_drafts=None, q=None, use_graph=True, dry_run=False, engine_drafts=False):
+        """Verify + accept + commit with the caller's drafts: int32 CUDA tensors drafts [n, k], n_drafts [n] (optional),
+        q = (ids [n, k, 64] int32, probs [n, k, 64] float32, counts [n, k] int32) (optional)."""
+        sl = np.asarray(slots, np.uint32)
+        flags = (self.VERIFY_GRAPH if use_graph else 0) | (self.VERIFY_DRY_RUN if dry_run else 0) | (self.VERIFY_ENGINE_DRAFTS if engine_drafts else 0)
+        p = lambda t: C.c_void_p(t.data_ptr() if t is not None else 0)
+        qi, qp, qn = q if q is not None else (None, None, None)
+        check(self.lib.wein_b200_engine_spec_verify(self.h, C.c_uint32(sl.size), sl.ctypes.data_as(C.c_void_p), C.c_uint32(k), p(drafts), p(n_drafts),
+                                                    p(qi), p(qp), p(qn), C.c_uint32(min(ctx_bound, self.max_pos)), C.c_uint32(flags), self._stream()))
+
+    def warm(self, slots, k, ctx_bound, what=1):
+        """Captures the graphs of later rounds of this shape (what: 1 spec_step, 2 spec_verify, 4 dry-run verify, 8 draft)."""
+        sl = np.asarray(slots, np.uint32)
+        check(self.lib.wein_b200_engine_warm(self.h, C.c_uint32(sl.size), sl.ctypes.data_as(C.c_void_p), C.c_uint32(k),
+                                             C.c_uint32(min(ctx_bound, self.max_pos)), C.c_uint32(what), self._stream()))
+
+    STATS_WORDS = 24
+
+    def stats(self, slot):
+        """All speculation counters of a slot: rounds, drafts, accepted, fallbacks, k switches, rounds by draft count,
+        rounds by accept length."""
+        w = (C.c_uint64 * self.STATS_WORDS)()
+        check(self.lib.wein_b200_engine_stats(self.h, C.c_uint32(slot), w, self._stream()))
+        v = [int(x) for x in w]
+        return dict(rounds=v[0], drafts=v[1], accepted=v[2], fallbacks=v[3], k_switches=v[4], by_k=v[5:13], by_accept=v[13:22], last_k=v[22])
+
+    def status(self, slot, clear=False):
+        v = C.c_uint32()
+        check(self.lib.wein_b200_engine_status(self.h, C.c_uint32(slot), C.byref(v), C.c_uint32(int(clear)), self._stream()))
+        return v.value
+
+    def timing(self, on):
+        """Switches the phase timers of eager rounds on / off; returns the totals (draft, forward, finish) in ms so far."""
+        ms = (C.c_double * 3)()
+        check(self.lib.wein_b200_engine_timing(self.h, C.c_uint32(int(on)), ms))
+        return tuple(float(x) for x in ms)
+
     def read(self, slot, cap=8192):
         toks = np.zeros(cap, np.uint32)
         n, pos = C.c_uint32(), C.c_uint32()
@@ -224,9 +278,9 @@ class Engine:
         return toks[: min(n.value, cap)].copy(), pos.value, dict(rounds=int(stats[0]), drafts=int(stats[1]), accepted=int(stats[2]))
 
     def read_round(self, n):
-        """One readback for the batch of the most recent round: array [n, 3 + k_max + 1] of
-        (accept length, position, tokens emitted since admission, the round's tokens padded with 0xFFFFFFFF)."""
-        stride = 3 + self.k_max + 1
+        """One readback for the batch of the most recent round: array [n, 4 + k_max + 1] of
+        (accept length, position, tokens emitted since admission, the round's tokens padded with 0xFFFFFFFF, status word)."""
+        stride = 4 + self.k_max + 1
         out = np.empty(n * stride, np.uint32)
         check(self.lib.wein_b200_engine_read_round(self.h, out.ctypes.data_as(C.c_void_p), C.c_uint32(out.size), self._stream()))
         return out.reshape(n, stride)
@@ -267,19 +321,22 @@ class Engine:
             cnt = self.counts(slots)
             left = n_new - min(c for c, _ in cnt)
             bound = max(p for _, p in cnt)
-            if left <= 0 or bound + k + 1 > self.max_pos:
+            # rounds that certainly stay below every slot's position limit (a round advances a slot by at most k + 1)
+            room = min((self._cap.get(s, self.max_pos) - p) // (k + 1) for s, (_, p) in zip(slots, cnt))
+            if left <= 0 or room <= 0:
                 return rounds
-            burst = max(1, left // (k + 1))
+            burst = min(max(1, left // (k + 1)), room)
             for _ in range(burst):
                 bound = min(bound + k + 1, self.max_pos)
                 self.spec_step(slots, k, bound, use_graph)
                 rounds += 1
 
     def generate_adaptive(self, slots, n_new, k_cap, use_graph=True):
-        """As generate(), with the draft length chosen per round by the reference's adaptive policy (spec_policy.SpecPolicy,
-        one state per slot; the batch drafts as far as its most optimistic slot).  The policy needs each round's accept
-        counts, so the counters are read back after every round: this is the host-paced mode the reference runs in.
-        Returns (rounds, list of the k used per round)."""
+        """As generate(), with each slot's draft length chosen per round by the reference's adaptive policy
+        (spec_policy.SpecPolicy, one state per slot, qwen.rs:2510-2568): the round drafts as far as its most optimistic slot
+        and every slot verifies its own number of drafts (set_spec), as the reference's per-request k.  The policy needs
+        each round's accept counts, so the counters are read back after every round: the host-paced mode the reference
+        runs in.  Returns (rounds, list of the round k used)."""
         from .spec_policy import SpecPolicy, batch_k
         slots = list(slots)
         k_max = self.k_max
@@ -292,12 +349,14 @@ class Engine:
             for p in pol.values():
                 p.before_step()
             k = batch_k(pol.values())
-            if n_new - min(c for c, _ in cnt) <= 0 or bound + k + 1 > self.max_pos:
+            room = min(self._cap.get(s, self.max_pos) - p for s, (_, p) in zip(slots, cnt))
+            if n_new - min(c for c, _ in cnt) <= 0 or room < k + 1:
                 return len(ks), ks
+            for s in slots:
+                self.set_spec(s, pol[s].k)
             self.spec_step(slots, k, min(bound + k + 1, self.max_pos), use_graph)
             ks.append(k)
             for s in slots:
                 st = self.read(s, cap=1)[2]
                 pol[s].observe(st["accepted"] - prev[s]["accepted"], st["drafts"] - prev[s]["drafts"])
                 prev[s] = st
-

@@ -133,13 +133,14 @@ def attn_scratch_bytes(n_spans, kv_heads, head_dim, max_segs):
 
 
 def attn_verify(q, k_cache, v_cache, block_table, seq_ids, positions, row_start, row_count, gate, out, q_scale, bpr,
-                block_size, q_heads, kv_heads, head_dim, n_spans, max_count, max_ctx, seg_pages, scratch):
+                block_size, q_heads, kv_heads, head_dim, n_spans, max_count, max_ctx, seg_pages, scratch, status=None):
+    """status: optional int32 tensor indexed by sequence id; an understated max_ctx sets bit 4 (STATUS_CTX_BOUND) there."""
     sb = scratch.numel() * scratch.element_size()
     check(load().wein_b200_attn_verify(_ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(block_table), _ptr(seq_ids),
                                        _ptr(positions), _ptr(row_start), _ptr(row_count), _ptr(gate), _ptr(out),
                                        F32(q_scale), U32(bpr), U32(block_size), U32(q_heads), U32(kv_heads),
                                        U32(head_dim), U32(n_spans), U32(max_count), U32(max_ctx), U32(seg_pages),
-                                       _ptr(scratch), U64(sb), _stream()))
+                                       _ptr(scratch), U64(sb), _ptr(status), _stream()))
 
 
 def gemm_scratch_bytes(n_max):
@@ -148,10 +149,20 @@ def gemm_scratch_bytes(n_max):
     return int(fn(U32(n_max)))
 
 
-def gemm_wt(a, w, c, m, n, k, scratch=None):
-    """C[m,n] = A[m,k] W[n,k]^T.  scratch (zero-initialised once, gemm_scratch_bytes) enables split-k."""
+def gemm_wt(a, w, c, m, n, k, scratch=None, tc=False):
+    """C[m,n] = A[m,k] W[n,k]^T.  tc: the tensor-memory kernel whatever m (otherwise m <= 32 runs the mma.sync kernel)."""
+    if tc:
+        check(load().wein_b200_gemm_wt_tc(_ptr(a), _ptr(w), _ptr(c), U32(m), U32(n), U32(k), _stream()))
+        return
     sb = scratch.numel() * scratch.element_size() if scratch is not None else 0
     check(load().wein_b200_gemm_wt(_ptr(a), _ptr(w), _ptr(c), U32(m), U32(n), U32(k), _ptr(scratch), U64(sb), _stream()))
+
+
+def gemm_wait_timeouts():
+    """Barrier waits of the tensor-memory GEMM that ran into their time limit since the library was loaded (0 in a healthy run)."""
+    v = C.c_uint32(0)
+    check(load().wein_b200_gemm_wait_timeouts(C.byref(v)))
+    return v.value
 
 
 DIST_CAP = 64
@@ -175,15 +186,13 @@ def accept_sampled(drafts, n_drafts, p_ids, p_probs, p_n, q_ids, q_probs, q_n, t
                                           _ptr(accept_len), _ptr(out_tokens), _stream()))
 
 
-def gemm_swiglu(a, w_gate_up, out, m, inter, k, scratch=None):
-    """out[m, inter] = silu_mul(a @ gate^T, a @ up^T) with W = [gate; up] ([2*inter, k]); m <= 32."""
+def gemm_swiglu(a, w_gate_up, out, m, inter, k, scratch=None, tc=False):
+    """out[m, inter] = silu_mul(a @ gate^T, a @ up^T) with W = [gate; up] ([2*inter, k])."""
+    if tc:
+        check(load().wein_b200_gemm_swiglu_tc(_ptr(a), _ptr(w_gate_up), _ptr(out), U32(m), U32(inter), U32(k), _stream()))
+        return
     sb = scratch.numel() * scratch.element_size() if scratch is not None else 0
     check(load().wein_b200_gemm_swiglu(_ptr(a), _ptr(w_gate_up), _ptr(out), U32(m), U32(inter), U32(k), _ptr(scratch), U64(sb), _stream()))
-
-
-def gemm_tune(kw=0, ksplit=0, unr=0):
-    """Benchmark hook: force the skinny GEMM's decomposition (0 = automatic)."""
-    load().wein_b200_gemm_tune(U32(kw), U32(ksplit), U32(unr))
 
 
 def gdn_layer_lite(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state_f32, out, row_start, row_count, in_row, out_base,
@@ -221,18 +230,6 @@ def gdn_commit(states, logs, state_f32, row_start, row_count, in_row, out_base, 
         torch.cuda.current_stream().synchronize()   # the pointer tables above are temporaries
 
 
-def gemm_impl(impl=0):
-    """A/B hook: 0 = register-streaming skinny GEMM (default), 1 = TMA-staged skinny GEMM (k % 64 == 0; other shapes keep 0)."""
-    load().wein_b200_gemm_impl(U32(impl))
-
-
-def gemm_stream_timeouts():
-    """Barrier waits of the TMA-staged GEMM that gave up since the library was loaded (0 in a healthy run); synchronises."""
-    v = C.c_uint32(0)
-    check(load().wein_b200_gemm_stream_timeouts(C.byref(v)))
-    return v.value
-
-
 def gdn_layer(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state_f32, out, row_start, row_count, in_row, out_base,
               n_rows, k_heads, v_heads, l2_eps, rms_eps):
     check(load().wein_b200_gdn_layer(_ptr(proj), U32(ld), _ptr(conv_w), _ptr(conv_state), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w),
@@ -252,3 +249,22 @@ def sample_rows(x, rows, slots, temp, top_k, top_p, seed, rng, out, n, s):
     """SampleRowsOp::run: per-row temperature / top-k / top-p sampling with PCG state in `rng` (int64 tensor, advanced in place)."""
     check(load().wein_b200_sample_rows(_ptr(x), _ptr(rows), _ptr(slots), _ptr(temp), _ptr(top_k), _ptr(top_p), _ptr(seed), _ptr(rng),
                                        _ptr(out), U32(n), U32(s), _stream()))
+
+
+def qk_prep(qgkv, ld, qn, kn, cos, sin, rope_pos, kv_pos, seq_ids, block_table, bpr, qh, gate, k_pool, v_pool, tokens, q_heads,
+            kv_heads, head_dim, rot_dim, eps):
+    """Fused q / gate split + q-norm + k-norm + partial rotary + KV page scatter of a full-attention layer."""
+    check(load().wein_b200_qk_prep(_ptr(qgkv), U32(ld), _ptr(qn), _ptr(kn), _ptr(cos), _ptr(sin), _ptr(rope_pos), _ptr(kv_pos),
+                                   _ptr(seq_ids), _ptr(block_table), U32(bpr), _ptr(qh), _ptr(gate), _ptr(k_pool), _ptr(v_pool),
+                                   U32(tokens), U32(q_heads), U32(kv_heads), U32(head_dim), U32(rot_dim), F32(eps), _stream()))
+
+
+def mtp_cat(tok, embed_w, hid, hid_rows, pre_e, pre_h, cat, rows, hidden, eps):
+    """Input of the MTP head: [norm(embed[tok]) | norm(hidden)] per row."""
+    check(load().wein_b200_mtp_cat(_ptr(tok), _ptr(embed_w), _ptr(hid), _ptr(hid_rows), _ptr(pre_e), _ptr(pre_h), _ptr(cat),
+                                   U32(rows), U32(hidden), F32(eps), _stream()))
+
+
+def silu_mul_rows(gu, ld, out, rows, inter):
+    """SwiGLU activation over rows holding gate | up side by side."""
+    check(load().wein_b200_silu_mul_rows(_ptr(gu), U32(ld), _ptr(out), U32(rows), U32(inter), _stream()))

@@ -129,9 +129,11 @@ class RefModel:
         self.pos += 1
         return self._gemm(xn, self.embed, 1, s.vocab, h)
 
-    def mtp_draft(self, hidden, tokens_first, k, start_pos):
+    def mtp_draft(self, hidden, tokens_first, k, start_pos, force=None):
         """k greedy drafts of the MTP head (crates/wein-exec/src/qwen.rs:2805-2848, :4435-4522): a clean chain per
-        round (chain-local KV), absolute rotary positions, hidden chained through the head's own normalised output."""
+        round (chain-local KV), absolute rotary positions, hidden chained through the head's own normalised output.
+        Returns per draft (token, logits, normalised hidden fed to the next draft); force[i], when given, replaces draft
+        i as the token fed to draft i + 1 (teacher forcing with another implementation's drafts)."""
         s = self.s
         h = s.hidden
         m = self.mtp
@@ -150,6 +152,8 @@ class RefModel:
             n2 = orc.rms_norm_zc(x, m["norm"], 1, h, s.rms_eps)
             logits = self._gemm(n2, self.embed, 1, s.vocab, h)
             tok = int(orc.argmax_rows(logits, [0], s.vocab)[0])
-            out.append((tok, logits))
+            out.append((tok, logits, n2))
+            if force is not None:
+                tok = int(force[i])
             hid = n2
         return out
