@@ -346,6 +346,7 @@ def measure_workload(torch, dist, world, rank, weights, shape, wl, args, peak, s
     # the verify step alone: the drafts handed in are the tokens the MTP head would have proposed or any ids -- the time of the
     # verify forward does not depend on them
     drafts = torch.randint(0, shape.vocab, (B, k), dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
     job.timed(min(args.warmup, 3), "verify", drafts)
     ms_verify, _ = job.timed(args.steps, "verify", drafts)
     job.timed(min(args.warmup, 3), "e2e")
@@ -402,12 +403,14 @@ def sweep_c4(torch, job, shape, peak, rounds=10):
             q_probs = torch.zeros(B, k, 64, dtype=torch.float32, device="cuda")
             q_n = torch.zeros(B, k, dtype=torch.int32, device="cuda")
             tv, kv, pv = (torch.full((B,), temp, device="cuda"), torch.full((B,), 64, dtype=torch.int32, device="cuda"), torch.ones(B, device="cuda"))
+            torch.cuda.synchronize()    # these were filled on torch's stream; the engine reads them on its own
             ms_total, tok0 = 0.0, sum(c for c, _ in eng.counts(slots))
             bound = job.wl["prompt"] + P
             for r in range(rounds):
                 bound = min(bound + P, job.max_pos)
                 for j in range(k):
                     nd = torch.full((B,), j, dtype=torch.int32, device="cuda")
+                    torch.cuda.synchronize()
                     eng.spec_verify(slots, k, drafts, bound, n_drafts=nd, q=(q_ids, q_probs, q_n) if temp > 0 else None, dry_run=True)
                     with torch.cuda.stream(eng.stream):
                         noisy = (logits[:, j].float() + sigma * torch.randn(B, V, device="cuda", generator=g)).to(torch.bfloat16).contiguous()
@@ -421,6 +424,7 @@ def sweep_c4(torch, job, shape, peak, rounds=10):
                             q_ids[:, j], q_probs[:, j], q_n[:, j] = ids, pr, nn
                         else:
                             drafts[:, j] = noisy.float().argmax(dim=1).to(torch.int32)
+                torch.cuda.synchronize()
                 e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
                 with torch.cuda.stream(eng.stream):
                     e0.record(eng.stream)

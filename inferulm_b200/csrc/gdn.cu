@@ -301,7 +301,8 @@ template <bool F32, int MINB>
 __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerParams P) {
     PDL_ENTRY();
     constexpr int KD = 128, VD = 128, R = 8, WARPS = 16, MAXT = 8;
-    __shared__ __align__(16) float T[WARPS][R][36];   // row stride 36 words: float4 reads by lanes 0..7 hit disjoint banks
+    __shared__ __align__(16) float T[WARPS][R][36];   // lane partials of kvm, then of o; row stride 36 words: float4 reads of 8 lanes hit disjoint banks
+    __shared__ float d_s[128];                                          // delta of the head's 128 v-rows for the current token
     __shared__ __align__(16) bf16_t qc[MAXT][KD], kc[MAXT][KD], vc[MAXT][VD];
     __shared__ float o_s[MAXT][VD];
     __shared__ float inv_s[MAXT][2], gate_s[MAXT][2], red_s[4][4];
@@ -411,6 +412,21 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
     }
     __syncthreads();
     }   // !P.kq
+    // The recurrence.  Warp w owns v-rows 8w .. 8w+7, lane l the k slice 4l .. 4l+3 of each.  A row's kvm and o are sums of 32
+    // lane partials in ascending lane order (the reference's two-level tree, reference.rs:644-678): a chain of 32 dependent
+    // additions that one thread must make.  The four warps of a group (32 rows) therefore hand their partials to ONE warp,
+    // whose 32 lanes fold one row each: a quarter of the fold instructions of a per-warp fold on 8 lanes (the kernel is bound
+    // by instruction issue at large grids); the other three wait at the group's barrier and leave the issue slots to the
+    // SM's other groups.  The folding duty rotates over the group's warps.
+    const int grp4 = w >> 2, wg = w & 3, grow = grp4 * 32 + lane;   // group, warp within it, the row this lane folds
+    auto group_sync = [&]() {   // barrier of the group's 128 threads (hardware barriers 1..4; 0 is the CTA's)
+        switch (grp4) {
+            case 0: asm volatile("bar.sync 1, 128;" ::: "memory"); break;
+            case 1: asm volatile("bar.sync 2, 128;" ::: "memory"); break;
+            case 2: asm volatile("bar.sync 3, 128;" ::: "memory"); break;
+            default: asm volatile("bar.sync 4, 128;" ::: "memory"); break;
+        }
+    };
     for (uint32_t i = 0; i < cnt; i++) {
         const float decay = gate_s[i][0], beta = gate_s[i][1];
         float kk[4], qq[4];
@@ -419,8 +435,6 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
             kk[0] = k4.x; kk[1] = k4.y; kk[2] = k4.z; kk[3] = k4.w;
             qq[0] = q4.x; qq[1] = q4.y; qq[2] = q4.z; qq[3] = q4.w;
         }
-        float vin = 0.0f;
-        if (lane < R) vin = bf2f(vc[i][row0 + lane]);
 #pragma unroll
         for (int rr = 0; rr < R; rr++) {
             float p = 0.0f;
@@ -431,24 +445,26 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
             }
             T[w][rr][lane] = p;
         }
-        __syncwarp();
-        float delta = 0.0f;
-        if (lane < R) {
-            float tv[32];   // all 32 slice partials first (8 vector loads in flight), then the ordered fold
+        group_sync();
+        if (wg == (int)((2 * i) & 3)) {
+            float tv[32];   // all 32 slice partials of this lane's row first (8 vector loads in flight), then the ordered fold
+            const float *src = &T[grp4 * 4 + (lane >> 3)][lane & 7][0];
 #pragma unroll
             for (int v4 = 0; v4 < 8; v4++) {
-                const float4 t4 = *reinterpret_cast<const float4 *>(&T[w][lane][v4 * 4]);
+                const float4 t4 = *reinterpret_cast<const float4 *>(src + v4 * 4);
                 tv[v4 * 4] = t4.x; tv[v4 * 4 + 1] = t4.y; tv[v4 * 4 + 2] = t4.z; tv[v4 * 4 + 3] = t4.w;
             }
             float kvm = 0.0f;
 #pragma unroll
             for (int sl = 0; sl < 32; sl++) kvm = __fadd_rn(tv[sl], kvm);
-            delta = __fmul_rn(__fsub_rn(vin, kvm), beta);
+            const float delta = __fmul_rn(__fsub_rn(bf2f(vc[i][grow]), kvm), beta);
+            d_s[grow] = delta;
+            if (P.log) P.log[((size_t)(t0 + i) * P.v_heads + h) * GDN_LOG_W + grow] = delta;
         }
-        __syncwarp();
+        group_sync();
 #pragma unroll
         for (int rr = 0; rr < R; rr++) {
-            float d = __shfl_sync(full, delta, rr);
+            const float d = d_s[row0 + rr];
             float p = 0.0f;
 #pragma unroll
             for (int u = 0; u < 4; u++) {
@@ -459,24 +475,24 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
             }
             T[w][rr][lane] = p;
         }
-        __syncwarp();
-        if (lane < R) {
+        group_sync();
+        if (wg == (int)((2 * i + 1) & 3)) {
             float tv[32];
+            const float *src = &T[grp4 * 4 + (lane >> 3)][lane & 7][0];
 #pragma unroll
             for (int v4 = 0; v4 < 8; v4++) {
-                const float4 t4 = *reinterpret_cast<const float4 *>(&T[w][lane][v4 * 4]);
+                const float4 t4 = *reinterpret_cast<const float4 *>(src + v4 * 4);
                 tv[v4 * 4] = t4.x; tv[v4 * 4 + 1] = t4.y; tv[v4 * 4 + 2] = t4.z; tv[v4 * 4 + 3] = t4.w;
             }
             float o = 0.0f;
 #pragma unroll
             for (int sl = 0; sl < 32; sl++) o = __fadd_rn(tv[sl], o);
-            o_s[i][row0 + lane] = rbf(o);   // the core output is stored as bf16 by the reference before the norm reads it
+            o_s[i][grow] = rbf(o);   // the core output is stored as bf16 by the reference before the norm reads it
         }
-        __syncwarp();
+        group_sync();   // the o partials have been consumed: the next token may overwrite them
         if (P.log) {
-            float *lg = P.log + ((size_t)(t0 + i) * P.v_heads + h) * GDN_LOG_W;
-            if (lane < R) lg[row0 + lane] = delta;
             if (w == 0) {
+                float *lg = P.log + ((size_t)(t0 + i) * P.v_heads + h) * GDN_LOG_W;
                 *reinterpret_cast<float4 *>(&lg[128 + lane * 4]) = make_float4(kk[0], kk[1], kk[2], kk[3]);
                 if (lane == 0) lg[256] = decay;
             }
