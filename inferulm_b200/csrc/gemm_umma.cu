@@ -23,8 +23,8 @@
 //  * one thread issues tcgen05.mma (kind::f16, M = 128, K = 16: four per stage and tile); tcgen05.commit frees the
 //    stage for the producer and finally signals the epilogue warps;
 //  * narrow outputs (n = 2560) have only 20 tiles, so k is split over the CTAs of a thread-block cluster (up to 8): each
-//    CTA leaves its f32 partial in its own shared memory and CTA j of the cluster adds column slice j of all partials in
-//    rank order through distributed shared memory.  The split depends on (n, k) only: the order of every sum is fixed by
+//    CTA sends its f32 partial of token-column slice j to CTA j of the cluster through distributed shared memory, and CTA j
+//    adds the partials of its slice in rank order.  The split depends on (n, k) only: the order of every sum is fixed by
 //    the weight shape, never by m, so a token's result does not depend on the batch it is computed in;
 //  * the epilogue reads the accumulators with tcgen05.ld (lane = weight row), rounds to bf16 and writes C, or applies
 //    SwiGLU across the two tiles of a CTA (tile 0 = 128 gate rows, tile 1 = the matching up rows).
@@ -115,20 +115,19 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
                  : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
                    "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                  : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ float ld_remote_f32(uint32_t local_saddr, uint32_t rank) {
+// Store into the shared memory of CTA `rank` of the cluster, at the address that `local_saddr` has in this CTA
+__device__ __forceinline__ void st_remote_f32(uint32_t local_saddr, uint32_t rank, float v) {
     uint32_t ra;
-    float v;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_saddr), "r"(rank));
-    asm volatile("ld.shared::cluster.f32 %0, [%1];" : "=f"(v) : "r"(ra) : "memory");
-    return v;
+    asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_saddr), "r"(rank));
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
 }
 
 // Dynamic shared memory (base rounded up to 1024 bytes): [stages x (MT weight tiles | token tile)] ; the f32 partials of a
@@ -230,77 +229,79 @@ ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ 
 
     // ---- epilogue: warps 2-5; warp w may touch the 32 tensor-memory lanes of quadrant w % 4
     const uint32_t q = warp & 3, row = q * 32 + lane;           // row of the tile this thread owns (warps 2..5)
-    float *part = reinterpret_cast<float *>(ring);               // [MT][npad cols][128 rows] partials (k-split only)
+    const uint32_t tq = tmem_base + ((q * 32u) << 16);
     bool go = false;    // warp-uniform: the tensor-memory loads below are warp-wide instructions
     if (warp >= 2) {
         const bool accum_ok = my_kb == 0 || mbar_wait(smem_u32(&bar_accum), 0, &abort_s);
         go = __all_sync(0xffffffffu, accum_ok && !abort_s) != 0;
         tc_fence_after();
     }
+    // one finished element: round, optionally SwiGLU across the two tiles, store (a warp writes 64 contiguous bytes per token)
+    auto emit = [&](uint32_t tok, float a0, float a1) {
+        if (P.swiglu) {
+            const uint32_t col = r0 + row;
+            if (col < P.half_n) P.C[(size_t)tok * P.ldc + col] = f2bf(__fmul_rn(rbf(silu_ref(rbf(a0))), rbf(a1)));
+        } else {
+            if (r0 + row < P.n) P.C[(size_t)tok * P.ldc + r0 + row] = f2bf(a0);
+            if (MT == 2 && r1 + row < P.n) P.C[(size_t)tok * P.ldc + r1 + row] = f2bf(a1);
+        }
+    };
     if (P.ksplit == 1) {
         if (go) {
             for (uint32_t c0 = 0; c0 < P.m; c0 += 16) {
                 uint32_t v0[16], v1[16];
-                tmem_ld16(tmem_base + ((q * 32u) << 16) + c0, v0);
-                if (MT == 2) tmem_ld16(tmem_base + ((q * 32u) << 16) + P.npad + c0, v1);
+                tmem_ld16(tq + c0, v0);
+                if (MT == 2) tmem_ld16(tq + P.npad + c0, v1);
+                tmem_ld_wait();
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const uint32_t tok = c0 + j;
-                    if (tok >= P.m) break;
-                    if (P.swiglu) {
-                        const uint32_t col = r0 + row;
-                        if (col < P.half_n) {
-                            const float gv = rbf(__uint_as_float(v0[j])), uv = rbf(__uint_as_float(MT == 2 ? v1[j] : 0u));
-                            P.C[(size_t)tok * P.ldc + col] = f2bf(__fmul_rn(rbf(silu_ref(gv)), uv));
-                        }
-                    } else {
-                        if (r0 + row < P.n) P.C[(size_t)tok * P.ldc + r0 + row] = f2bf(__uint_as_float(v0[j]));
-                        if (MT == 2 && r1 + row < P.n) P.C[(size_t)tok * P.ldc + r1 + row] = f2bf(__uint_as_float(v1[j]));
-                    }
-                }
+                for (int j = 0; j < 16; j++)
+                    if (c0 + j < P.m) emit(c0 + j, __uint_as_float(v0[j]), MT == 2 ? __uint_as_float(v1[j]) : 0.0f);
             }
         }
         tc_fence_before();
         __syncthreads();
     } else {
-        // partials to this CTA's shared memory (the ring is idle: every copy has landed and every MMA has read it)
+        // k split over the cluster: token column c belongs to CTA c / cs.  Once every CTA of the cluster has left its main
+        // loop (its ring is idle: every copy has landed and every MMA has read it), each CTA sends the columns of its f32
+        // partial straight from tensor memory into the owner's ring, [source rank][tile][column of the slice][128 rows];
+        // after a second barrier the owner adds the partials of a column in rank order from its own shared memory.
+        const uint32_t cs = (P.m + P.ksplit - 1) / P.ksplit;
+        float *recv = reinterpret_cast<float *>(ring);
+        tc_fence_before();
+        cluster_sync_all();
         if (go) {
             for (uint32_t c0 = 0; c0 < P.m; c0 += 16) {
-#pragma unroll
-                for (int t = 0; t < MT; t++) {
-                    uint32_t v[16];
-                    if (my_kb) tmem_ld16(tmem_base + ((q * 32u) << 16) + t * P.npad + c0, v);
-#pragma unroll
-                    for (int j = 0; j < 16; j++)
-                        if (c0 + j < P.m) part[((size_t)t * P.npad + c0 + j) * 128 + row] = my_kb ? __uint_as_float(v[j]) : 0.0f;
+                uint32_t v0[16], v1[16];
+                if (my_kb) {
+                    tmem_ld16(tq + c0, v0);
+                    if (MT == 2) tmem_ld16(tq + P.npad + c0, v1);
+                    tmem_ld_wait();
                 }
+#pragma unroll
+                for (int j = 0; j < 16; j++) {
+                    const uint32_t c = c0 + j;
+                    if (c >= P.m) break;
+                    const uint32_t owner = c / cs, slot = c - owner * cs;
+                    const uint32_t a0 = smem_u32(&recv[(((size_t)rank * MT + 0) * cs + slot) * 128 + row]);
+                    st_remote_f32(a0, owner, my_kb ? __uint_as_float(v0[j]) : 0.0f);
+                    if (MT == 2) st_remote_f32(a0 + cs * 128 * 4, owner, my_kb ? __uint_as_float(v1[j]) : 0.0f);
+                }
+            }
+        }
+        cluster_sync_all();   // release / acquire: the partials sent above are visible to their owners
+        const uint32_t c_lo = min(P.m, rank * cs), c_hi = min(P.m, c_lo + cs);
+        if (warp >= 2 && !abort_s) {   // (a peer that gave up sends nothing: the result is flagged by the timeout counter, not trusted)
+            for (uint32_t c = c_lo; c < c_hi; c++) {
+                float acc0 = 0.0f, acc1 = 0.0f;
+                for (uint32_t rk = 0; rk < P.ksplit; rk++) {
+                    acc0 += recv[(((size_t)rk * MT + 0) * cs + (c - c_lo)) * 128 + row];
+                    if (MT == 2) acc1 += recv[(((size_t)rk * MT + 1) * cs + (c - c_lo)) * 128 + row];
+                }
+                emit(c, acc0, acc1);
             }
         }
         tc_fence_before();
-        cluster_sync_all();
-        // CTA `rank` owns the column slice [rank * cs, ...): sums the partials of the cluster's CTAs in rank order
-        const uint32_t cs = (P.m + P.ksplit - 1) / P.ksplit;
-        const uint32_t c_lo = min(P.m, rank * cs), c_hi = min(P.m, c_lo + cs);
-        if (warp >= 2 && !abort_s) {   // (a peer that gave up leaves zeros or stale partials: the result is flagged, not trusted)
-            for (uint32_t c = c_lo; c < c_hi; c++) {
-                float acc[MT];
-#pragma unroll
-                for (int t = 0; t < MT; t++) {
-                    const uint32_t a = smem_u32(&part[((size_t)t * P.npad + c) * 128 + row]);
-                    float s = 0.0f;
-                    for (uint32_t rk = 0; rk < P.ksplit; rk++) s += ld_remote_f32(a, rk);
-                    acc[t] = s;
-                }
-                if (P.swiglu) {
-                    const uint32_t col = r0 + row;
-                    if (col < P.half_n) P.C[(size_t)c * P.ldc + col] = f2bf(__fmul_rn(rbf(silu_ref(rbf(acc[0]))), rbf(acc[MT - 1])));
-                } else {
-                    if (r0 + row < P.n) P.C[(size_t)c * P.ldc + r0 + row] = f2bf(acc[0]);
-                    if (MT == 2 && r1 + row < P.n) P.C[(size_t)c * P.ldc + r1 + row] = f2bf(acc[MT - 1]);
-                }
-            }
-        }
-        cluster_sync_all();   // nobody leaves while a peer may still read its partials
+        __syncthreads();
     }
     if (warp == 1) {
         tc_fence_after();
@@ -414,7 +415,8 @@ int32_t wb_ugemm(const void *a, const void *w, void *c, uint32_t m, uint32_t n, 
         auto stage_bytes = [&](uint32_t mt) { return (size_t)mt * UG_WTILE + (size_t)p.npad * 128; };
         auto fits = [&](uint32_t mt, uint32_t ks) {
             const size_t ring = (UG_SMEM_MAX - 1024) / stage_bytes(mt) * stage_bytes(mt);
-            return (UG_SMEM_MAX - 1024) / stage_bytes(mt) >= 3 && (ks == 1 || (size_t)mt * p.npad * 128 * 4 <= ring) && mt * p.npad <= 512;
+            const size_t cs = (mc + ks - 1) / ks;
+            return (UG_SMEM_MAX - 1024) / stage_bytes(mt) >= 3 && (ks == 1 || (size_t)ks * mt * cs * 128 * 4 <= ring) && mt * p.npad <= 512;
         };
         if (!fits(pl.mt, pl.ksplit)) {
             if (swiglu || !fits(1, pl.ksplit)) { wb_set_error("gemm: m = %u rows do not fit the tensor-core kernel's shared memory", mc); return WB_ERR_SHAPE; }

@@ -173,7 +173,9 @@ def test_mtp_drafts_match_cpu_mirror(small_weights):
     checked = 0
     for k in (1, 2, 3):
         out = torch.zeros(k, dtype=torch.int32, device="cuda")
+        torch.cuda.synchronize()           # `out` was filled on torch's stream; the engine writes it on its own
         eng.draft([0], k, out=out, use_graph=(k == 2))
+        torch.cuda.synchronize()
         drafts = host(out, np.uint32)
         assert np.array_equal(drafts, host(eng.buffer("drafts", torch.int32), np.uint32)[:k])
         want = ref.mtp_draft(hid, pending, k, len(prompt), force=[int(d) for d in drafts])   # device stash, device tokens
