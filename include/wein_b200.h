@@ -162,7 +162,8 @@ int32_t wein_b200_attn_verify(const void *q, const void *k_cache, const void *v_
 /* GemmOp::run_wt (ops/mod.rs:3378-3449): C[m,n] = A[m,k] W[n,k]^T, bf16, f32 accumulate; k a multiple of 32, operands 16-byte
  * aligned.  Two hand-written weight-streaming kernels, no library call (the reference sends m > 1 to cuBLASLt,
  * cuda/cublaslt.rs:249-257): m <= 32 runs the register-streaming mma.sync kernel, larger m the tensor-memory kernel
- * (tcgen05.mma, weights as the M operand, tensor-map bulk copies, k split over a thread-block cluster for narrow n).  In both
+ * (tcgen05.mma with the tokens as the M operand and 128 / 256 weight rows as N, tensor-map bulk copies, k split over a
+ * thread-block cluster for narrow n).  In both
  * the result of a row does not depend on the other rows of the call; the two kernels do not agree with each other bit for bit,
  * so forwards that must agree across row counts use the _tc entries (the tensor-memory kernel at every m) throughout.
  * scratch is optional and may be null (reserved for a split-k mode of the m <= 32 kernel). */
@@ -177,6 +178,10 @@ int32_t wein_b200_gemm_swiglu(const void *a, const void *w_gate_up, void *out, u
                               void *scratch, uint64_t scratch_bytes, void *stream);
 int32_t wein_b200_gemm_swiglu_tc(const void *a, const void *w_gate_up, void *out, uint32_t m, uint32_t inter, uint32_t k,
                                  void *stream);
+/* How the tensor-memory kernel runs a product of m rows with an [n, k] weight matrix (swiglu != 0: [2n, k] = gate | up) on the
+ * current device: out[5] = CTAs, k split (thread-block cluster size), pipeline stages, shared-memory bytes per CTA, weight rows
+ * per tile.  The k split, which fixes the summation order, depends on (n, k) and the device only. */
+int32_t wein_b200_gemm_plan(uint32_t m, uint32_t n, uint32_t k, uint32_t swiglu, uint32_t *out);
 /* Barrier waits of the tensor-memory kernel that ran into their time limit since the library was loaded (0 in a healthy
  * run; a non-zero count means a result was abandoned, not that a kernel hung).  Synchronises the device. */
 int32_t wein_b200_gemm_wait_timeouts(uint32_t *out);

@@ -6,54 +6,77 @@
 // Reference contract: GemmOp::run_wt (crates/wein-kernel/src/ops/mod.rs:3378-3449), which hands these shapes to cuBLASLt
 // (crates/wein-kernel/src/cuda/cublaslt.rs:249-257) and accepts |got - ref| <= max(2^-7 |ref|, 2^-11) against an f64 product
 // (crates/wein-kernel/tests/gemm.rs:11).  The reference's own hand-written attempt (kernels/src/lib.rs:8655) lost on
-// activation re-reads (ops/mod.rs:3392-3397); the shape of this kernel follows from that traffic algebra.
+// activation re-reads (ops/mod.rs:3392-3397).
 //
 // The product is bound by streaming W from HBM once (at most 256 flop per weight byte, the ridge is ~270).  Design:
-//  * the WEIGHTS are the M operand of the MMA: a CTA owns MT (1 or 2) tiles of 128 weight rows and a slice of k; the
-//    tokens are the N operand (m rounded up to 16).  D[128 x N] f32 lives in tensor memory (MT x N columns), so no
-//    register holds an accumulator during the main loop;
-//  * a stage = 64 k of the MT weight tiles (16 KB each) + 64 k of all tokens (N x 128 B), brought in by tensor-map bulk
-//    copies (cp.async.bulk.tensor, 128-byte swizzle, no multicast) that complete on an mbarrier; 3-7 stages per CTA keep
-//    100-200 KB in flight per SM.  With MT = 2 the token stage is read once for 256 weight rows, which halves the
-//    L2 -> SM activation traffic that decides the rate at m = 128 (it equals the weight traffic with MT = 1);
+//  * the TOKENS are the M operand of the MMA (128 rows; only the rows up to m, rounded up to 8, are copied and kept in shared
+//    memory -- a token's result is row-local, so what the MMA reads past them only lands in accumulator rows nobody reads;
+//    a second block of 128 for m > 128) and a tile of NT = 128 or 256 WEIGHT rows is the N operand: D[128 tokens x NT] f32 lives in tensor memory.
+//    Measured on B200: the thread that issues tcgen05.mma spends ~115 cycles per instruction whatever N is (16 or 128),
+//    plus ~100 per stage on barriers, so what bounds an SM's streaming rate is weight bytes per instruction: 8 KB at
+//    N = 256 against 4 KB with the weights as the M operand (which capped an SM at ~40 GB/s, below its share of HBM);
+//  * a stage = 64 k of the weight tile (NT x 128 B) + 64 k of the token block(s) (16 KB each), brought in by tensor-map
+//    bulk copies (cp.async.bulk.tensor, 128-byte swizzle, no multicast) that complete on an mbarrier.  A grid of at least
+//    two CTAs per SM takes half an SM per CTA when three stages fit in that, so that one CTA streams while the other is in
+//    its prologue or epilogue (measured: with one 225 KB CTA per SM an SM idled for a third of each CTA's life);
 //  * weights are never written inside a round, so the producer thread issues the weight copies of the first stages
 //    BEFORE the kernel waits for its predecessor (programmatic dependent launch); token copies, the tensor-memory
 //    allocation and everything else come after the wait.  Allocating tensor memory before the wait could deadlock: a
 //    CTA that holds columns while it waits for the predecessor grid can starve a predecessor CTA of columns;
-//  * one thread issues tcgen05.mma (kind::f16, M = 128, K = 16: four per stage and tile); tcgen05.commit frees the
+//  * one thread issues the MMAs (kind::f16, M = 128, K = 16: four per stage and token block); tcgen05.commit frees the
 //    stage for the producer and finally signals the epilogue warps;
-//  * narrow outputs (n = 2560) have only 20 tiles, so k is split over the CTAs of a thread-block cluster (up to 8): each
-//    CTA sends its f32 partial of token-column slice j to CTA j of the cluster through distributed shared memory, and CTA j
-//    adds the partials of its slice in rank order.  The split depends on (n, k) only: the order of every sum is fixed by
-//    the weight shape, never by m, so a token's result does not depend on the batch it is computed in;
-//  * the epilogue reads the accumulators with tcgen05.ld (lane = weight row), rounds to bf16 and writes C, or applies
-//    SwiGLU across the two tiles of a CTA (tile 0 = 128 gate rows, tile 1 = the matching up rows).
+//  * the epilogue is row-local and runs on all eight warps: thread = token (tensor-memory lane), columns = consecutive weight
+//    rows, so a thread reads 16 columns with tcgen05.ld, rounds them to bf16 (or applies SwiGLU to a gate column and its up
+//    column, which sit in the same lane; the activation comes from a table of all 65,536 bf16 inputs) and writes 32
+//    contiguous bytes of its C row: no transposition, no shared memory;
+//  * outputs with few tiles (n = 2560) split k over the CTAs of a thread-block cluster (up to 8, as many as the device
+//    keeps resident at once): each CTA sends column slice j of its f32 partial to CTA j of the cluster through
+//    distributed shared memory (16-byte remote stores), and CTA j adds the partials of its slice in rank order.  The split
+//    depends on (n, k) and the device only: the order of every sum is fixed by the weight shape, never by m, so a token's
+//    result does not depend on the batch it is computed in.
 // Every mbarrier wait is bounded by a clock; a wait that gives up raises a CTA-wide abort flag, is counted in a device
 // counter, the CTA still joins its cluster barriers, frees its tensor memory and leaves after its copies have landed.
 #include <cuda.h>
 #include "common.cuh"
 #include "internal.h"
+#include <math.h>
 #include <mutex>
 
 namespace {
 
 constexpr int UG_BK = 64;                      // k elements per stage (one 128-byte swizzle row)
-constexpr int UG_WTILE = 128 * UG_BK * 2;      // bytes of one weight tile per stage
-constexpr int UG_THREADS = 192;                // warp 0 producer, warp 1 MMA + tensor-memory owner, warps 2-5 epilogue
+constexpr int UG_XTILE = 128 * UG_BK * 2;      // bytes of one block of 128 token rows per stage
+constexpr int UG_NS = 2;                       // independent pipelines (producer + MMA issuer + accumulator) per CTA
+constexpr int UG_THREADS = (2 * UG_NS + 4) * 32;   // per stream a producer warp and an MMA warp, then four epilogue warps
 constexpr long long UG_WAIT_CYCLES = 2000000000ll;   // ~1 s
-constexpr int UG_SMEM_MAX = 225 * 1024;
+constexpr int UG_SMEM_MAX = 225 * 1024;        // one CTA per SM
+constexpr int UG_SMEM_PAIR = 110 * 1024;       // two CTAs per SM
+constexpr int UG_MAX_STAGES = 6;               // per stream
 
 __device__ unsigned int g_ug_timeouts;
+
+// bf16(silu(x)) for every bf16 x, filled once per device by the exact expression of the SwiGLU operator (silu_ref on the value,
+// rounded to bf16: kernels/src/lib.rs:576-584 of the reference).  The SwiGLU epilogue looks the activation up instead of
+// evaluating ~80 instructions per element; the table IS the function on its 65,536 possible inputs, so nothing changes.
+__device__ bf16_t g_silu_lut[65536];
+__global__ void silu_lut_kernel() {
+    const uint32_t i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < 65536u) g_silu_lut[i] = f2bf(silu_ref(bf2f((bf16_t)i)));
+}
 
 struct UgParams {
     bf16_t *C;
     uint32_t m, n, k, ldc;          // n = weight rows of the product (2 * inter with swiglu)
-    uint32_t npad;                  // m rounded up to 16: N of the MMA, rows of the token box
+    uint32_t nt;                    // weight rows per tile: N of the MMA (128 or 256; swiglu: nt/2 gate rows + nt/2 up rows)
+    uint32_t passes;                // token blocks of 128 rows: 1 (m <= 128) or 2
+    uint32_t x_bytes;               // bytes of the token rows a stage holds: passes == 2: 2 x 16 KB, else m rounded up to 8 rows x 128 B
     uint32_t nkb;                   // k blocks of 64 in the whole product
-    uint32_t ksplit;                // cluster size: CTAs that share the k range of a tile group
-    uint32_t stages;                // ring depth
-    uint32_t swiglu, half_n;        // swiglu: tile 0 = gate rows r0.., tile 1 = up rows (half_n + r0..); output [m, half_n]
-    uint32_t tmem_cols;             // power of two >= MT * npad
+    uint32_t ksplit;                // cluster size: CTAs that share the k range of a tile
+    uint32_t cw;                    // k split: output columns of a tile owned by each CTA of the cluster (a multiple of 8)
+    uint32_t stages;                // ring depth of each stream
+    uint32_t swiglu, half_n;        // swiglu: output [m, half_n], tile columns [0, nt/2) gate, [nt/2, nt) the matching up rows
+    uint32_t tmem_cols;             // power of two >= UG_NS * passes * nt
+    uint32_t vec_ok;                // C rows may be written in 16-byte pieces (C 16-byte aligned, ldc a multiple of 8)
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -98,7 +121,7 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t saddr) {
     d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
     return d;
 }
-// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = npad.
+// Instruction descriptor: bf16 x bf16 -> f32, both operands K-major, M = 128, N = n.
 __device__ __forceinline__ uint32_t umma_idesc(uint32_t n) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((n >> 3) << 17) | ((128u >> 4) << 24);
 }
@@ -123,60 +146,80 @@ __device__ __forceinline__ void cluster_sync_all() {
     asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 __device__ __forceinline__ uint32_t cluster_rank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
-// Store into the shared memory of CTA `rank` of the cluster, at the address that `local_saddr` has in this CTA
-__device__ __forceinline__ void st_remote_f32(uint32_t local_saddr, uint32_t rank, float v) {
+// 16-byte store into the shared memory of CTA `rank` of the cluster, at the address that `local_saddr` has in this CTA
+__device__ __forceinline__ void st_remote_f32x4(uint32_t local_saddr, uint32_t rank, float a, float b, float c, float d) {
     uint32_t ra;
     asm("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(ra) : "r"(local_saddr), "r"(rank));
-    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(ra), "f"(v) : "memory");
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(ra), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
 }
+__device__ __forceinline__ uint32_t pack2(float lo, float hi) { return (uint32_t)f2bf(lo) | ((uint32_t)f2bf(hi) << 16); }
 
-// Dynamic shared memory (base rounded up to 1024 bytes): [stages x (MT weight tiles | token tile)] ; the f32 partials of a
-// k-split CTA alias the ring once the main loop is over.  Barriers, the abort flag and the tensor-memory address are static.
-template <int MT>
-__global__ void __launch_bounds__(UG_THREADS, 1)
+// Dynamic shared memory (base rounded up to 1024 bytes): [UG_NS streams x stages x (weight tile | token block(s))]; once the main
+// loop is over the idle ring holds, in a k-split CTA, the f32 partials it owns: [source rank][token][cw (x2 with swiglu)].
+// Barriers, the abort flag and the tensor-memory address are static.
+//
+// Warps: 0 / 2 = producers and 1 / 3 = MMA issuers of streams 0 / 1, 4-7 = epilogue.  Measured on B200: the thread that issues
+// tcgen05.mma needs ~800 cycles per k block (barrier wait ~200, four MMAs and the commit ~600) whatever the tile size and
+// wherever the data comes from, which caps ONE issuing thread at ~40 GB/s of weights for a 128-row tile -- below an SM's share
+// of HBM.  So a CTA runs UG_NS = 2 independent pipelines: stream j takes k blocks j, j + 2, ... through its own stages and
+// barriers into its own accumulator; the epilogue adds accumulator 1 to accumulator 0.  Which block goes to which stream is
+// fixed by the block index, so the order of every sum is still fixed by (n, k) alone.
+__global__ void __launch_bounds__(UG_THREADS, 2)
 ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
              const __grid_constant__ CUtensorMap tm_x, const UgParams P) {
     pdl_trigger();
     extern __shared__ unsigned char ug_smem_raw[];
-    __shared__ uint64_t bar_full[8], bar_empty[8], bar_accum;
+    __shared__ uint64_t bar_full[UG_NS][UG_MAX_STAGES], bar_empty[UG_NS][UG_MAX_STAGES], bar_accum[UG_NS];
     __shared__ uint32_t tmem_base_s;
     __shared__ volatile uint32_t abort_s;
     unsigned char *ring = ug_smem_raw + ((1024u - (smem_u32(ug_smem_raw) & 1023u)) & 1023u);
-    const uint32_t ring0 = smem_u32(ring);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const uint32_t S = P.stages, x_bytes = P.npad * 128u, stage_bytes = MT * UG_WTILE + x_bytes;
+    const uint32_t S = P.stages, NT = P.nt, w_bytes = NT * 128u, stage_bytes = w_bytes + P.x_bytes;   // S: stages per stream
     const uint32_t rank = P.ksplit > 1 ? cluster_rank() : 0u;
-    const uint32_t group = blockIdx.x / P.ksplit;            // which tile group of MT x 128 weight rows
-    // weight rows of the two tiles: consecutive 128-row tiles, or gate rows and the matching up rows
-    const uint32_t r0 = P.swiglu ? group * 128u : group * (MT * 128u);
-    const uint32_t r1 = P.swiglu ? r0 : r0 + 128u;            // swiglu: same coordinate in the second map (the up half)
+    const uint32_t tile = blockIdx.x / P.ksplit;
+    const uint32_t ocols = P.swiglu ? NT / 2 : NT;          // output columns of a tile
+    const uint32_t r0 = tile * ocols;                        // first weight row of the tile (swiglu: in both halves), = first output column
     // k blocks of this CTA: nkb split into ksplit contiguous parts, the first `rem` parts one block longer
     const uint32_t per = P.nkb / P.ksplit, rem = P.nkb % P.ksplit;
     const uint32_t kb_lo = rank * per + min(rank, rem), my_kb = per + (rank < rem ? 1u : 0u);
+    const uint32_t acc_cols = P.passes * NT;                 // tensor-memory columns of one stream's accumulator(s)
 
     if (tid == 0) {
-        for (uint32_t s = 0; s < S; s++) { mbar_init(smem_u32(&bar_full[s]), 1); mbar_init(smem_u32(&bar_empty[s]), 1); }
-        mbar_init(smem_u32(&bar_accum), 1);
+        for (uint32_t j = 0; j < UG_NS; j++) {
+            for (uint32_t s = 0; s < S; s++) { mbar_init(smem_u32(&bar_full[j][s]), 1); mbar_init(smem_u32(&bar_empty[j][s]), 1); }
+            mbar_init(smem_u32(&bar_accum[j]), 1);
+        }
         abort_s = 0;
         tmem_base_s = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
 
-    const uint32_t pre = min(S, my_kb);
-    if (warp == 0 && lane == 0) {
+    auto load_w = [&](uint32_t dst, uint32_t kb, uint32_t fb) {
+        tma_2d(dst, &tm_w0, kb * UG_BK, r0, fb);
+        if (P.swiglu) tma_2d(dst + (NT / 2) * 128, &tm_w1, kb * UG_BK, r0, fb);
+    };
+    auto load_x = [&](uint32_t dst, uint32_t kb, uint32_t fb) {
+        tma_2d(dst, &tm_x, kb * UG_BK, 0, fb);
+        if (P.passes == 2) tma_2d(dst + UG_XTILE, &tm_x, kb * UG_BK, 128, fb);
+    };
+    // role of this warp: stream j = warp / 2 for warps 0..3 (even: producer, odd: MMA issuer)
+    const uint32_t strm = (uint32_t)warp >> 1;
+    const bool is_prod = warp < 2 * UG_NS && (warp & 1) == 0, is_mma = warp < 2 * UG_NS && (warp & 1) == 1;
+    const uint32_t sring = smem_u32(ring) + strm * S * stage_bytes;                      // this stream's stages
+    const uint32_t my_n = my_kb > strm ? (my_kb - strm + UG_NS - 1) / UG_NS : 0u;        // k blocks of this stream: kb_lo + strm + UG_NS * i
+    const uint32_t pre = min(S, my_n);
+    if (is_prod && lane == 0) {
         // ---- producer, part 1: weight copies of the first stages while the predecessor kernel is still running
         for (uint32_t i = 0; i < pre; i++) {
-            const uint32_t fb = smem_u32(&bar_full[i]), dst = ring0 + i * stage_bytes;
+            const uint32_t fb = smem_u32(&bar_full[strm][i]);
             mbar_expect_tx(fb, stage_bytes);
-            tma_2d(dst, &tm_w0, (kb_lo + i) * UG_BK, r0, fb);
-            if (MT == 2) tma_2d(dst + UG_WTILE, &tm_w1, (kb_lo + i) * UG_BK, r1, fb);
+            load_w(sring + i * stage_bytes, kb_lo + strm + UG_NS * i, fb);
         }
     }
     pdl_wait();   // the tokens are the predecessor's output; tensor memory may only be claimed once that grid is gone
-    if (warp == 0 && lane == 0) {
-        for (uint32_t i = 0; i < pre; i++)
-            tma_2d(ring0 + i * stage_bytes + MT * UG_WTILE, &tm_x, (kb_lo + i) * UG_BK, 0, smem_u32(&bar_full[i]));
+    if (is_prod && lane == 0) {
+        for (uint32_t i = 0; i < pre; i++) load_x(sring + i * stage_bytes + w_bytes, kb_lo + strm + UG_NS * i, smem_u32(&bar_full[strm][i]));
     }
     __syncwarp();
     if (warp == 1) {
@@ -188,121 +231,162 @@ ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ 
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
 
-    if (warp == 0) {
+    if (is_prod) {
         // ---- producer, part 2: the remaining stages, each as soon as the MMAs that read its slot have completed
         if (lane == 0) {
-            for (uint32_t i = pre; i < my_kb; i++) {
+            for (uint32_t i = pre; i < my_n; i++) {
                 const uint32_t s = i % S;
-                if (!mbar_wait(smem_u32(&bar_empty[s]), ((i / S) - 1) & 1, &abort_s)) break;
-                const uint32_t fb = smem_u32(&bar_full[s]), dst = ring0 + s * stage_bytes;
+                if (!mbar_wait(smem_u32(&bar_empty[strm][s]), ((i / S) - 1) & 1, &abort_s)) break;
+                const uint32_t fb = smem_u32(&bar_full[strm][s]), dst = sring + s * stage_bytes;
                 mbar_expect_tx(fb, stage_bytes);
-                tma_2d(dst, &tm_w0, (kb_lo + i) * UG_BK, r0, fb);
-                if (MT == 2) tma_2d(dst + UG_WTILE, &tm_w1, (kb_lo + i) * UG_BK, r1, fb);
-                tma_2d(dst + MT * UG_WTILE, &tm_x, (kb_lo + i) * UG_BK, 0, fb);
+                load_w(dst, kb_lo + strm + UG_NS * i, fb);
+                load_x(dst + w_bytes, kb_lo + strm + UG_NS * i, fb);
             }
         }
         __syncwarp();
-    } else if (warp == 1) {
-        // ---- MMA issue: one thread; D (+)= W_tile[128 x 16] * X[npad x 16]^T, four k-steps per stage and tile
+    } else if (is_mma) {
+        // ---- MMA issue: one thread per stream; D_j[128 tokens x NT] (+)= X[128 x 16] * W_tile[NT x 16]^T, four k-steps per stage
         if (lane == 0) {
-            const uint32_t idesc = umma_idesc(P.npad);
-            bool ok = true;
-            for (uint32_t i = 0; i < my_kb && ok; i++) {
+            const uint32_t idesc = umma_idesc(NT), td = tmem_base + strm * acc_cols;
+            for (uint32_t i = 0; i < my_n; i++) {
                 const uint32_t s = i % S;
-                ok = mbar_wait(smem_u32(&bar_full[s]), (i / S) & 1, &abort_s);
-                if (!ok) break;
+                if (!mbar_wait(smem_u32(&bar_full[strm][s]), (i / S) & 1, &abort_s)) break;
                 tc_fence_after();
-                const uint32_t base = ring0 + s * stage_bytes;
-                const uint64_t db = umma_desc(base + MT * UG_WTILE);
+                const uint32_t base = sring + s * stage_bytes;
+                const uint64_t dw = umma_desc(base), dx = umma_desc(base + w_bytes);
 #pragma unroll
                 for (int kk = 0; kk < UG_BK / 16; kk++) {
-#pragma unroll
-                    for (int t = 0; t < MT; t++)
-                        umma_bf16(tmem_base + t * P.npad, umma_desc(base + t * UG_WTILE) + 2 * kk, db + 2 * kk, idesc, (i | kk) != 0 ? 1u : 0u);
+                    umma_bf16(td, dx + 2 * kk, dw + 2 * kk, idesc, (i | kk) != 0 ? 1u : 0u);
+                    if (P.passes == 2) umma_bf16(td + NT, dx + (UG_XTILE >> 4) + 2 * kk, dw + 2 * kk, idesc, (i | kk) != 0 ? 1u : 0u);
                 }
-                umma_commit(smem_u32(&bar_empty[s]));   // the slot is free once these MMAs have read it
+                umma_commit(smem_u32(&bar_empty[strm][s]));   // the slot is free once these MMAs have read it
             }
-            umma_commit(smem_u32(&bar_accum));           // all MMAs of this CTA complete: the accumulators are final
+            umma_commit(smem_u32(&bar_accum[strm]));           // all MMAs of this stream complete: its accumulators are final
         }
         __syncwarp();
     }
 
-    // ---- epilogue: warps 2-5; warp w may touch the 32 tensor-memory lanes of quadrant w % 4
-    const uint32_t q = warp & 3, row = q * 32 + lane;           // row of the tile this thread owns (warps 2..5)
+    // ---- epilogue: all eight warps (the producers and MMA issuers are done); warp w may touch the 32 tensor-memory lanes
+    // (= tokens) of quadrant w % 4, so warps w and w + 4 share a quadrant and take one half of the tile's output columns each
+    const uint32_t q = warp & 3, half = (uint32_t)warp >> 2;
     const uint32_t tq = tmem_base + ((q * 32u) << 16);
+    const uint32_t n_acc = my_kb < UG_NS ? my_kb : UG_NS;     // streams that got at least one k block
     bool go = false;    // warp-uniform: the tensor-memory loads below are warp-wide instructions
-    if (warp >= 2) {
-        const bool accum_ok = my_kb == 0 || mbar_wait(smem_u32(&bar_accum), 0, &abort_s);
+    {
+        bool accum_ok = true;
+        for (uint32_t j = 0; j < n_acc; j++) accum_ok = accum_ok && mbar_wait(smem_u32(&bar_accum[j]), 0, &abort_s);
         go = __all_sync(0xffffffffu, accum_ok && !abort_s) != 0;
         tc_fence_after();
     }
-    // one finished element: round, optionally SwiGLU across the two tiles, store (a warp writes 64 contiguous bytes per token)
-    auto emit = [&](uint32_t tok, float a0, float a1) {
-        if (P.swiglu) {
-            const uint32_t col = r0 + row;
-            if (col < P.half_n) P.C[(size_t)tok * P.ldc + col] = f2bf(__fmul_rn(rbf(silu_ref(rbf(a0))), rbf(a1)));
-        } else {
-            if (r0 + row < P.n) P.C[(size_t)tok * P.ldc + r0 + row] = f2bf(a0);
-            if (MT == 2 && r1 + row < P.n) P.C[(size_t)tok * P.ldc + r1 + row] = f2bf(a1);
+    // 16 accumulator columns of this thread's token from each stream that ran: issue, then (after tmem_ld_wait) add stream 1 to
+    // stream 0 (which k block went to which stream is fixed by the block index: a fixed order)
+    auto acc_issue = [&](uint32_t col, uint32_t (&v)[16], uint32_t (&w)[16]) {
+        if (n_acc >= 1) tmem_ld16(tq + col, v);
+        if (n_acc == 2) tmem_ld16(tq + acc_cols + col, w);
+    };
+    auto acc_sum = [&](uint32_t (&v)[16], const uint32_t (&w)[16]) {
+#pragma unroll
+        for (int e = 0; e < 16; e++) {
+            const float a = n_acc >= 1 ? __uint_as_float(v[e]) : 0.0f;
+            v[e] = __float_as_uint(n_acc == 2 ? a + __uint_as_float(w[e]) : a);
         }
+    };
+    const uint32_t n_out = P.swiglu ? P.half_n : P.n;
+    // eight finished output values of one token, columns col0 .. col0+7 of the tile
+    auto store8 = [&](uint32_t tok, uint32_t col0, const float (&o)[8]) {
+        const uint32_t gc = r0 + col0;
+        if (gc >= n_out) return;
+        bf16_t *dst = P.C + (size_t)tok * P.ldc + gc;
+        if (P.vec_ok && gc + 8 <= n_out) *reinterpret_cast<uint4 *>(dst) = make_uint4(pack2(o[0], o[1]), pack2(o[2], o[3]), pack2(o[4], o[5]), pack2(o[6], o[7]));
+        else for (uint32_t e = 0; e < 8 && gc + e < n_out; e++) dst[e] = f2bf(o[e]);
     };
     if (P.ksplit == 1) {
         if (go) {
-            for (uint32_t c0 = 0; c0 < P.m; c0 += 16) {
-                uint32_t v0[16], v1[16];
-                tmem_ld16(tq + c0, v0);
-                if (MT == 2) tmem_ld16(tq + P.npad + c0, v1);
-                tmem_ld_wait();
+            const uint32_t c_lo = half * (ocols / 2), c_hi = c_lo + ocols / 2;   // ocols is a multiple of 32
+            for (uint32_t p = 0; p < P.passes; p++) {
+                if (p * 128 + q * 32 >= P.m) break;                 // no token of this warp's quadrant in this block (warp-uniform)
+                const uint32_t tok = p * 128 + q * 32 + lane;
+                for (uint32_t c0 = c_lo; c0 < c_hi; c0 += 16) {
+                    uint32_t g[16], g1[16], u[16], u1[16];
+                    acc_issue(p * NT + c0, g, g1);
+                    if (P.swiglu) acc_issue(p * NT + NT / 2 + c0, u, u1);
+                    tmem_ld_wait();
+                    acc_sum(g, g1);
+                    if (P.swiglu) acc_sum(u, u1);
+                    if (tok < P.m) {
 #pragma unroll
-                for (int j = 0; j < 16; j++)
-                    if (c0 + j < P.m) emit(c0 + j, __uint_as_float(v0[j]), MT == 2 ? __uint_as_float(v1[j]) : 0.0f);
+                        for (int h = 0; h < 2; h++) {
+                            float o[8];
+#pragma unroll
+                            for (int e = 0; e < 8; e++) {
+                                const float a = __uint_as_float(g[h * 8 + e]);
+                                // SiluMulOp: bf16(bf16(silu(bf16 gate)) * bf16 up), the activation from the table of all bf16 inputs
+                                o[e] = P.swiglu ? __fmul_rn(bf2f(g_silu_lut[f2bf(a)]), rbf(__uint_as_float(u[h * 8 + e]))) : a;
+                            }
+                            store8(tok, c0 + h * 8, o);
+                        }
+                    }
+                }
             }
         }
-        tc_fence_before();
-        __syncthreads();
     } else {
-        // k split over the cluster: token column c belongs to CTA c / cs.  Once every CTA of the cluster has left its main
-        // loop (its ring is idle: every copy has landed and every MMA has read it), each CTA sends the columns of its f32
-        // partial straight from tensor memory into the owner's ring, [source rank][tile][column of the slice][128 rows];
-        // after a second barrier the owner adds the partials of a column in rank order from its own shared memory.
-        const uint32_t cs = (P.m + P.ksplit - 1) / P.ksplit;
-        float *recv = reinterpret_cast<float *>(ring);
+        // k split over the cluster: output column c of the tile belongs to CTA c / cw.  Once every CTA of the cluster has left its
+        // main loop (its ring is idle: every copy has landed and every MMA has read it), each CTA sends the columns of its f32
+        // partial straight from tensor memory into the owner's ring, [source rank][token][cw] (gate | up: 2 cw); after a second
+        // barrier the owner adds the partials of its columns in rank order from its own shared memory.
+        const uint32_t cw = P.cw, roww = P.swiglu ? 2 * cw : cw;   // floats per staged token row
+        float *stg = reinterpret_cast<float *>(ring);
         tc_fence_before();
         cluster_sync_all();
         if (go) {
-            for (uint32_t c0 = 0; c0 < P.m; c0 += 16) {
-                uint32_t v0[16], v1[16];
-                if (my_kb) {
-                    tmem_ld16(tq + c0, v0);
-                    if (MT == 2) tmem_ld16(tq + P.npad + c0, v1);
+            const uint32_t c_lo = half * (NT / 2), c_hi = c_lo + NT / 2;
+            for (uint32_t p = 0; p < P.passes; p++) {
+                if (p * 128 + q * 32 >= P.m) break;
+                const uint32_t tok = p * 128 + q * 32 + lane;
+                for (uint32_t c0 = c_lo; c0 < c_hi; c0 += 16) {
+                    uint32_t v[16], v1[16];
+                    acc_issue(p * NT + c0, v, v1);
                     tmem_ld_wait();
-                }
+                    acc_sum(v, v1);
+                    if (tok < P.m) {
 #pragma unroll
-                for (int j = 0; j < 16; j++) {
-                    const uint32_t c = c0 + j;
-                    if (c >= P.m) break;
-                    const uint32_t owner = c / cs, slot = c - owner * cs;
-                    const uint32_t a0 = smem_u32(&recv[(((size_t)rank * MT + 0) * cs + slot) * 128 + row]);
-                    st_remote_f32(a0, owner, my_kb ? __uint_as_float(v0[j]) : 0.0f);
-                    if (MT == 2) st_remote_f32(a0 + cs * 128 * 4, owner, my_kb ? __uint_as_float(v1[j]) : 0.0f);
+                        for (int h = 0; h < 4; h++) {
+                            const uint32_t col = c0 + h * 4;                            // tile column of this 4-wide piece
+                            const uint32_t oc = P.swiglu && col >= NT / 2 ? col - NT / 2 : col;   // the output column it feeds
+                            const uint32_t owner = oc / cw, off = oc - owner * cw + (P.swiglu && col >= NT / 2 ? cw : 0u);
+                            const uint32_t a = smem_u32(&stg[((size_t)rank * P.m + tok) * roww + off]);
+                            st_remote_f32x4(a, owner, __uint_as_float(v[h * 4]), __uint_as_float(v[h * 4 + 1]), __uint_as_float(v[h * 4 + 2]), __uint_as_float(v[h * 4 + 3]));
+                        }
+                    }
                 }
-            }
-        }
-        cluster_sync_all();   // release / acquire: the partials sent above are visible to their owners
-        const uint32_t c_lo = min(P.m, rank * cs), c_hi = min(P.m, c_lo + cs);
-        if (warp >= 2 && !abort_s) {   // (a peer that gave up sends nothing: the result is flagged by the timeout counter, not trusted)
-            for (uint32_t c = c_lo; c < c_hi; c++) {
-                float acc0 = 0.0f, acc1 = 0.0f;
-                for (uint32_t rk = 0; rk < P.ksplit; rk++) {
-                    acc0 += recv[(((size_t)rk * MT + 0) * cs + (c - c_lo)) * 128 + row];
-                    if (MT == 2) acc1 += recv[(((size_t)rk * MT + 1) * cs + (c - c_lo)) * 128 + row];
-                }
-                emit(c, acc0, acc1);
             }
         }
         tc_fence_before();
-        __syncthreads();
+        cluster_sync_all();   // release / acquire: the partials sent above are visible to their owners
+        const uint32_t oc_lo = min(ocols, rank * cw), oc_hi = min(ocols, oc_lo + cw);
+        if (!abort_s && oc_hi > oc_lo) {   // (a peer that gave up sends nothing: the timeout counter flags the result)
+            const uint32_t chunks = (oc_hi - oc_lo + 7) / 8;
+            for (uint32_t it = tid; it < P.m * chunks; it += UG_THREADS) {
+                const uint32_t tok = it / chunks, ch = it - tok * chunks;
+                float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+                for (uint32_t rk = 0; rk < P.ksplit; rk++) {
+                    const float *src = &stg[((size_t)rk * P.m + tok) * roww + ch * 8];
+                    const float4 x0 = *reinterpret_cast<const float4 *>(src), x1 = *reinterpret_cast<const float4 *>(src + 4);
+                    a[0] += x0.x; a[1] += x0.y; a[2] += x0.z; a[3] += x0.w; a[4] += x1.x; a[5] += x1.y; a[6] += x1.z; a[7] += x1.w;
+                    if (P.swiglu) {
+                        const float4 y0 = *reinterpret_cast<const float4 *>(src + cw), y1 = *reinterpret_cast<const float4 *>(src + cw + 4);
+                        b[0] += y0.x; b[1] += y0.y; b[2] += y0.z; b[3] += y0.w; b[4] += y1.x; b[5] += y1.y; b[6] += y1.z; b[7] += y1.w;
+                    }
+                }
+                float o[8];
+#pragma unroll
+                for (int e = 0; e < 8; e++) o[e] = P.swiglu ? __fmul_rn(bf2f(g_silu_lut[f2bf(a[e])]), rbf(b[e])) : a[e];
+                store8(tok, oc_lo + ch * 8, o);
+            }
+        }
     }
+    tc_fence_before();
+    __syncthreads();
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(P.tmem_cols) : "memory");
@@ -327,51 +411,44 @@ bool ug_map(CUtensorMap *tm, const void *base, uint64_t rows, uint64_t k, uint64
                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
-template <int MT>
-cudaError_t ug_launch(const CUtensorMap &w0, const CUtensorMap &w1, const CUtensorMap &x, const UgParams &p, uint32_t ctas, size_t smem,
-                      cudaStream_t st) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(ctas); cfg.blockDim = dim3(UG_THREADS); cfg.dynamicSmemBytes = smem; cfg.stream = st;
-    cudaLaunchAttribute at[2];
+void ug_launch_cfg(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *at, uint32_t ctas, uint32_t ksplit, size_t smem, cudaStream_t st) {
+    *cfg = cudaLaunchConfig_t{};
+    cfg->gridDim = dim3(ctas); cfg->blockDim = dim3(UG_THREADS); cfg->dynamicSmemBytes = smem; cfg->stream = st;
     int na = 0;
     at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     at[na].val.programmaticStreamSerializationAllowed = 1;
     na++;
-    if (p.ksplit > 1) {
+    if (ksplit > 1) {
         at[na].id = cudaLaunchAttributeClusterDimension;
-        at[na].val.clusterDim.x = p.ksplit; at[na].val.clusterDim.y = 1; at[na].val.clusterDim.z = 1;
+        at[na].val.clusterDim.x = ksplit; at[na].val.clusterDim.y = 1; at[na].val.clusterDim.z = 1;
         na++;
     }
-    cfg.attrs = at; cfg.numAttrs = na;
-    return cudaLaunchKernelEx(&cfg, ugemm_kernel<MT>, w0, w1, x, p);
+    cfg->attrs = at; cfg->numAttrs = na;
 }
 
 }  // namespace
 
-// Decomposition of a product, from the weight shape alone (never from m): tiles per CTA and the k split.
-struct UgPlan { uint32_t mt, ksplit; };
-static UgPlan ug_plan(uint32_t n, uint32_t k, bool swiglu, int sms) {
-    const uint32_t nkb = (k + UG_BK - 1) / UG_BK;
-    UgPlan best{swiglu ? 2u : 1u, 1u};
-    double best_eff = -1.0;
-    for (uint32_t mt = swiglu ? 2 : 1; mt <= 2; mt++) {
-        const uint32_t rows = swiglu ? n / 2 : n;
-        const uint32_t groups = swiglu ? (rows + 127) / 128 : (rows + mt * 128 - 1) / (mt * 128);
-        for (uint32_t s = 1; s <= 8; s++) {
-            if (s > 1 && nkb / s < 6) break;
-            const uint32_t ctas = groups * s, waves = (ctas + sms - 1) / sms;
-            // useful share of the machine over the product's waves; two tiles per CTA halve the token traffic (small bonus);
-            // every extra k slice costs a partial exchange (small penalty)
-            double eff = (double)ctas / ((double)waves * sms);
-            if (!swiglu && mt == 2 && groups * 2 * 128 > rows + 128) eff *= (double)((rows + 127) / 128) / (double)(groups * 2);   // an empty half tile
-            eff += (mt == 2 ? 0.02 : 0.0) - 0.004 * (s - 1);
-            if (eff > best_eff) { best_eff = eff; best = {mt, s}; }
-        }
+// Per device: SM count and how many clusters of each size the device keeps resident at once (CTAs of the paired-CTA size).
+struct UgDevice { int sms = 0; int max_clusters[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0}; };   // sms != 0: the device is set up (opt-ins made, activation table filled)
+static UgDevice g_ug_dev[64];   // written once per device ordinal by wb_ugemm_init (the same values by any thread)
+
+// The k split of a product, from the weight shape and the device alone (never from m, so a row's summation order is the same
+// in every batch).  Cost of a split s, in k blocks: rounds of CTAs x (blocks per CTA + a CTA's fixed cost); one round holds
+// as many CTAs as the device has SMs (two CTAs of an SM share its bandwidth, the second one only hides fixed costs) and, with
+// a split, as many clusters as the device keeps resident.  Measured fixed costs: ~8 blocks per CTA, ~6 more for the
+// cluster's exchange.
+static uint32_t ug_ksplit(uint32_t tiles, uint32_t nkb, const UgDevice &d) {
+    uint32_t best = 1;
+    double best_cost = 1e30;
+    for (uint32_t s = 1; s <= 8; s++) {
+        if (s > 1 && (nkb / s < 6 || d.max_clusters[s] <= 0)) continue;
+        const double cap = s == 1 ? (double)d.sms : (double)((uint32_t)d.max_clusters[s] * s < (uint32_t)d.sms ? d.max_clusters[s] * s : d.sms);
+        const double rounds = ceil((double)tiles * s / cap);
+        const double cost = rounds * ((double)((nkb + s - 1) / s) + (s == 1 ? 8.0 : 14.0));
+        if (cost < best_cost - 1e-9) { best_cost = cost; best = s; }
     }
     return best;
 }
-
-static int g_ug_sms[64];   // SM count per device ordinal (0 = not looked up yet; written once, the same value by any thread)
 
 int32_t wb_ugemm_init() {
     std::call_once(g_ug_once, [] {
@@ -383,15 +460,64 @@ int32_t wb_ugemm_init() {
     if (!g_ug_encode) { wb_set_error("gemm: the driver does not export cuTensorMapEncodeTiled"); return WB_ERR_CUDA; }
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { wb_set_error("gemm: cudaGetDevice failed or device ordinal >= 64"); return WB_ERR_CUDA; }
-    if (!g_ug_sms[dev]) {
-        int n = 0;
-        cudaError_t e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(ugemm_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_MAX);
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(ugemm_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_MAX);
-        if (e != cudaSuccess || n <= 0) { wb_set_error("gemm: shared-memory opt-in failed: %s", cudaGetErrorString(e)); return WB_ERR_CUDA; }
-        g_ug_sms[dev] = n;
+    if (!g_ug_dev[dev].sms) {
+        UgDevice d;
+        cudaError_t e = cudaDeviceGetAttribute(&d.sms, cudaDevAttrMultiProcessorCount, dev);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(ugemm_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, UG_SMEM_MAX);
+        if (e != cudaSuccess || d.sms <= 0) { wb_set_error("gemm: shared-memory opt-in failed: %s", cudaGetErrorString(e)); return WB_ERR_CUDA; }
+        silu_lut_kernel<<<256, 256>>>();   // the activation table of this device, before anything can read it
+        e = cudaGetLastError();
+        if (e == cudaSuccess) e = cudaDeviceSynchronize();
+        if (e != cudaSuccess) { wb_set_error("gemm: filling the activation table failed: %s", cudaGetErrorString(e)); return WB_ERR_CUDA; }
+        for (uint32_t s = 2; s <= 8; s++) {
+            cudaLaunchConfig_t cfg;
+            cudaLaunchAttribute at[2];
+            ug_launch_cfg(&cfg, at, s * 8, s, UG_SMEM_PAIR, nullptr);
+            int n = 0;
+            if (cudaOccupancyMaxActiveClusters(&n, ugemm_kernel, &cfg) == cudaSuccess) d.max_clusters[s] = n;
+            else cudaGetLastError();
+        }
+        g_ug_dev[dev] = d;
     }
     return WB_OK;
+}
+
+// Launch geometry of one chunk of mc <= 256 token rows.
+struct UgGeom { uint32_t nt, tiles, nkb, ksplit, cw, passes, x_rows, x_bytes, stages, tmem_cols; size_t smem; };
+static bool ug_geometry(uint32_t mc, uint32_t n, uint32_t k, bool swiglu, const UgDevice &d, UgGeom *g) {
+    const uint32_t out_cols = swiglu ? n / 2 : n;
+    g->nkb = (k + UG_BK - 1) / UG_BK;
+    g->passes = mc > 128 ? 2 : 1;
+    g->x_rows = g->passes == 2 ? 128 : (mc + 7) / 8 * 8;          // rows of the token box
+    g->x_bytes = g->passes * g->x_rows * 128;
+    // Weight rows per tile: 256 (8 KB of weights per MMA) when that still gives every SM a CTA, else 128.  The choice groups
+    // output columns and never changes a sum; the k split is taken for 128-row tiles so that it does not depend on it.
+    const uint32_t tiles128 = swiglu ? (out_cols + 63) / 64 : (out_cols + 127) / 128;
+    g->ksplit = ug_ksplit(tiles128, g->nkb, d);
+    const uint32_t tiles256 = (tiles128 + 1) / 2;
+    g->nt = ((uint64_t)tiles256 * g->ksplit >= (uint64_t)d.sms && UG_NS * g->passes * 256 <= 512) ? 256 : 128;
+    g->tiles = g->nt == 256 ? tiles256 : tiles128;
+    const uint32_t ocols = swiglu ? g->nt / 2 : g->nt;
+    g->cw = ((ocols + g->ksplit - 1) / g->ksplit + 7) / 8 * 8;
+    // Shared memory.  In a k-split CTA the ring must hold the partials it owns.  A grid of at least two CTAs per SM takes half
+    // an SM per CTA when three stages fit in that (two CTAs overlap each other's prologue and epilogue); a smaller grid takes
+    // the whole SM, because what then counts is the weight bytes one CTA keeps in flight.
+    const size_t stage = (size_t)g->nt * 128 + g->x_bytes;
+    const size_t tail = UG_XTILE;   // the MMA reads 128 token rows from a stage that may hold fewer: keep that read inside the allocation
+    const size_t staging = g->ksplit > 1 ? (size_t)g->ksplit * mc * (swiglu ? 2 : 1) * g->cw * 4 : 0;
+    size_t budget = UG_SMEM_MAX;
+    if ((uint64_t)g->tiles * g->ksplit >= 2ull * (uint64_t)d.sms && UG_NS * g->passes * g->nt <= 256 && (UG_SMEM_PAIR - 1024 - tail) / (UG_NS * stage) >= 2 &&
+        (UG_SMEM_PAIR - 1024 - tail) / (UG_NS * stage) * (UG_NS * stage) >= staging)
+        budget = UG_SMEM_PAIR;
+    uint32_t stages = (uint32_t)((budget - 1024 - tail) / (UG_NS * stage));   // per stream
+    if (stages > UG_MAX_STAGES) stages = UG_MAX_STAGES;
+    if (stages < 1 || UG_NS * stages * stage < staging || UG_NS * g->passes * g->nt > 512) return false;
+    g->stages = stages;
+    g->smem = 1024 + (size_t)UG_NS * stages * stage + tail;
+    uint32_t cols = 32;
+    while (cols < UG_NS * g->passes * g->nt) cols *= 2;
+    g->tmem_cols = cols;
+    return true;
 }
 
 // C[m,n] = A W^T (swiglu: W = [gate; up] of n = 2 * inter rows, C[m, inter]); arguments validated by the callers in gemm.cu.
@@ -401,45 +527,44 @@ int32_t wb_ugemm(const void *a, const void *w, void *c, uint32_t m, uint32_t n, 
     if (int32_t rc = wb_ugemm_init()) return rc;
     int dev = 0;
     cudaGetDevice(&dev);
-    const int sms = g_ug_sms[dev];
-    for (uint32_t m0 = 0; m0 < m; m0 += 256) {
+    const UgDevice &d = g_ug_dev[dev];
+    const uint32_t rows = swiglu ? n / 2 : n;                                   // rows of each weight map
+    CUtensorMap tw0, tw1, tx;
+    bool ok = true;
+    for (uint32_t m0 = 0; ok && m0 < m; m0 += 256) {
         const uint32_t mc = m - m0 < 256 ? m - m0 : 256;
+        UgGeom g;
+        if (!ug_geometry(mc, n, k, swiglu, d, &g)) { wb_set_error("gemm: m = %u rows do not fit the tensor-memory kernel's shared memory", mc); return WB_ERR_SHAPE; }
         UgParams p{};
         p.C = (bf16_t *)c + (size_t)m0 * ldc;
         p.m = mc; p.n = n; p.k = k; p.ldc = ldc;
-        p.npad = (mc + 15) / 16 * 16;
-        p.nkb = (k + UG_BK - 1) / UG_BK;
+        p.nt = g.nt; p.passes = g.passes; p.x_bytes = g.x_bytes; p.nkb = g.nkb; p.ksplit = g.ksplit; p.cw = g.cw; p.stages = g.stages; p.tmem_cols = g.tmem_cols;
         p.swiglu = swiglu ? 1 : 0; p.half_n = n / 2;
-        UgPlan pl = ug_plan(n, k, swiglu, sms);
-        // shared memory: at least 3 stages, and the k-split partials must fit in the ring
-        auto stage_bytes = [&](uint32_t mt) { return (size_t)mt * UG_WTILE + (size_t)p.npad * 128; };
-        auto fits = [&](uint32_t mt, uint32_t ks) {
-            const size_t ring = (UG_SMEM_MAX - 1024) / stage_bytes(mt) * stage_bytes(mt);
-            const size_t cs = (mc + ks - 1) / ks;
-            return (UG_SMEM_MAX - 1024) / stage_bytes(mt) >= 3 && (ks == 1 || (size_t)ks * mt * cs * 128 * 4 <= ring) && mt * p.npad <= 512;
-        };
-        if (!fits(pl.mt, pl.ksplit)) {
-            if (swiglu || !fits(1, pl.ksplit)) { wb_set_error("gemm: m = %u rows do not fit the tensor-core kernel's shared memory", mc); return WB_ERR_SHAPE; }
-            pl.mt = 1;   // tiles per CTA never change a result bit
-        }
-        p.ksplit = pl.ksplit;
-        uint32_t stages = (uint32_t)((UG_SMEM_MAX - 1024) / stage_bytes(pl.mt));
-        if (stages > 8) stages = 8;
-        p.stages = stages;
-        const size_t smem = 1024 + (size_t)stages * stage_bytes(pl.mt);
-        uint32_t cols = 32;
-        while (cols < pl.mt * p.npad) cols *= 2;
-        p.tmem_cols = cols;
-        const uint32_t rows = swiglu ? n / 2 : n;
-        const uint32_t groups = swiglu ? (rows + 127) / 128 : (rows + pl.mt * 128 - 1) / (pl.mt * 128);
-        CUtensorMap tw0, tw1, tx;
-        bool ok = ug_map(&tw0, w, rows, k, k, 128) &&
-                  ug_map(&tw1, swiglu ? (const bf16_t *)w + (size_t)rows * k : (const bf16_t *)w, rows, k, k, 128) &&
-                  ug_map(&tx, (const bf16_t *)a + (size_t)m0 * lda, mc, k, lda, p.npad);
-        if (!ok) { wb_set_error("gemm: cuTensorMapEncodeTiled failed for m=%u n=%u k=%u", mc, n, k); return WB_ERR_CUDA; }
-        cudaError_t e = pl.mt == 2 ? ug_launch<2>(tw0, tw1, tx, p, groups * pl.ksplit, smem, st) : ug_launch<1>(tw0, tw1, tx, p, groups * pl.ksplit, smem, st);
+        p.vec_ok = (ldc % 8 == 0 && ((uintptr_t)p.C & 15u) == 0) ? 1 : 0;
+        const uint32_t wbox = swiglu ? g.nt / 2 : g.nt;
+        ok = ug_map(&tw0, w, rows, k, k, wbox) && ug_map(&tw1, swiglu ? (const bf16_t *)w + (size_t)rows * k : (const bf16_t *)w, rows, k, k, wbox) &&
+             ug_map(&tx, (const bf16_t *)a + (size_t)m0 * lda, mc, k, lda, g.x_rows);
+        if (!ok) break;
+        cudaLaunchConfig_t cfg;
+        cudaLaunchAttribute at[2];
+        ug_launch_cfg(&cfg, at, g.tiles * g.ksplit, g.ksplit, g.smem, st);
+        cudaError_t e = cudaLaunchKernelEx(&cfg, ugemm_kernel, tw0, tw1, tx, p);
         if (e != cudaSuccess) { wb_set_error("gemm: launch failed for m=%u n=%u k=%u: %s", mc, n, k, cudaGetErrorString(e)); return WB_ERR_CUDA; }
     }
+    if (!ok) { wb_set_error("gemm: cuTensorMapEncodeTiled failed for m=%u n=%u k=%u", m, n, k); return WB_ERR_CUDA; }
+    return WB_OK;
+}
+
+// How the tensor-memory kernel would run a product on the current device: out[0] = CTAs, out[1] = k split (cluster size),
+// out[2] = pipeline stages, out[3] = shared memory per CTA in bytes, out[4] = weight rows per tile.  The k split depends on (n, k) and the device, never on m.
+extern "C" int32_t wein_b200_gemm_plan(uint32_t m, uint32_t n, uint32_t k, uint32_t swiglu, uint32_t *out) {
+    WB_CHECK_ARG(out && m >= 1 && n >= 1 && k >= 8, "gemm_plan: bad argument");
+    if (int32_t rc = wb_ugemm_init()) return rc;
+    int dev = 0;
+    cudaGetDevice(&dev);
+    UgGeom g;
+    if (!ug_geometry(m < 256 ? m : 256, swiglu ? 2 * n : n, k, swiglu != 0, g_ug_dev[dev], &g)) { wb_set_error("gemm_plan: shape does not fit"); return WB_ERR_SHAPE; }
+    out[0] = g.tiles * g.ksplit; out[1] = g.ksplit; out[2] = g.stages; out[3] = (uint32_t)g.smem; out[4] = g.nt;
     return WB_OK;
 }
 

@@ -38,18 +38,32 @@ def _time(fn, n_launch, reps):
     return best * 1e-3
 
 
-def case_gemm(reps, m=4, inter=9216, k=2560, n_mat=8, tc=-1):
+def _graph_time(one, n_mat, reps):
+    """Seconds per launch of `one(i)`, i = 0..n_mat-1, replayed as one CUDA graph (the host's launch rate stays out)."""
+    side = torch.cuda.Stream()
+    with torch.cuda.stream(side):
+        one(0)
+    torch.cuda.synchronize()
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=side):
+        for i in range(n_mat):
+            one(i)
+    return _time(lambda i: g.replay(), 1, reps) / n_mat
+
+
+def case_gemm(reps, m=4, inter=9216, k=2560, n_mat=8, tc=-1, graph=1):
     """gate|up projection with the SwiGLU epilogue (the round's dominant launch), 8 matrices of 94 MB in rotation.
-    tc = 1 forces the tensor-memory kernel, 0 the choice by row count (m <= 32: register-streaming kernel), -1 = by m."""
+    tc = 1 forces the tensor-memory kernel, 0 the register-streaming kernel (m <= 32), -1 = by m; graph = 0 launches eagerly
+    (one kernel per launch, easy to select with `ncu -k`; the host launch gap is then inside the time)."""
     tc = (m > 32) if tc < 0 else bool(tc)
     ws = [torch.randn(2 * inter, k, device="cuda").to(torch.bfloat16) * 0.02 for _ in range(n_mat)]
     a = torch.randn(m, k, device="cuda").to(torch.bfloat16)
     out = torch.empty(m, inter, dtype=torch.bfloat16, device="cuda")
-    sec = _time(lambda i: ops.gemm_swiglu(a, ws[i], out, m, inter, k, tc=tc), n_mat, reps)
+    one = lambda i: ops.gemm_swiglu(a, ws[i], out, m, inter, k, tc=tc)
+    sec = _graph_time(one, n_mat, reps) if graph else _time(one, n_mat, reps)
     byt = 2 * inter * k * 2 + m * k * 2 + m * inter * 2
     return dict(kernel=("ugemm_kernel" if tc else "wgemm_kernel") + " (gate|up + SwiGLU)", m=m, n=2 * inter, k=k, us=sec * 1e6, bytes=byt, gbs=byt / sec / 1e9,
-                timeouts=ops.gemm_wait_timeouts(),
-                note="eager launches: the host launch gap is inside the time; bench.py times the same kernel by graph replay")
+                timeouts=ops.gemm_wait_timeouts(), graph=bool(graph), plan=ops.gemm_plan(m, inter, k, True) if tc else None)
 
 
 def case_gemm_wt(reps, m=128, n=2560, k=9216, tc=-1, graph=1):
@@ -63,20 +77,9 @@ def case_gemm_wt(reps, m=128, n=2560, k=9216, tc=-1, graph=1):
     out = torch.empty(m, n, dtype=torch.bfloat16, device="cuda")
     one = lambda i: ops.gemm_wt(a, ws[i], out, m, n, k, tc=tc)
     byt = n * k * 2 + m * k * 2 + m * n * 2
-    if graph:
-        side = torch.cuda.Stream()
-        with torch.cuda.stream(side):
-            one(0)
-        torch.cuda.synchronize()
-        g = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(g, stream=side):
-            for i in range(n_mat):
-                one(i)
-        sec = _time(lambda i: g.replay(), 1, reps) / n_mat
-    else:
-        sec = _time(one, n_mat, reps)
+    sec = _graph_time(one, n_mat, reps) if graph else _time(one, n_mat, reps)
     return dict(kernel="ugemm_kernel" if tc else "wgemm_kernel", m=m, n=n, k=k, us=sec * 1e6, bytes=byt, gbs=byt / sec / 1e9, matrices=n_mat,
-                timeouts=ops.gemm_wait_timeouts())
+                timeouts=ops.gemm_wait_timeouts(), plan=ops.gemm_plan(m, n, k) if tc else None)
 
 
 def case_gdn(reps, B=32, P=4, n_layers=2):

@@ -158,6 +158,14 @@ def gemm_wt(a, w, c, m, n, k, scratch=None, tc=False):
     check(load().wein_b200_gemm_wt(_ptr(a), _ptr(w), _ptr(c), U32(m), U32(n), U32(k), _ptr(scratch), U64(sb), _stream()))
 
 
+def gemm_plan(m, n, k, swiglu=False):
+    """(CTAs, k split, stages, shared-memory bytes, weight rows per tile) the tensor-memory GEMM uses for this shape on the
+    current device."""
+    out = (C.c_uint32 * 5)()
+    check(load().wein_b200_gemm_plan(U32(m), U32(n), U32(k), U32(int(swiglu)), out))
+    return tuple(int(v) for v in out)
+
+
 def gemm_wait_timeouts():
     """Barrier waits of the tensor-memory GEMM that ran into their time limit since the library was loaded (0 in a healthy run)."""
     v = C.c_uint32(0)

@@ -175,6 +175,15 @@ def test_tensor_memory_gemm_tolerance_and_batch_invariance(ops, m, n, k):
     assert ops.gemm_wait_timeouts() == 0
 
 
+def test_tensor_memory_gemm_split_depends_on_the_weight_shape_only(ops):
+    """The k split (cluster size) fixes the order in which a row's partial sums are added, so it must come from (n, k) and
+    the device alone: the same for every row count, and for the plain and SwiGLU forms of a shape family."""
+    for n, k in [(2560, 9216), (2560, 4096), (12352, 2560), (10240, 2560), (151936, 2560), (2560, 5120), (1544, 512)]:
+        splits = {ops.gemm_plan(m, n, k)[1] for m in (1, 8, 31, 32, 33, 40, 128, 160, 256, 300)}
+        assert len(splits) == 1, (n, k, splits)
+    assert len({ops.gemm_plan(m, 9216, 2560, True)[1] for m in (1, 4, 40, 128, 256)}) == 1
+
+
 @pytest.mark.parametrize("m,inter,k", [(128, 9216, 2560), (40, 9216, 2560), (8, 9216, 2560), (1, 1000, 576), (50, 1024, 512)])
 def test_tensor_memory_gemm_swiglu_matches_operator_chain(ops, m, inter, k):
     """gate|up + SwiGLU through the tensor-memory kernel == its own plain products followed by the oracle's silu_mul, bit for bit."""
