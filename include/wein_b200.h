@@ -210,7 +210,9 @@ int32_t wein_b200_argmax_rows(const void *x, const void *rows, void *scratch, vo
  * receives one call's tensors; code inside a graph-capture region or under a memory pool it does not own): the slice maxima
  * live in a 64 KiB array built into the library (held by every GPU that loads it) instead of a caller buffer.  At most 256
  * rows per call (WEIN_B200_ERR_CAPACITY beyond).  The first call on each device looks the array's address up on the host:
- * make it outside any stream capture.  All calls on a device share the array: calls that may overlap on the GPU race. */
+ * make it outside any stream capture.  All calls on a device share the array: calls that may overlap on the GPU race.  The
+ * looked-up address is kept per device ordinal (ordinals >= 64 are refused with WEIN_B200_ERR_CUDA) without a lock -- two
+ * threads making the first call together store the same value -- and does not survive a cudaDeviceReset of that device. */
 int32_t wein_b200_argmax_rows_noalloc(const void *x, const void *rows, void *out, uint32_t n, uint32_t s, void *stream);
 
 /* SampleRowsOp::run (ops/mod.rs:1379-1393): temperature / top-k (<= 64) / top-p sampler with one PCG-XSH-RR state per slot in

@@ -24,7 +24,11 @@
 #include "internal.h"
 
 #define ATT_PAGE 16
-#define ATT_STAGES 2   // per-warp page pipeline depth.  Measured: 3 stages (200 KB per CTA) is no faster on its own and slows the whole round (batch 1: 2.71 -> 3.6 ms): the SM has to be re-split towards shared memory for this kernel and back to L1 for the GEMM that follows
+// Per-warp page pipeline depth NS (a template parameter: it never changes a result).  Two stages (136 KB per CTA at head_dim 256)
+// for callers whose GEMMs run on the register-streaming kernel: that kernel wants the SM's memory as L1, and with 200 KB
+// attention CTAs in between the SM is re-split around every attention launch (measured at batch 1: 2.71 -> 3.6 ms per round).
+// Three stages for callers whose GEMMs take the whole shared memory anyway (the tensor-memory kernel): two page pairs in
+// flight per warp instead of one.
 
 __device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void cp_async16(uint32_t dst, const void *src, uint32_t src_bytes) {
@@ -60,13 +64,12 @@ struct AttnParams {
 template <int HD>
 __device__ __forceinline__ uint32_t tile_off(uint32_t r, uint32_t ch) { return r * (HD * 2) + ((ch ^ (r & 7)) << 4); }
 
-template <int HD>
+template <int HD, int NS>
 __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
     PDL_ENTRY();
     constexpr int KS = HD / 16, ND = HD / 8, CH = HD / 8;       // k-steps of QK^T, d n-tiles of PV, 16-byte chunks per row
     constexpr int KL = 4;                                        // the four warps take the segment's pages round-robin
     constexpr int PAGE_BYTES = ATT_PAGE * HD * 2;
-    constexpr int NS = ATT_STAGES;                               // (K, V) page pairs per warp: NS - 1 of them in flight while one is used
     extern __shared__ __align__(128) unsigned char smem[];
     // layout: Q tile [16][HD] | per warp: NS stages x (K page, V page) ; merge area aliases the stages
     unsigned char *q_s = smem;
@@ -283,32 +286,32 @@ __global__ void attn_combine_kernel(const AttnParams P) {
     *reinterpret_cast<uint2 *>(P.out + oi) = make_uint2((uint32_t)r[0] | ((uint32_t)r[1] << 16), (uint32_t)r[2] | ((uint32_t)r[3] << 16));
 }
 
-template <int HD>
+template <int HD, int NS>
 static size_t attn_smem_bytes() {
-    size_t smem = 16 * HD * 2 + 4 * ATT_STAGES * 2 * (size_t)ATT_PAGE * HD * 2;
+    size_t smem = 16 * HD * 2 + 4 * NS * 2 * (size_t)ATT_PAGE * HD * 2;
     size_t merge = 16 * HD * 2 + 4 * 16 * (size_t)(HD + 4) * 4;
     return smem < merge ? merge : smem;
 }
 // The shared-memory opt-in is a per-device function attribute: one flag per device ordinal, set once (writing it twice from
 // two threads stores the same value).
-static bool g_attn_ready[3][64];
-template <int HD>
+static bool g_attn_ready[6][64];
+template <int HD, int NS>
 static int32_t attn_prepare(int which) {
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { wb_set_error("attn: cudaGetDevice failed or device ordinal >= 64"); return WB_ERR_CUDA; }
     if (g_attn_ready[which][dev]) return WB_OK;
-    const size_t smem = attn_smem_bytes<HD>();
-    cudaError_t e = cudaFuncSetAttribute(attn_verify_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = attn_smem_bytes<HD, NS>();
+    cudaError_t e = cudaFuncSetAttribute(attn_verify_kernel<HD, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { wb_set_error("attn: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return WB_ERR_CUDA; }
     g_attn_ready[which][dev] = true;
     return WB_OK;
 }
 
-template <int HD>
+template <int HD, int NS>
 static int32_t attn_launch(const AttnParams &p, int which, cudaStream_t st) {
-    if (int32_t rc = attn_prepare<HD>(which)) return rc;
+    if (int32_t rc = attn_prepare<HD, NS>(which)) return rc;
     dim3 grid(p.max_segs, p.kv_heads, p.n_spans * p.n_mtiles);
-    WB_LAUNCH((attn_verify_kernel<HD>), grid, 128, attn_smem_bytes<HD>(), st, p);
+    WB_LAUNCH((attn_verify_kernel<HD, NS>), grid, 128, attn_smem_bytes<HD, NS>(), st, p);
     WB_LAUNCH_CHECK();
     dim3 g2(16 * p.n_mtiles, p.kv_heads, p.n_spans);
     WB_LAUNCH((attn_combine_kernel<HD>), g2, HD / 4, 0, st, p);
@@ -318,9 +321,9 @@ static int32_t attn_launch(const AttnParams &p, int which, cudaStream_t st) {
 
 int32_t wb_attn_init(uint32_t head_dim) {
     switch (head_dim) {
-        case 256: return attn_prepare<256>(0);
-        case 128: return attn_prepare<128>(1);
-        case 64: return attn_prepare<64>(2);
+        case 256: { int32_t rc = attn_prepare<256, 2>(0); return rc ? rc : attn_prepare<256, 3>(3); }
+        case 128: { int32_t rc = attn_prepare<128, 2>(1); return rc ? rc : attn_prepare<128, 3>(4); }
+        case 64: { int32_t rc = attn_prepare<64, 2>(2); return rc ? rc : attn_prepare<64, 3>(5); }
         default: wb_set_error("attn: head_dim %u not built", head_dim); return WB_ERR_SHAPE;
     }
 }
@@ -336,7 +339,7 @@ int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, 
                        const void *positions, const void *row_start, const void *row_count, const void *gate, void *out,
                        float q_scale, uint32_t bpr, uint32_t block_size, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
                        uint32_t n_spans, uint32_t max_count, uint32_t max_ctx, uint32_t seg_pages, void *scratch,
-                       uint64_t scratch_bytes, uint32_t *status, cudaStream_t st) {
+                       uint64_t scratch_bytes, uint32_t *status, bool deep, cudaStream_t st) {
     WB_CHECK_ARG(q && k_cache && v_cache && block_table && seq_ids && positions && out && scratch, "attn_verify: null pointer");
     if (block_size != ATT_PAGE) { wb_set_error("attn_verify: built for 16-token pages, got %u", block_size); return WB_ERR_SHAPE; }
     WB_CHECK_ARG(kv_heads > 0 && q_heads % kv_heads == 0, "attn_verify: q_heads %u not a multiple of kv_heads %u", q_heads, kv_heads);
@@ -358,9 +361,9 @@ int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, 
     p.scale_log2 = q_scale * 1.4426950408889634f;
     p.bpr = bpr; p.q_heads = q_heads; p.kv_heads = kv_heads; p.n_spans = n_spans; p.status = status;
     switch (head_dim) {
-        case 256: return attn_launch<256>(p, 0, st);
-        case 128: return attn_launch<128>(p, 1, st);
-        case 64: return attn_launch<64>(p, 2, st);
+        case 256: return deep ? attn_launch<256, 3>(p, 3, st) : attn_launch<256, 2>(p, 0, st);
+        case 128: return deep ? attn_launch<128, 3>(p, 4, st) : attn_launch<128, 2>(p, 1, st);
+        case 64: return deep ? attn_launch<64, 3>(p, 5, st) : attn_launch<64, 2>(p, 2, st);
         default: wb_set_error("attn_verify: head_dim %u not built (64, 128, 256)", head_dim); return WB_ERR_SHAPE;
     }
 }
@@ -374,7 +377,7 @@ int32_t wein_b200_paged_attn(const void *q, const void *k_cache, const void *v_c
                              uint32_t kv_heads, uint32_t head_dim, uint32_t tokens, void *scratch, uint64_t scratch_bytes, void *stream) {
     uint32_t seg = (bpr + 15) / 16;  // at most 16 segments per row
     return wb_attn_verify(q, k_cache, v_cache, block_table, seq_ids, positions, nullptr, nullptr, nullptr, out, q_scale, bpr, block_size,
-                          q_heads, kv_heads, head_dim, tokens, 1, bpr * ATT_PAGE, seg, scratch, scratch_bytes, nullptr, (cudaStream_t)stream);
+                          q_heads, kv_heads, head_dim, tokens, 1, bpr * ATT_PAGE, seg, scratch, scratch_bytes, nullptr, false, (cudaStream_t)stream);
 }
 
 int32_t wein_b200_attn_verify(const void *q, const void *k_cache, const void *v_cache, const void *block_table, const void *seq_ids,
@@ -384,7 +387,7 @@ int32_t wein_b200_attn_verify(const void *q, const void *k_cache, const void *v_
                               uint64_t scratch_bytes, void *status, void *stream) {
     WB_CHECK_ARG(row_start && row_count, "attn_verify: span tables are required");
     return wb_attn_verify(q, k_cache, v_cache, block_table, seq_ids, positions, row_start, row_count, gate, out, q_scale, bpr, block_size,
-                          q_heads, kv_heads, head_dim, n_spans, max_count, max_ctx, seg_pages, scratch, scratch_bytes, (uint32_t *)status, (cudaStream_t)stream);
+                          q_heads, kv_heads, head_dim, n_spans, max_count, max_ctx, seg_pages, scratch, scratch_bytes, (uint32_t *)status, false, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -543,7 +543,7 @@ static int32_t full_attn_block(Engine *e, const wein_b200_layer_weights &w, void
                    c.kv_heads, c.head_dim, c.rot_dim, c.rms_eps, st));
     float q_scale = 1.0f / sqrtf((float)c.head_dim);
     TRY(wb_attn_verify(e->qh, kp, vp, bt, seq_ids, kv_pos, row_start, row_count, e->gate, e->attn, q_scale, bpr, 16, c.q_heads, c.kv_heads,
-                       c.head_dim, n_spans, max_count, max_ctx, seg_pages, e->attn_scratch, e->attn_scratch_bytes, status, st));
+                       c.head_dim, n_spans, max_count, max_ctx, seg_pages, e->attn_scratch, e->attn_scratch_bytes, status, e->gemm_path == WB_GEMM_TC, st));
     e->launches += 3;
     TRY(gemm(e, e->attn, w.o, e->o, T, H, qd, qd, H, st));
     return WB_OK;

@@ -16,9 +16,8 @@
 //    plus ~100 per stage on barriers, so what bounds an SM's streaming rate is weight bytes per instruction: 8 KB at
 //    N = 256 against 4 KB with the weights as the M operand (which capped an SM at ~40 GB/s, below its share of HBM);
 //  * a stage = 64 k of the weight tile (NT x 128 B) + 64 k of the token block(s) (16 KB each), brought in by tensor-map
-//    bulk copies (cp.async.bulk.tensor, 128-byte swizzle, no multicast) that complete on an mbarrier.  A grid of at least
-//    two CTAs per SM takes half an SM per CTA when three stages fit in that, so that one CTA streams while the other is in
-//    its prologue or epilogue (measured: with one 225 KB CTA per SM an SM idled for a third of each CTA's life);
+//    bulk copies (cp.async.bulk.tensor, 128-byte swizzle, no multicast) that complete on an mbarrier; a CTA takes the whole
+//    SM's shared memory for its stages;
 //  * weights are never written inside a round, so the producer thread issues the weight copies of the first stages
 //    BEFORE the kernel waits for its predecessor (programmatic dependent launch); token copies, the tensor-memory
 //    allocation and everything else come after the wait.  Allocating tensor memory before the wait could deadlock: a
@@ -50,7 +49,6 @@ constexpr int UG_NS = 2;                       // independent pipelines (produce
 constexpr int UG_THREADS = (2 * UG_NS + 4) * 32;   // per stream a producer warp and an MMA warp, then four epilogue warps
 constexpr long long UG_WAIT_CYCLES = 2000000000ll;   // ~1 s
 constexpr int UG_SMEM_MAX = 225 * 1024;        // one CTA per SM
-constexpr int UG_SMEM_PAIR = 110 * 1024;       // two CTAs per SM
 constexpr int UG_MAX_STAGES = 6;               // per stream
 
 __device__ unsigned int g_ug_timeouts;
@@ -139,6 +137,13 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t (&v)[16]) {
                    "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15])
                  : "r"(taddr));
 }
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]),
+                   "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]),
+                   "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                 : "r"(taddr));
+}
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -164,10 +169,14 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) { return (uint32_t
 // of HBM.  So a CTA runs UG_NS = 2 independent pipelines: stream j takes k blocks j, j + 2, ... through its own stages and
 // barriers into its own accumulator; the epilogue adds accumulator 1 to accumulator 0.  Which block goes to which stream is
 // fixed by the block index, so the order of every sum is still fixed by (n, k) alone.
-__global__ void __launch_bounds__(UG_THREADS, 2)
+__global__ void __launch_bounds__(UG_THREADS, 1)
 ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ CUtensorMap tm_w1,
              const __grid_constant__ CUtensorMap tm_x, const UgParams P) {
     pdl_trigger();
+    if (threadIdx.x < 3) {   // the copy engine reads a 128-byte descriptor before its first copy: fetch the three of them now
+        const CUtensorMap *tm = threadIdx.x == 0 ? &tm_w0 : (threadIdx.x == 1 ? &tm_w1 : &tm_x);
+        asm volatile("prefetch.tensormap [%0];" ::"l"(tm) : "memory");
+    }
     extern __shared__ unsigned char ug_smem_raw[];
     __shared__ uint64_t bar_full[UG_NS][UG_MAX_STAGES], bar_empty[UG_NS][UG_MAX_STAGES], bar_accum[UG_NS];
     __shared__ uint32_t tmem_base_s;
@@ -306,6 +315,28 @@ ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ 
             for (uint32_t p = 0; p < P.passes; p++) {
                 if (p * 128 + q * 32 >= P.m) break;                 // no token of this warp's quadrant in this block (warp-uniform)
                 const uint32_t tok = p * 128 + q * 32 + lane;
+                if (!P.swiglu) {
+                    // plain rows: 32 columns per step (one load per stream, one wait), 64 contiguous bytes of the C row
+                    for (uint32_t c0 = c_lo; c0 < c_hi; c0 += 32) {
+                        uint32_t v[32], w[32];
+                        if (n_acc >= 1) tmem_ld32(tq + p * NT + c0, v);
+                        if (n_acc == 2) tmem_ld32(tq + acc_cols + p * NT + c0, w);
+                        tmem_ld_wait();
+                        if (tok < P.m) {
+#pragma unroll
+                            for (int h = 0; h < 4; h++) {
+                                float o[8];
+#pragma unroll
+                                for (int e = 0; e < 8; e++) {
+                                    const float a = n_acc >= 1 ? __uint_as_float(v[h * 8 + e]) : 0.0f;
+                                    o[e] = n_acc == 2 ? a + __uint_as_float(w[h * 8 + e]) : a;
+                                }
+                                store8(tok, c0 + h * 8, o);
+                            }
+                        }
+                    }
+                    continue;
+                }
                 for (uint32_t c0 = c_lo; c0 < c_hi; c0 += 16) {
                     uint32_t g[16], g1[16], u[16], u1[16];
                     acc_issue(p * NT + c0, g, g1);
@@ -428,7 +459,7 @@ void ug_launch_cfg(cudaLaunchConfig_t *cfg, cudaLaunchAttribute *at, uint32_t ct
 
 }  // namespace
 
-// Per device: SM count and how many clusters of each size the device keeps resident at once (CTAs of the paired-CTA size).
+// Per device: SM count and how many clusters of each size the device keeps resident at once (CTAs of the full shared-memory size).
 struct UgDevice { int sms = 0; int max_clusters[9] = {0, 0, 0, 0, 0, 0, 0, 0, 0}; };   // sms != 0: the device is set up (opt-ins made, activation table filled)
 static UgDevice g_ug_dev[64];   // written once per device ordinal by wb_ugemm_init (the same values by any thread)
 
@@ -472,7 +503,7 @@ int32_t wb_ugemm_init() {
         for (uint32_t s = 2; s <= 8; s++) {
             cudaLaunchConfig_t cfg;
             cudaLaunchAttribute at[2];
-            ug_launch_cfg(&cfg, at, s * 8, s, UG_SMEM_PAIR, nullptr);
+            ug_launch_cfg(&cfg, at, s * 8, s, UG_SMEM_MAX, nullptr);
             int n = 0;
             if (cudaOccupancyMaxActiveClusters(&n, ugemm_kernel, &cfg) == cudaSuccess) d.max_clusters[s] = n;
             else cudaGetLastError();
@@ -499,16 +530,13 @@ static bool ug_geometry(uint32_t mc, uint32_t n, uint32_t k, bool swiglu, const 
     g->tiles = g->nt == 256 ? tiles256 : tiles128;
     const uint32_t ocols = swiglu ? g->nt / 2 : g->nt;
     g->cw = ((ocols + g->ksplit - 1) / g->ksplit + 7) / 8 * 8;
-    // Shared memory.  In a k-split CTA the ring must hold the partials it owns.  A grid of at least two CTAs per SM takes half
-    // an SM per CTA when three stages fit in that (two CTAs overlap each other's prologue and epilogue); a smaller grid takes
-    // the whole SM, because what then counts is the weight bytes one CTA keeps in flight.
+    // Shared memory: one CTA per SM with as many stages as fit (measured: CTAs of half an SM with fewer stages each were slower
+    // in every shape, 24 against 20 us for the gate|up product at 40 rows); in a k-split CTA the ring must hold the partials it
+    // owns.
     const size_t stage = (size_t)g->nt * 128 + g->x_bytes;
     const size_t tail = UG_XTILE;   // the MMA reads 128 token rows from a stage that may hold fewer: keep that read inside the allocation
     const size_t staging = g->ksplit > 1 ? (size_t)g->ksplit * mc * (swiglu ? 2 : 1) * g->cw * 4 : 0;
-    size_t budget = UG_SMEM_MAX;
-    if ((uint64_t)g->tiles * g->ksplit >= 2ull * (uint64_t)d.sms && UG_NS * g->passes * g->nt <= 256 && (UG_SMEM_PAIR - 1024 - tail) / (UG_NS * stage) >= 2 &&
-        (UG_SMEM_PAIR - 1024 - tail) / (UG_NS * stage) * (UG_NS * stage) >= staging)
-        budget = UG_SMEM_PAIR;
+    const size_t budget = UG_SMEM_MAX;
     uint32_t stages = (uint32_t)((budget - 1024 - tail) / (UG_NS * stage));   // per stream
     if (stages > UG_MAX_STAGES) stages = UG_MAX_STAGES;
     if (stages < 1 || UG_NS * stages * stage < staging || UG_NS * g->passes * g->nt > 512) return false;

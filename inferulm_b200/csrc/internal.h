@@ -16,7 +16,8 @@ int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, 
                        const void *positions, const void *row_start, const void *row_count, const void *gate, void *out,
                        float q_scale, uint32_t bpr, uint32_t block_size, uint32_t q_heads, uint32_t kv_heads, uint32_t head_dim,
                        uint32_t n_spans, uint32_t max_count, uint32_t max_ctx, uint32_t seg_pages, void *scratch,
-                       uint64_t scratch_bytes, uint32_t *status, cudaStream_t st);  // status: optional, indexed by sequence id
+                       uint64_t scratch_bytes, uint32_t *status, bool deep, cudaStream_t st);  // status: optional, indexed by sequence id;
+                       // deep: three page stages per warp (200 KB CTAs) instead of two; never changes a result
 int32_t wb_attn_init(uint32_t head_dim);  // one-time shared-memory opt-in, outside any stream capture
 int32_t wein_b200_argmax_partials(const void *x, const void *rows, void *part, uint32_t n, uint32_t s, uint32_t split, cudaStream_t st);
 

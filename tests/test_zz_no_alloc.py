@@ -33,6 +33,25 @@ def test_noalloc_argmax_matches_scratch_entry_twice():
         assert np.array_equal(host(got, np.uint32), host(want, np.uint32)), call
         assert host(got, np.uint32)[-1] == 5                                       # rows[-1] == 0, the tied row
         assert np.array_equal(host(got, np.uint32), orc.argmax_rows(x.reshape(-1), rows, n, threads=4)), call
+    # the capacity edge: 256 rows fill the built-in array to its last word (row 255's slices sit at words 8160..8191)
+    s, n2 = ops.ARGMAX_NOALLOC_MAX_ROWS, 4099
+    rs = np.random.default_rng(3)
+    x = rand_bf16(rs, s * n2, 3.0)
+    rows = rs.permutation(s).astype(np.uint32)
+    xd, rd = dev(x), dev(rows)
+    want = torch.empty(s, dtype=torch.int32, device="cuda")
+    scratch = torch.empty(s * ops.ARGMAX_SPLIT, dtype=torch.int64, device="cuda")
+    ops.argmax_rows(xd, rd, scratch, want, n2, s)
+    got = torch.full((s,), -1, dtype=torch.int32, device="cuda")
+    ops.argmax_rows_noalloc(xd, rd, got, n2, s)
+    torch.cuda.synchronize()
+    assert np.array_equal(host(got, np.uint32), host(want, np.uint32))
+    assert np.array_equal(host(got, np.uint32), orc.argmax_rows(x, rows, n2, threads=4))
+    # an empty call is accepted and touches nothing
+    keep = got.clone()
+    ops.argmax_rows_noalloc(xd, rd, got, n2, 0)
+    torch.cuda.synchronize()
+    assert torch.equal(got, keep)
     # beyond the built-in capacity the call is refused before any launch
     big = ops.ARGMAX_NOALLOC_MAX_ROWS + 1
     z = torch.zeros(big * 8, dtype=torch.int16, device="cuda")
