@@ -340,7 +340,11 @@ def measure_workload(torch, dist, world, rank, weights, shape, wl, args, peak, s
     job = Job(torch, dist, world, weights, wl, 3 * (args.warmup + args.steps) + 8, rank, synthetic_kv)
     eng, B, k = job.eng, job.B, job.k
     job.timed(args.warmup, "graph")
+    if args.profile:
+        torch.cuda.profiler.start()
     ms, toks = job.timed(args.steps, "graph")
+    if args.profile:
+        torch.cuda.profiler.stop()
     launches = eng.last_launches() * args.steps
     ctx_now = max(p for _, p in eng.counts(job.slots))
     # the verify step alone: the drafts handed in are the tokens the MTP head would have proposed or any ids -- the time of the
@@ -609,6 +613,7 @@ def main():
     ap.add_argument("--workload", default="c2", choices=sorted(WORKLOADS))
     ap.add_argument("--prompt", type=int, default=0, help="override the workload's prompt length (profiling captures use a short one)")
     ap.add_argument("--only-headline", action="store_true", help="skip the bs32 / c4 / c5 objects (profiling captures)")
+    ap.add_argument("--profile", action="store_true", help="bracket the timed rounds with cudaProfilerStart/Stop (for ncu --profile-from-start off)")
     args = ap.parse_args()
     wl = dict(WORKLOADS[args.workload])
     if args.prompt:

@@ -16,12 +16,11 @@
 //    plus ~100 per stage on barriers, so what bounds an SM's streaming rate is weight bytes per instruction: 8 KB at
 //    N = 256 against 4 KB with the weights as the M operand (which capped an SM at ~40 GB/s, below its share of HBM);
 //  * a stage = 64 k of the weight tile (NT x 128 B) + 64 k of the token block(s) (16 KB each), brought in by tensor-map
-//    bulk copies (cp.async.bulk.tensor, 128-byte swizzle, no multicast) that complete on an mbarrier; a CTA takes the whole
+//    bulk copies (cp.async.bulk.tensor, 128-byte swizzle, each CTA fetching its own tiles) that complete on an mbarrier; a CTA takes the whole
 //    SM's shared memory for its stages;
 //  * weights are never written inside a round, so the producer thread issues the weight copies of the first stages
-//    BEFORE the kernel waits for its predecessor (programmatic dependent launch); token copies, the tensor-memory
-//    allocation and everything else come after the wait.  Allocating tensor memory before the wait could deadlock: a
-//    CTA that holds columns while it waits for the predecessor grid can starve a predecessor CTA of columns;
+//    and claims its tensor memory BEFORE the kernel waits for its predecessor (programmatic dependent launch); only the
+//    token copies and the MMAs come after the wait;
 //  * one thread issues the MMAs (kind::f16, M = 128, K = 16: four per stage and token block); tcgen05.commit frees the
 //    stage for the producer and finally signals the epilogue warps;
 //  * the epilogue is row-local and runs on all eight warps: thread = token (tensor-memory lane), columns = consecutive weight
@@ -49,6 +48,7 @@ constexpr int UG_NS = 2;                       // independent pipelines (produce
 constexpr int UG_THREADS = (2 * UG_NS + 4) * 32;   // per stream a producer warp and an MMA warp, then four epilogue warps
 constexpr long long UG_WAIT_CYCLES = 2000000000ll;   // ~1 s
 constexpr int UG_SMEM_MAX = 225 * 1024;        // one CTA per SM
+constexpr int UG_SMEM_SOLO = 120 * 1024;       // a request of at least this much keeps a second CTA of the kernel off the SM
 constexpr int UG_MAX_STAGES = 6;               // per stream
 
 __device__ unsigned int g_ug_timeouts;
@@ -226,11 +226,10 @@ ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ 
             load_w(sring + i * stage_bytes, kb_lo + strm + UG_NS * i, fb);
         }
     }
-    pdl_wait();   // the tokens are the predecessor's output; tensor memory may only be claimed once that grid is gone
-    if (is_prod && lane == 0) {
-        for (uint32_t i = 0; i < pre; i++) load_x(sring + i * stage_bytes + w_bytes, kb_lo + strm + UG_NS * i, smem_u32(&bar_full[strm][i]));
-    }
-    __syncwarp();
+    // Tensor memory is claimed before the wait for the predecessor grid.  That is safe only because no two CTAs that use
+    // tensor memory can share an SM: every launch of this kernel takes more than half of an SM's shared memory (the host
+    // pads the request), and nothing else in the library allocates tensor memory.  (A CTA that held columns while waiting
+    // for a predecessor CTA on the same SM that still needed columns would deadlock.)
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)), "r"(P.tmem_cols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
@@ -239,6 +238,11 @@ ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = tmem_base_s;
+    pdl_wait();   // the tokens are the predecessor's output
+    if (is_prod && lane == 0) {
+        for (uint32_t i = 0; i < pre; i++) load_x(sring + i * stage_bytes + w_bytes, kb_lo + strm + UG_NS * i, smem_u32(&bar_full[strm][i]));
+    }
+    __syncwarp();
 
     if (is_prod) {
         // ---- producer, part 2: the remaining stages, each as soon as the MMAs that read its slot have completed
@@ -542,6 +546,7 @@ static bool ug_geometry(uint32_t mc, uint32_t n, uint32_t k, bool swiglu, const 
     if (stages < 1 || UG_NS * stages * stage < staging || UG_NS * g->passes * g->nt > 512) return false;
     g->stages = stages;
     g->smem = 1024 + (size_t)UG_NS * stages * stage + tail;
+    if (g->smem < (size_t)UG_SMEM_SOLO) g->smem = UG_SMEM_SOLO;   // never two of these CTAs on one SM (see the tensor-memory claim in the kernel)
     uint32_t cols = 32;
     while (cols < UG_NS * g->passes * g->nt) cols *= 2;
     g->tmem_cols = cols;
