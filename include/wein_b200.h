@@ -128,14 +128,20 @@ int32_t wein_b200_gdn_layer_lite(const void *proj, uint32_t ld, const void *conv
                                  const void *row_start, const void *row_count, const void *in_row, const void *out_base,
                                  uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps, float rms_eps, void *log,
                                  void *stream);
-/* gdn_layer / gdn_layer_lite in one entry: log may be null (state snapshots), kq_scratch may be null.  kq_scratch
- * [tokens, k_heads, 256] f32 (16-byte aligned, sized by the caller for every token row of the call) lets calls with at
- * least 296 (span, v-head) pairs compute k-hat / q-hat once per k-head in a launch of their own; results are identical. */
+/* gdn_layer / gdn_layer_lite in one entry: log may be null (state snapshots), kq_scratch may be null.  kq_scratch (f32,
+ * 16-byte aligned, tokens x v_heads x 388 words, sized by the caller for every token row of the call) lets calls with at
+ * least 296 (span, v-head) pairs -- and 16-byte aligned proj / state, ld a multiple of 8 -- run the large-grid kernel: a
+ * launch of its own makes the per-token operands (conv + SiLU, l2 norms, k-hat / q-hat, gates) once per span, and persistent
+ * CTAs stream the heads' states through shared memory one item ahead.  Results are identical; the scratch contents after
+ * the call are unspecified. */
 int32_t wein_b200_gdn_layer_ws(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log,
                                const void *dt_bias, const void *norm_w, void *state, uint32_t state_f32, void *out,
                                const void *row_start, const void *row_count, const void *in_row, const void *out_base,
                                uint32_t n_rows, uint32_t k_heads, uint32_t v_heads, float l2_eps, float rms_eps, void *log,
                                void *kq_scratch, void *stream);
+/* Copy waits of the large-grid layer kernel that ran into their time limit since the library was loaded (0 in a healthy
+ * run; a non-zero count means a launch's results were abandoned, not that a kernel hung).  Synchronises the device. */
+int32_t wein_b200_gdn_wait_timeouts(uint32_t *out);
 int32_t wein_b200_gdn_commit(const void *states, const void *logs, uint32_t n_layers, uint32_t state_f32, const void *row_start,
                              const void *row_count, const void *in_row, const void *out_base, const void *accept_len,
                              uint32_t n_rows, uint32_t v_heads, void *stream);

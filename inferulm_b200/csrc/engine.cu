@@ -53,7 +53,7 @@ struct wein_b200_engine {
     uint64_t bytes = 0;
     std::vector<void *> lin_state, conv_state, k_pool, v_pool;  // k/v pools: full layers then the MTP layer
     std::vector<float *> lin_log;      // per DeltaNet layer: update records of a round's positions (snapshot-lite verification)
-    float *gdn_kq = nullptr;           // k-hat / q-hat of a layer's tokens, [T, k_heads, 256]: scratch of the large-grid DeltaNet path
+    float *gdn_kq = nullptr;           // per-token operands of a DeltaNet layer (k-hat, q-hat, conv of v, gates): T x v_heads x 388 floats
     void **d_state_ptrs = nullptr;     // device copies of lin_state / lin_log for the one-launch commit
     float **d_log_ptrs = nullptr;
     // per-slot device state
@@ -357,7 +357,7 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
         TRY(dalloc(e, &c, (size_t)S * e->rows_per_slot * conv_row, ("conv_state:" + std::to_string(i)).c_str(), false));
         e->lin_state.push_back(p); e->conv_state.push_back(c);
     }
-    if (e->n_lin) TRY(dalloc(e, &e->gdn_kq, (size_t)T * cfg->lin_k_heads * 256, "gdn_kq", false));
+    if (e->n_lin) TRY(dalloc(e, &e->gdn_kq, (size_t)T * ((size_t)cfg->lin_v_heads * 388), "gdn_kq", false));
     if (e->P >= 3 && e->n_lin && !e->snapshots) {
         // from three positions per round on, a round logs its state updates instead of writing a snapshot per position
         for (uint32_t i = 0; i < e->n_lin; i++) {

@@ -19,6 +19,7 @@
 // Bit parity with the reference holds in the bf16-pool mode (state rounded on
 // every store, as the reference's pool); the f32-pool mode keeps the same tree
 // without that rounding.  Compiled with -fmad=false.
+#include <cuda.h>
 #include "common.cuh"
 #include "internal.h"
 
@@ -285,20 +286,20 @@ struct GdnLayerParams {
     const uint32_t *row_start, *row_count, *in_row, *out_base;
     uint32_t n_rows, k_heads, v_heads;
     float l2_eps, rms_eps;
-    float *kq;                 // null: this kernel derives k-hat / q-hat itself.  Else [tokens, k_heads, 256] f32 from gdn_qk_kernel
+    float *kq;                 // null: the layer kernel derives its per-token operands itself.  Else the scratch gdn_pre_kernel fills:
+                               // per token and v-head a record of 388 floats = k-hat | q-hat | conv + SiLU of v (bf16) | z (bf16) | decay, beta, 0, 0
     float *log;                // null: write a state snapshot per position.  Else [tokens, v_heads, GDN_LOG_W]: write only what a
                                // position did to the state (delta[128], k-hat[128], decay) and no state at all
 };
 #define GDN_LOG_W 264          // floats per (token, v-head) record: delta at 0, k-hat at 128, decay at 256; 1056 bytes, 16-byte aligned
 
-// Measured and dropped: the 128 v-rows of a head split over a cluster of 4 CTAs of 128 threads (gated-norm leaders exchanged
-// through distributed shared memory, bit-identical).  The recurrence gets faster, but every CTA repeats the q / k conv, l2
-// norms and k-hat / q-hat with a quarter of the threads, and those phases are half of the kernel: 2.78 vs 2.71 ms per round
-// at batch 1, 6.80 vs 6.33 ms at batch 32.
-// MINB = CTAs per SM the register budget is planned for: 2 for large grids (bandwidth: more bytes in flight per SM),
-// 1 for small ones (latency: no spills in the token loop)
+// Small grids (fewer CTAs than two per SM) and calls without a scratch: one CTA = (span, v-head) = 16 warps x 8 v-rows, lane l
+// holds the 4-wide k slice [4l, 4l+4) of each of its warp's rows, and the whole prologue (conv, norms, gates) is made by the
+// CTA's 512 threads.  The two ordered 32-term folds per token go through a shared-memory transpose; the four warps of a
+// group hand their partials to ONE warp, whose 32 lanes fold one row each, the folding duty rotating over the group.
+// MINB = CTAs per SM the register budget is planned for.
 template <bool F32, int MINB>
-__global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerParams P) {
+__global__ void __launch_bounds__(512, MINB) gdn_layer_small_kernel(const GdnLayerParams P) {
     PDL_ENTRY();
     constexpr int KD = 128, VD = 128, R = 8, WARPS = 16, MAXT = 8;
     __shared__ __align__(16) float T[WARPS][R][36];   // lane partials of kvm, then of o; row stride 36 words: float4 reads of 8 lanes hit disjoint banks
@@ -334,13 +335,7 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
         n_z[q2] = t < cnt ? P.proj[(size_t)(t0 + t) * P.ld + cd + h * VD + n_i] : (bf16_t)0;
     }
     // ---- conv + SiLU (reference.rs:476-506) and conv-state rows (reference.rs:511-562): one thread per channel
-    if (P.kq && tid < 2 * KD) {
-        // k-hat and q-hat of the span's tokens were made once per k-head by gdn_qk_kernel: stage them (256 floats per token)
-        for (uint32_t t = 0; t < cnt; t++) {
-            const float v = P.kq[((size_t)(t0 + t) * P.k_heads + kh) * 256 + tid];
-            if (tid < KD) kk_s[t][tid] = v; else qq_s[t][tid - KD] = v;
-        }
-    } else if (tid < 3 * KD) {
+    if (tid < 3 * KD) {
         const uint32_t part = tid / KD, i = tid % KD;
         const uint32_t ch = part == 0 ? kh * KD + i : (part == 1 ? keyd + kh * KD + i : 2 * keyd + h * VD + i);
         const bool owns_state = part == 2 || (h % group) == 0;   // q / k channels are shared by the v-heads of a k-head
@@ -380,7 +375,7 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
         }
     }
     __syncthreads();
-    if (!P.kq) {
+    {
     // ---- l2 norms of q and k (reference.rs:629-637): thread (t, which) sums 128 squares in order, two roundings per term
     if (tid < 2 * (int)cnt) {
         const bf16_t *src = (tid & 1) ? kc[tid >> 1] : qc[tid >> 1];
@@ -411,7 +406,7 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
         }
     }
     __syncthreads();
-    }   // !P.kq
+    }
     // The recurrence.  Warp w owns v-rows 8w .. 8w+7, lane l the k slice 4l .. 4l+3 of each.  A row's kvm and o are sums of 32
     // lane partials in ascending lane order (the reference's two-level tree, reference.rs:644-678): a chain of 32 dependent
     // additions that one thread must make.  The four warps of a group (32 rows) therefore hand their partials to ONE warp,
@@ -531,24 +526,339 @@ __global__ void __launch_bounds__(512, MINB) gdn_layer_kernel(const GdnLayerPara
     }
 }
 
-// k-hat and q-hat once per (span, k-head) instead of once per v-head: conv + SiLU of the head's q and k channels with their
-// conv-state rows, the two l2 norms and the scaling, for every token of the span.  Used in front of gdn_layer_kernel when
-// the grid is large: there the layer kernel is bound by the instructions and serial chains of its CTAs, and this part is
-// repeated by the v-heads that share a k-head.  Output kq [tokens, k_heads, 256] f32: k-hat then q-hat.  Same arithmetic.
-__global__ void __launch_bounds__(256) gdn_qk_kernel(const GdnLayerParams P) {
+
+// Large grids.  Work item = (span, v-head); a CTA of 128 threads takes items blockIdx.x, blockIdx.x + gridDim.x, ... and a
+// thread owns a 2 x 64 block of the head's state in registers for the whole span: v-rows 32w + 16j + g (j = 0, 1) x
+// k-columns 64q .. 64q+63, with g = lane & 15 and q = lane >> 4.  A row's kvm and o are, in the reference, sums of 32 slice
+// partials (4 fused terms each) folded in ascending slice order (reference.rs:644-678).  Here a thread makes the 16 slice
+// partials of its half for each of its 2 rows, and the fold walks the row's two owners -- lanes 16 apart in ONE warp -- with
+// one shuffle in between.  The token loop has no barrier and no shared-memory exchange; k-hat / q-hat are read from shared
+// memory once per 2 rows, and the fold of a token's o runs beside the next token's first half (they are independent).
+//
+// Everything an item reads arrives by copies that complete on one mbarrier: the state as four tensor-map copies of 128 rows x
+// 128 bytes under the 128-byte swizzle (the per-thread reads -- lanes one row apart -- are then free of bank conflicts),
+// and per token ONE bulk copy of a 1552-byte record that gdn_pre_kernel made once per span: k-hat | q-hat, conv + SiLU of
+// v, z, the gates (128 threads that hold a head's state are too few to make them quickly).  One thread issues them.  As
+// soon as an item's state has moved into registers the copies of the CTA's NEXT item are issued, so they land while this
+// item's tokens are processed: the HBM read of the state and every dependent load latency leave the critical path.  Every
+// wait is bounded by a clock; a wait that gives up counts itself, and the CTA leaves after a delay.
+//
+// Measured and dropped: the small-grid kernel above on large grids -- 47.7 us per layer at 32 chains x 4 positions: bound by
+// the chain of barriers and 32 dependent additions per fold, not by memory or issue slots; 4 x 32 blocks per thread (four fold
+// passes of 8 additions: three quarters of them wasted); a whole row per thread (the broadcast reads of k-hat / q-hat then
+// bound the loop); this kernel with one item per CTA and its own prologue (the serial load latencies and the prologue on
+// 128 threads cost more than the recurrence); the state as one bulk copy per row into padded rows (128 copy instructions
+// per item take 6,000 cycles to issue); the head split over a cluster of 4 CTAs.
+template <bool F32> struct GdnStage {
+    static constexpr uint32_t ROWB = F32 ? 512u : 256u;   // bytes of a state row of one head
+    static constexpr uint32_t BOXES = ROWB / 128u;        // tensor-map boxes of 128 rows x 128 bytes
+    static constexpr uint32_t BYTES = 128u * ROWB;
+};
+// per-token record of an item (scratch and shared memory): k-hat | q-hat (1024 B), conv + SiLU of v (256 B), z (256 B), decay | beta | 0 | 0
+#define GDN_REC_VC 1024u
+#define GDN_REC_Z 1280u
+#define GDN_REC_GATE 1536u
+#define GDN_REC_BYTES 1552u
+#define GDN_OPS_BYTES (8u * GDN_REC_BYTES)
+#define GDN_TAIL_BYTES (4096u + 256u)   // core outputs [8][128] f32, norm leaders / inverse norms
+template <bool F32>
+static constexpr uint32_t gdn_layer_smem() { return 1024u + GdnStage<F32>::BYTES + 2u * GDN_OPS_BYTES + GDN_TAIL_BYTES; }   // 1024: alignment slack
+#define GDN_WAIT_CYCLES 2000000000ll   // about a second
+__device__ unsigned int g_gdn_timeouts;   // bounded waits that gave up (that launch's results are then undefined, nothing hangs)
+
+// floats of scratch per token: one record per v-head
+__host__ __device__ __forceinline__ uint32_t gdn_pre_words(uint32_t v_heads) { return v_heads * (GDN_REC_BYTES / 4u); }
+
+// This thread's half of state row r out of the staging area: box b holds bytes [128 b, 128 b + 128) of every row, 16-byte
+// chunk c of row r at r * 128 + ((c ^ (r & 7)) << 4).
+template <bool F32>
+__device__ __forceinline__ void gdn_block_from(const unsigned char *stage, uint32_t r, uint32_t q, float (&S)[64]) {
+    const uint32_t sw = r & 7;
+    if (F32) {
+#pragma unroll
+        for (uint32_t cc = 0; cc < 16; cc++) {
+            const float4 v = *reinterpret_cast<const float4 *>(stage + (2 * q + (cc >> 3)) * 16384 + r * 128 + (((cc & 7) ^ sw) << 4));
+            S[4 * cc] = v.x; S[4 * cc + 1] = v.y; S[4 * cc + 2] = v.z; S[4 * cc + 3] = v.w;
+        }
+    } else {
+#pragma unroll
+        for (uint32_t c2 = 0; c2 < 8; c2++) {
+            const uint4 raw = *reinterpret_cast<const uint4 *>(stage + q * 16384 + r * 128 + ((c2 ^ sw) << 4));
+            const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                S[8 * c2 + 2 * u] = __uint_as_float(wv[u] << 16);
+                S[8 * c2 + 2 * u + 1] = __uint_as_float(wv[u] & 0xffff0000u);
+            }
+        }
+    }
+}
+__device__ __forceinline__ void gdn_bulk(void *dst_smem, const void *src, uint32_t bytes, uint32_t bar_a) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(src), "r"(bytes), "r"(bar_a) : "memory");
+}
+__device__ __forceinline__ void gdn_tensor_2d(void *dst_smem, const CUtensorMap *tm, uint32_t x, uint32_t y, uint32_t bar_a) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+                 ::"r"((uint32_t)__cvta_generic_to_shared(dst_smem)), "l"(tm), "r"(x), "r"(y), "r"(bar_a) : "memory");
+}
+struct GdnItem { uint32_t t0, cnt, h, in_row, base; };
+
+template <bool F32>
+__global__ void __launch_bounds__(128, 2) gdn_layer_kernel(const __grid_constant__ CUtensorMap tm_state, const GdnLayerParams P) {
+    constexpr int KD = 128, VD = 128, MAXT = 8;
+    constexpr uint32_t ROWB = GdnStage<F32>::ROWB;
+    constexpr size_t EB = F32 ? 4 : 2;   // bytes per state word
+    extern __shared__ unsigned char gsm_raw[];
+    unsigned char *stage = reinterpret_cast<unsigned char *>(((uintptr_t)gsm_raw + 1023) & ~(uintptr_t)1023);   // swizzled boxes: 1024-byte aligned
+    unsigned char *ops0 = stage + GdnStage<F32>::BYTES;
+    float (*o_s)[VD] = reinterpret_cast<float (*)[VD]>(ops0 + 2 * GDN_OPS_BYTES);
+    float (*red_s)[4] = reinterpret_cast<float (*)[4]>(ops0 + 2 * GDN_OPS_BYTES + 4096);   // [8][4]
+    float *inv_s = reinterpret_cast<float *>(ops0 + 2 * GDN_OPS_BYTES + 4096 + 128);        // [8]
+    __shared__ __align__(8) unsigned long long bar[2];
+    __shared__ volatile uint32_t abort_s;
+    const unsigned full = 0xffffffffu;
+    const int tid = threadIdx.x, lane = tid & 31, w = tid >> 5;
+    const size_t head_elems = (size_t)VD * KD, row_elems = (size_t)P.v_heads * head_elems;
+    const uint32_t W = gdn_pre_words(P.v_heads);
+    const uint32_t n_items = P.n_rows * P.v_heads;
+    const uint32_t g16 = lane & 15, q = lane >> 4;
+    const uint32_t row_a = w * 32 + g16, row_b = row_a + 16;   // this thread's two v-rows
+    const float n_wv = P.norm_w[tid];                          // a weight: no produced data
+    pdl_trigger();
+    if (tid == 0) {
+        asm volatile("prefetch.tensormap [%0];" ::"l"(&tm_state) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&bar[0])) : "memory");
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"((uint32_t)__cvta_generic_to_shared(&bar[1])) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        abort_s = 0;
+    }
+    pdl_wait();
+    auto item_of = [&](uint32_t idx) {
+        GdnItem it;
+        it.cnt = 0; it.t0 = 0; it.h = 0; it.in_row = 0; it.base = 0;
+        if (idx < n_items) {
+            const uint32_t r = idx / P.v_heads;
+            it.h = idx % P.v_heads;
+            it.t0 = P.row_start[r];
+            it.cnt = min(P.row_count[r], (uint32_t)MAXT);
+            it.in_row = P.in_row[r];
+            it.base = P.out_base[r];
+        }
+        return it;
+    };
+    // thread 0 announces the bytes of an item on its barrier and issues the item's copies
+    auto issue = [&](const GdnItem &it, uint32_t b) {
+        if (tid != 0 || !it.cnt) return;
+        const uint32_t bar_a = (uint32_t)__cvta_generic_to_shared(&bar[b]);
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar_a), "r"(128u * ROWB + it.cnt * GDN_REC_BYTES) : "memory");
+        const uint32_t y = (it.in_row * P.v_heads + it.h) * 128u;
+#pragma unroll
+        for (uint32_t bx = 0; bx < GdnStage<F32>::BOXES; bx++) gdn_tensor_2d(stage + bx * 16384, &tm_state, bx * (F32 ? 32u : 64u), y, bar_a);
+        unsigned char *ob = ops0 + b * GDN_OPS_BYTES;
+        for (uint32_t t = 0; t < it.cnt; t++)
+            gdn_bulk(ob + t * GDN_REC_BYTES, P.kq + (size_t)(it.t0 + t) * W + it.h * (GDN_REC_BYTES / 4u), GDN_REC_BYTES, bar_a);
+    };
+    // ascending fold of a row's 32 slice partials: the owner of the upper half adds its 16 on top of the lower half's sum
+    auto fold = [&](const float (&p)[2][16], float (&res)[2]) {
+        float c[2] = {0.0f, 0.0f};
+#pragma unroll
+        for (int cc = 0; cc < 16; cc++)
+#pragma unroll
+            for (int j = 0; j < 2; j++) c[j] = __fadd_rn(p[j][cc], c[j]);
+        float d[2];
+#pragma unroll
+        for (int j = 0; j < 2; j++) d[j] = __shfl_up_sync(full, c[j], 16);
+#pragma unroll
+        for (int cc = 0; cc < 16; cc++)
+#pragma unroll
+            for (int j = 0; j < 2; j++) d[j] = __fadd_rn(p[j][cc], d[j]);
+#pragma unroll
+        for (int j = 0; j < 2; j++) res[j] = d[j];   // complete in the lanes of the upper half (q == 1)
+    };
+    uint32_t idx = blockIdx.x, b = 0, ph0 = 0, ph1 = 0;
+    GdnItem cur = item_of(idx), nxt = item_of(idx + gridDim.x);
+    issue(cur, 0);     // (thread 0 initialised the barriers itself)
+    __syncthreads();   // barriers initialised before anyone polls them
+    for (; idx < n_items; idx += gridDim.x, b ^= 1) {
+        GdnItem after;
+        after.cnt = 0; after.t0 = 0; after.h = 0; after.in_row = 0; after.base = 0;
+        const unsigned char *ob = ops0 + b * GDN_OPS_BYTES;
+        float S[2][64];
+        if (cur.cnt) {
+            // ---- the item's copies have landed: this thread's blocks of the state move into registers
+            const uint32_t bar_a = (uint32_t)__cvta_generic_to_shared(&bar[b]), parity = b ? ph1 : ph0;
+            if (b) ph1 ^= 1; else ph0 ^= 1;
+            const long long c0 = clock64();
+            for (;;) {
+                uint32_t ok;
+                asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                             : "=r"(ok) : "r"(bar_a), "r"(parity) : "memory");
+                if (ok || abort_s) break;
+                if (clock64() - c0 > GDN_WAIT_CYCLES) { abort_s = 1; atomicAdd(&g_gdn_timeouts, 1u); break; }
+            }
+            gdn_block_from<F32>(stage, row_a, q, S[0]);
+            gdn_block_from<F32>(stage, row_b, q, S[1]);
+        }
+        __syncthreads();   // the staging area and the other operand buffer are free
+        if (abort_s) { __nanosleep(1000000); return; }   // a copy did not arrive: leave, after a delay that outlasts what is in flight
+        issue(nxt, b ^ 1);
+        if (cur.cnt) {
+            const uint32_t cnt = cur.cnt, t0 = cur.t0, h = cur.h;
+            // ---- the recurrence (reference.rs:639-690)
+            float p2[2][16];
+#pragma unroll
+            for (int j = 0; j < 2; j++)
+#pragma unroll
+                for (int cc = 0; cc < 16; cc++) p2[j][cc] = 0.0f;
+#pragma unroll 1
+            for (uint32_t i = 0; i < cnt; i++) {
+                const unsigned char *rec = ob + i * GDN_REC_BYTES;
+                const float *kk_i = reinterpret_cast<const float *>(rec), *qq_i = kk_i + KD;
+                const bf16_t *vc_i = reinterpret_cast<const bf16_t *>(rec + GDN_REC_VC);
+                const float decay = reinterpret_cast<const float *>(rec + GDN_REC_GATE)[0];
+                const float beta = reinterpret_cast<const float *>(rec + GDN_REC_GATE)[1];
+                float p1[2][16], kvm[2], o_prev[2], delta[2];
+#pragma unroll
+                for (int cc = 0; cc < 16; cc++) {
+                    const float4 k4 = *reinterpret_cast<const float4 *>(&kk_i[(16 * q + cc) * 4]);
+                    const float kk[4] = {k4.x, k4.y, k4.z, k4.w};
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        float pj = 0.0f;
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            S[j][cc * 4 + u] = __fmul_rn(S[j][cc * 4 + u], decay);
+                            pj = fmaf(S[j][cc * 4 + u], kk[u], pj);
+                        }
+                        p1[j][cc] = pj;
+                    }
+                }
+                fold(p2, o_prev);   // o of the previous token: independent of the lines above, the scheduler runs them side by side
+                if (i > 0 && q == 1) {
+                    // the core output is stored as bf16 by the reference before the norm reads it
+                    o_s[i - 1][row_a] = rbf(o_prev[0]);
+                    o_s[i - 1][row_b] = rbf(o_prev[1]);
+                }
+                fold(p1, kvm);
+#pragma unroll
+                for (int j = 0; j < 2; j++) {
+                    const float d = __fmul_rn(__fsub_rn(bf2f(vc_i[j ? row_b : row_a]), kvm[j]), beta);
+                    delta[j] = __shfl_sync(full, d, 16 + g16);
+                }
+#pragma unroll
+                for (int cc = 0; cc < 16; cc++) {
+                    const float4 k4 = *reinterpret_cast<const float4 *>(&kk_i[(16 * q + cc) * 4]), q4 = *reinterpret_cast<const float4 *>(&qq_i[(16 * q + cc) * 4]);
+                    const float kk[4] = {k4.x, k4.y, k4.z, k4.w}, qq[4] = {q4.x, q4.y, q4.z, q4.w};
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        float pj = 0.0f;
+#pragma unroll
+                        for (int u = 0; u < 4; u++) {
+                            float sv = fmaf(kk[u], delta[j], S[j][cc * 4 + u]);
+                            if (!F32) sv = rbf(sv);
+                            S[j][cc * 4 + u] = sv;
+                            pj = fmaf(sv, qq[u], pj);
+                        }
+                        p2[j][cc] = pj;
+                    }
+                }
+                if (P.log) {
+                    float *lg = P.log + ((size_t)(t0 + i) * P.v_heads + h) * GDN_LOG_W;
+                    if (q == 1) { lg[row_a] = delta[0]; lg[row_b] = delta[1]; }
+                    lg[128 + tid] = kk_i[tid];
+                    if (tid == 0) lg[256] = decay;
+                } else {
+                    // snapshot of position i, 16 bytes per lane
+                    unsigned char *st_out = (unsigned char *)P.state + (((size_t)cur.base + i) * row_elems + (size_t)h * head_elems) * EB;
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        unsigned char *rp = st_out + (size_t)(j ? row_b : row_a) * ROWB + q * (ROWB / 2);
+                        if (F32) {
+#pragma unroll
+                            for (int cc = 0; cc < 16; cc++)
+                                *reinterpret_cast<float4 *>(rp + cc * 16) = make_float4(S[j][4 * cc], S[j][4 * cc + 1], S[j][4 * cc + 2], S[j][4 * cc + 3]);
+                        } else {   // values are already bf16-representable: narrowing is exact
+#pragma unroll
+                            for (int c2 = 0; c2 < 8; c2++) {
+                                uint32_t wv[4];
+#pragma unroll
+                                for (int u = 0; u < 4; u++)
+                                    wv[u] = (__float_as_uint(S[j][8 * c2 + 2 * u]) >> 16) | (__float_as_uint(S[j][8 * c2 + 2 * u + 1]) & 0xffff0000u);
+                                *reinterpret_cast<uint4 *>(rp + c2 * 16) = make_uint4(wv[0], wv[1], wv[2], wv[3]);
+                            }
+                        }
+                    }
+                }
+            }
+            after = item_of(idx + 2 * gridDim.x);   // tables of the item after next (the state registers are free now)
+            {
+                float o_last[2];
+                fold(p2, o_last);
+                if (q == 1) {
+                    o_s[cnt - 1][row_a] = rbf(o_last[0]);
+                    o_s[cnt - 1][row_b] = rbf(o_last[1]);
+                }
+            }
+            __syncthreads();
+            // ---- gated RMSNorm over the head (reference.rs:699-713), thread = row: every token's sum of squares by the block
+            //      tree (lanes pairwise downwards, then the four warp leaders as (w0 + w2) + (w1 + w3)); thread t then makes
+            //      token t's inverse norm once for all rows
+            float ov[MAXT];
+#pragma unroll
+            for (int t = 0; t < MAXT; t++) {
+                if ((uint32_t)t >= cnt) break;
+                ov[t] = o_s[t][tid];
+                float s2 = fmaf(ov[t], ov[t], 0.0f);
+#pragma unroll
+                for (int off = 16; off >= 1; off >>= 1) {
+                    float o2 = __shfl_down_sync(full, s2, off);
+                    if (lane + off < 32) s2 = __fadd_rn(s2, o2);
+                }
+                if (lane == 0) red_s[t][w] = s2;
+            }
+            __syncthreads();
+            if ((uint32_t)tid < cnt) {
+                const float total = __fadd_rn(__fadd_rn(red_s[tid][0], red_s[tid][2]), __fadd_rn(red_s[tid][1], red_s[tid][3]));
+                inv_s[tid] = 1.0f / sqrtf(total / (float)VD + P.rms_eps);
+            }
+            __syncthreads();
+#pragma unroll
+            for (int t = 0; t < MAXT; t++) {
+                if ((uint32_t)t >= cnt) break;
+                const float xw = n_wv * rbf(ov[t] * inv_s[t]);
+                const float zv = bf2f(reinterpret_cast<const bf16_t *>(ob + t * GDN_REC_BYTES + GDN_REC_Z)[tid]);
+                P.out[((size_t)(t0 + t) * P.v_heads + h) * VD + tid] = f2bf(xw * (zv * (1.0f / (1.0f + expf_ref(-zv)))));
+            }
+        }
+        if (!cur.cnt) after = item_of(idx + 2 * gridDim.x);
+        cur = nxt;
+        nxt = after;
+    }
+}
+
+// Everything of a DeltaNet layer that is per token and not per state row, once per span instead of once per v-head CTA:
+// unit < k_heads: conv + SiLU of that k-head's q and k channels with their conv-state rows, the two l2 norms and the
+// scaling (k-hat, q-hat); unit >= k_heads: conv + SiLU and conv-state rows of two v-heads' channels, their z and their gates.
+// Output: per token one 1552-byte record per v-head (k-hat | q-hat | conv of v | z | decay, beta), gdn_pre_words() floats.  Same arithmetic as the small-grid kernel's own prologue.
+__global__ void __launch_bounds__(256) gdn_pre_kernel(const GdnLayerParams P) {
     PDL_ENTRY();
     constexpr int KD = 128, VD = 128, MAXT = 8;
     __shared__ __align__(16) bf16_t qk[2][MAXT][KD];   // [0] q, [1] k
     __shared__ float inv_s[MAXT][2];
     const int tid = threadIdx.x;
-    const uint32_t r = blockIdx.x / P.k_heads, kh = blockIdx.x % P.k_heads;
+    const uint32_t units = P.k_heads + (P.v_heads + 1) / 2;
+    const uint32_t r = blockIdx.x / units, unit = blockIdx.x % units;
     const uint32_t t0 = P.row_start[r], cnt = min(P.row_count[r], (uint32_t)MAXT);
     if (cnt == 0) return;
     const size_t in_row = P.in_row[r], base = P.out_base[r];
     const uint32_t keyd = P.k_heads * KD, vald = P.v_heads * VD, cd = 2 * keyd + vald;
+    const uint32_t W = gdn_pre_words(P.v_heads), RW = GDN_REC_BYTES / 4u, group = P.v_heads / P.k_heads;
+    const bool is_v = unit >= P.k_heads;
+    const uint32_t part = tid / KD, i = tid % KD;
+    const uint32_t kh = unit, h = 2 * (unit - P.k_heads) + part;
+    if (is_v && h >= P.v_heads) return;
     {
-        const uint32_t part = tid / KD, i = tid % KD;
-        const uint32_t ch = part == 0 ? kh * KD + i : keyd + kh * KD + i;
+        const uint32_t ch = is_v ? 2 * keyd + h * VD + i : (part == 0 ? kh * KD + i : keyd + kh * KD + i);
         const bf16_t *sp = P.conv_state + ((size_t)in_row * cd + ch) * 3;
         bf16_t w0 = sp[0], w1 = sp[1], w2 = sp[2];
         const float k0 = bf2f(P.conv_w[(size_t)ch * 4 + 0]), k1 = bf2f(P.conv_w[(size_t)ch * 4 + 1]),
@@ -565,11 +875,29 @@ __global__ void __launch_bounds__(256) gdn_qk_kernel(const GdnLayerParams P) {
             acc = __fadd_rn(__fmul_rn(bf2f(w1), k1), acc);
             acc = __fadd_rn(__fmul_rn(bf2f(w2), k2), acc);
             acc = __fadd_rn(__fmul_rn(bf2f(xv), k3), acc);
-            qk[part][t][i] = f2bf(silu_ref(rbf(acc)));
+            const bf16_t y = f2bf(silu_ref(rbf(acc)));
+            if (is_v) {
+                float *rec = P.kq + (size_t)(t0 + t) * W + h * RW;
+                reinterpret_cast<bf16_t *>(rec + GDN_REC_VC / 4u)[i] = y;
+                reinterpret_cast<bf16_t *>(rec + GDN_REC_Z / 4u)[i] = P.proj[(size_t)(t0 + t) * P.ld + cd + h * VD + i];
+            }
+            else qk[part][t][i] = y;
             w0 = w1; w1 = w2; w2 = xv;
             bf16_t *dp = P.conv_state + ((size_t)(base + t) * cd + ch) * 3;
             dp[0] = w0; dp[1] = w1; dp[2] = w2;
         }
+    }
+    if (is_v) {
+        if (i < cnt) {
+            // gates (reference.rs:624-626), one thread per (token, head)
+            const size_t g = t0 + i;
+            const float av = bf2f(P.proj[g * P.ld + cd + vald + h]), bv = bf2f(P.proj[g * P.ld + cd + vald + P.v_heads + h]);
+            const float big_a = expf_ref(P.a_log[h]);
+            float *gp = P.kq + g * W + h * RW + GDN_REC_GATE / 4u;
+            gp[0] = expf_ref(__fsub_rn(0.0f, __fmul_rn(big_a, softplus_ref(__fadd_rn(av, bf2f(P.dt_bias[h]))))));
+            gp[1] = rbf(sigmoid_ref(bv));
+        }
+        return;
     }
     __syncthreads();
     if (tid < 2 * (int)cnt) {
@@ -597,8 +925,28 @@ __global__ void __launch_bounds__(256) gdn_qk_kernel(const GdnLayerParams P) {
         float v;
         if (j < (uint32_t)KD) v = __fmul_rn(bf2f(qk[1][t][j]), inv_s[t][1]);
         else v = __fdiv_rn(__fmul_rn(bf2f(qk[0][t][j - KD]), inv_s[t][0]), kd_sqrt);
-        P.kq[((size_t)(t0 + t) * P.k_heads + kh) * 256 + j] = v;
+        for (uint32_t hh = kh * group; hh < (kh + 1) * group; hh++) P.kq[(size_t)(t0 + t) * W + hh * RW + j] = v;   // a copy per v-head of the group
     }
+}
+
+// The shared-memory opt-in is a per-device function attribute: one flag per device ordinal, set once (writing it twice from
+// two threads stores the same value).
+static bool g_gdn_ready[64];
+static int g_gdn_sms[64];
+static int32_t gdn_layer_prepare(int *sms) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { wb_set_error("gdn_layer: cudaGetDevice failed or device ordinal >= 64"); return WB_ERR_CUDA; }
+    if (!g_gdn_ready[dev]) {
+        int n = 0;
+        cudaError_t e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gdn_layer_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gdn_layer_smem<true>());
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gdn_layer_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gdn_layer_smem<false>());
+        if (e != cudaSuccess || n <= 0) { wb_set_error("gdn_layer: cannot reserve shared memory: %s", cudaGetErrorString(e)); return WB_ERR_CUDA; }
+        g_gdn_sms[dev] = n;
+        g_gdn_ready[dev] = true;
+    }
+    *sms = g_gdn_sms[dev];
+    return WB_OK;
 }
 
 int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *conv_state, const void *a_log, const void *dt_bias,
@@ -616,22 +964,40 @@ int32_t wb_gdn_layer(const void *proj, uint32_t ld, const void *conv_w, void *co
     p.in_row = (const uint32_t *)in_row; p.out_base = (const uint32_t *)out_base;
     p.n_rows = n_rows; p.k_heads = k_heads; p.v_heads = v_heads; p.l2_eps = l2_eps; p.rms_eps = rms_eps; p.log = (float *)log;
     WB_CHECK_ARG(((uintptr_t)log & 15u) == 0, "gdn_layer: the update log must be 16-byte aligned");
-    const bool big = (uint64_t)n_rows * v_heads >= 296;
-    if (big && kq_scratch) {
-        // large grid: k-hat / q-hat once per k-head in a launch of their own
-        WB_CHECK_ARG(((uintptr_t)kq_scratch & 15u) == 0, "gdn_layer: the k-hat / q-hat scratch must be 16-byte aligned");
+    const uint32_t items = n_rows * v_heads;
+    // the persistent kernel needs a scratch, more work than two CTAs per SM of the small-grid kernel cover, and operands its
+    // 16-byte bulk copies can address
+    const bool large = kq_scratch && items >= 296 && (((uintptr_t)state | (uintptr_t)proj | (uintptr_t)kq_scratch) & 15u) == 0 && ld % 8 == 0;
+    if (large) {
+        int sms = 0;
+        if (int32_t rc = gdn_layer_prepare(&sms)) return rc;
         p.kq = (float *)kq_scratch;
-        WB_LAUNCH((gdn_qk_kernel), n_rows * k_heads, 256, 0, st, p);
+        WB_LAUNCH((gdn_pre_kernel), n_rows * (k_heads + (v_heads + 1) / 2), 256, 0, st, p);
         WB_LAUNCH_CHECK();
-    }
-    if (state_f32) {
-        if (big) WB_LAUNCH((gdn_layer_kernel<true, 2>), n_rows * v_heads, 512, 0, st, p);
-        else WB_LAUNCH((gdn_layer_kernel<true, 1>), n_rows * v_heads, 512, 0, st, p);
+        // the state pool as rows of 128 words; its row count is not known here: the bound is nominal, the row indices come from
+        // the caller's tables as for every other access to the pool
+        alignas(64) CUtensorMap tm;
+        if (int32_t rc = wb_tensor_map_2d(&tm, state_f32 != 0, state, 128, 0x7fffff00ull, state_f32 ? 512 : 256, state_f32 ? 32 : 64, 128)) return rc;
+        const uint32_t grid = items < 2u * (uint32_t)sms ? items : 2u * (uint32_t)sms;
+        if (state_f32) WB_LAUNCH((gdn_layer_kernel<true>), grid, 128, gdn_layer_smem<true>(), st, tm, p);
+        else WB_LAUNCH((gdn_layer_kernel<false>), grid, 128, gdn_layer_smem<false>(), st, tm, p);
+    } else if (state_f32) {
+        if (items >= 296) WB_LAUNCH((gdn_layer_small_kernel<true, 2>), items, 512, 0, st, p);
+        else WB_LAUNCH((gdn_layer_small_kernel<true, 1>), items, 512, 0, st, p);
     } else {
-        if (big) WB_LAUNCH((gdn_layer_kernel<false, 2>), n_rows * v_heads, 512, 0, st, p);
-        else WB_LAUNCH((gdn_layer_kernel<false, 1>), n_rows * v_heads, 512, 0, st, p);
+        if (items >= 296) WB_LAUNCH((gdn_layer_small_kernel<false, 2>), items, 512, 0, st, p);
+        else WB_LAUNCH((gdn_layer_small_kernel<false, 1>), items, 512, 0, st, p);
     }
     WB_LAUNCH_CHECK();
+    return WB_OK;
+}
+
+// Barrier waits of the large-grid layer kernel that gave up since the library was loaded (0 in a healthy run); synchronises.
+extern "C" int32_t wein_b200_gdn_wait_timeouts(uint32_t *out) {
+    unsigned int v = 0;
+    cudaError_t e = cudaMemcpyFromSymbol(&v, g_gdn_timeouts, sizeof v);
+    if (e != cudaSuccess) { wb_set_error("gdn_wait_timeouts: %s", cudaGetErrorString(e)); return WB_ERR_CUDA; }
+    if (out) *out = v;
     return WB_OK;
 }
 

@@ -517,6 +517,23 @@ int32_t wb_ugemm_init() {
     return WB_OK;
 }
 
+// A 2-d tensor map for other kernels of the library: `rows` rows of `inner` elements (4-byte when f32, else 2-byte), rows
+// row_bytes apart, boxes of box_inner x box_rows elements (box_inner elements = 128 bytes), 128-byte swizzle.  `tm` points
+// at a CUtensorMap (128 bytes, 64-byte aligned).
+int32_t wb_tensor_map_2d(void *tm, bool f32, const void *base, uint64_t inner, uint64_t rows, uint64_t row_bytes, uint32_t box_inner, uint32_t box_rows) {
+    if (int32_t rc = wb_ugemm_init()) return rc;
+    const cuuint64_t dims[2] = {inner, rows};
+    const cuuint64_t strides[1] = {row_bytes};
+    const cuuint32_t box[2] = {box_inner, box_rows};
+    const cuuint32_t ones[2] = {1, 1};
+    CUresult r = g_ug_encode((CUtensorMap *)tm, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void *>(base), dims,
+                             strides, box, ones, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { wb_set_error("cuTensorMapEncodeTiled failed (%d)", (int)r); return WB_ERR_CUDA; }
+    return WB_OK;
+}
+
+
 // Launch geometry of one chunk of mc <= 256 token rows.
 struct UgGeom { uint32_t nt, tiles, nkb, ksplit, cw, passes, x_rows, x_bytes, stages, tmem_cols; size_t smem; };
 static bool ug_geometry(uint32_t mc, uint32_t n, uint32_t k, bool swiglu, const UgDevice &d, UgGeom *g) {

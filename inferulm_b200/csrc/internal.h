@@ -10,6 +10,8 @@ int32_t wb_gemm_swiglu(const void *a, const void *w_gate_up, void *out, uint32_t
                        uint32_t ldc, void *scratch, uint64_t scratch_bytes, uint32_t path, cudaStream_t st);
 int32_t wb_ugemm(const void *a, const void *w, void *c, uint32_t m, uint32_t n, uint32_t k, uint32_t lda, uint32_t ldc, bool swiglu,
                  cudaStream_t st);  // tensor-memory GEMM (gemm_umma.cu), arguments already validated
+int32_t wb_tensor_map_2d(void *tm, bool f32, const void *base, uint64_t inner, uint64_t rows, uint64_t row_bytes, uint32_t box_inner,
+                         uint32_t box_rows);   // 128-byte-swizzled 2-d map; tm -> CUtensorMap
 int32_t wb_ugemm_init();  // driver entry point and shared-memory opt-in of the current device, outside any stream capture
 int32_t wb_gemm_init();
 int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, const void *block_table, const void *seq_ids,

@@ -117,7 +117,7 @@ def case_gdn_lite(reps, B=32, P=4, n_layers=2, accept=3):
     states = [torch.randn(rows * VH * 128 * 128, device="cuda") * 0.1 for _ in range(n_layers)]
     convs = [torch.randn(rows * CD * 3, device="cuda").to(torch.bfloat16) for _ in range(n_layers)]
     logs = [torch.zeros(T * VH * 264, device="cuda") for _ in range(n_layers)]
-    kq = torch.zeros(T * KH * 256, device="cuda")
+    kq = torch.zeros(T * VH * 388, device="cuda")
     out = torch.empty(T * VALD, dtype=torch.bfloat16, device="cuda")
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
     rs, rc = i32([b * P for b in range(B)]), i32([P] * B)
@@ -130,7 +130,7 @@ def case_gdn_lite(reps, B=32, P=4, n_layers=2, accept=3):
     sec_commit = _time(lambda i: ops.gdn_commit(sp, lp, 1, rs, rc, ir, ob, acc, B, VH), 1, reps)
     byt_layer = B * VH * 65536 + B * P * VH * 1056 + B * (1 + P) * CD * 3 * 2 + T * LD * 2 + T * VALD * 2
     byt_commit = n_layers * B * VH * (2 * 65536 + (accept + 1) * 1056)
-    return dict(kernel="gdn_qk_kernel + gdn_layer_kernel<f32> (log mode); gdn_commit_kernel<f32>", batch=B, positions=P, layer_us=sec_layer * 1e6,
+    return dict(kernel="gdn_pre_kernel + gdn_layer_kernel<f32> (log mode); gdn_commit_kernel<f32>", batch=B, positions=P, layer_us=sec_layer * 1e6,
                 layer_bytes=byt_layer, layer_gbs=byt_layer / sec_layer / 1e9, commit_layers=n_layers, commit_us=sec_commit * 1e6,
                 commit_bytes=byt_commit, commit_gbs=byt_commit / sec_commit / 1e9)
 

@@ -214,11 +214,20 @@ def gdn_layer_lite(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, 
 
 def gdn_layer_ws(proj, ld, conv_w, conv_state, a_log, dt_bias, norm_w, state, state_f32, out, row_start, row_count, in_row, out_base,
                  n_rows, k_heads, v_heads, l2_eps, rms_eps, log=None, kq_scratch=None):
-    """General form of gdn_layer: optional update log, optional k-hat / q-hat scratch [tokens, k_heads, 256] f32."""
+    """General form of gdn_layer: optional update log, optional scratch of tokens x v_heads x 388 f32 words
+    for the per-token operands (used from 296 (span, v-head) pairs on)."""
     check(load().wein_b200_gdn_layer_ws(_ptr(proj), U32(ld), _ptr(conv_w), _ptr(conv_state), _ptr(a_log), _ptr(dt_bias), _ptr(norm_w),
                                         _ptr(state), U32(state_f32), _ptr(out), _ptr(row_start), _ptr(row_count), _ptr(in_row),
                                         _ptr(out_base), U32(n_rows), U32(k_heads), U32(v_heads), F32(l2_eps), F32(rms_eps), _ptr(log),
                                         _ptr(kq_scratch), _stream()))
+
+
+def gdn_wait_timeouts():
+    """Copy waits of the large-grid DeltaNet layer kernel that ran into their time limit since the library was loaded (0 in a
+    healthy run)."""
+    v = C.c_uint32(0)
+    check(load().wein_b200_gdn_wait_timeouts(C.byref(v)))
+    return v.value
 
 
 def ptr_table(tensors):

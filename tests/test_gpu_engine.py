@@ -373,7 +373,7 @@ def test_baseline_shape_batch8_k4_spec_equals_plain():
     for s in range(B):
         assert np.array_equal(outs[0][s], outs[1][s]), s
     from inferulm_b200 import ops
-    assert ops.gemm_wait_timeouts() == 0
+    assert ops.gemm_wait_timeouts() == 0 and ops.gdn_wait_timeouts() == 0
     del w
     torch.cuda.empty_cache()
 
@@ -402,7 +402,7 @@ def test_greedy_spec_equals_plain_above_32_rows(B, k):
     for s in range(B):
         assert np.array_equal(outs[0][s], outs[1][s]), s
     from inferulm_b200 import ops
-    assert ops.gemm_wait_timeouts() == 0
+    assert ops.gemm_wait_timeouts() == 0 and ops.gdn_wait_timeouts() == 0
 
 
 def test_spec_verify_with_caller_drafts_and_ragged_chains(small_weights):

@@ -338,16 +338,18 @@ def test_gdn_lite_commit_equals_snapshot(ops, state_f32):
         assert np.array_equal(got, want), trial
 
 
-@pytest.mark.parametrize("state_f32,lite", [(1, 0), (0, 1)])
-def test_gdn_layer_two_launch_path_equals_one_launch(ops, state_f32, lite):
-    """From 296 (span, v-head) pairs on and given a scratch, k-hat / q-hat are computed once per k-head by a launch of their
-    own: outputs, conv-state rows, state rows (or update records) are bit for bit those of the one-launch kernel."""
+@pytest.mark.parametrize("state_f32,lite,spans", [(1, 1, 12), (0, 1, 12), (1, 0, 12), (0, 0, 12), (1, 1, 3), (1, 1, 40), (0, 0, 40)])
+def test_gdn_layer_two_launch_path_equals_one_launch(ops, state_f32, lite, spans):
+    """Given a scratch and at least 296 (span, v-head) pairs, the per-token operands (conv + SiLU, l2 norms, k-hat / q-hat,
+    gates) are made once per span by a launch of their own and persistent CTAs stream the states through shared memory:
+    outputs, conv-state rows, state rows or update records are bit for bit those of the one-launch kernel (12 spans: more
+    items than CTAs of the test device would be needed to wrap around, so a case with 40 spans is run too)."""
     rs = np.random.default_rng(44)
     kh, vh = 16, 32
     keyd, vald = kh * 128, vh * 128
     cd = 2 * keyd + vald
     ld = cd + vald + 2 * vh
-    counts = [4, 1, 8, 3, 5, 4, 4, 2, 7, 4, 4, 6]
+    counts = ([4, 1, 8, 3, 5, 4, 4, 2, 7, 4, 4, 6] * 4)[:spans]
     n = len(counts)
     T = sum(counts)
     row_start = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.uint32)
@@ -365,7 +367,7 @@ def test_gdn_layer_two_launch_path_equals_one_launch(ops, state_f32, lite):
     state = orc.bf16_to_f32(st16).copy() if state_f32 else st16
     tabs = (dev(row_start), dev(row_count), dev(in_row), dev(out_base))
     res = []
-    for scratch in (None, torch.zeros(T * kh * 256, dtype=torch.float32, device="cuda")):
+    for scratch in (None, torch.zeros(T * vh * 388, dtype=torch.float32, device="cuda")):
         cs, st = dev(conv_state), dev(state)
         out = torch.zeros(T * vald, dtype=torch.int16, device="cuda")
         log = torch.zeros(T * vh * 264, dtype=torch.float32, device="cuda") if lite else None
@@ -378,6 +380,7 @@ def test_gdn_layer_two_launch_path_equals_one_launch(ops, state_f32, lite):
     assert np.array_equal(res[0][2], res[1][2])
     if lite:
         assert np.array_equal(res[0][3], res[1][3])
+    assert ops.gdn_wait_timeouts() == 0
 
 
 def test_snapshot_lite_entries_reject_bad_arguments_and_accept_empty_calls(ops):
