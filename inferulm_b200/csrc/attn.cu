@@ -64,21 +64,25 @@ struct AttnParams {
 template <int HD>
 __device__ __forceinline__ uint32_t tile_off(uint32_t r, uint32_t ch) { return r * (HD * 2) + ((ch ^ (r & 7)) << 4); }
 
-template <int HD, int NS>
-__global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
+// MT = m-tiles of 16 query rows a CTA reduces: with 17-32 rows per (chain, kv head) the two tiles sit in ONE CTA of 8 warps,
+// warps w and w + 4 work on the same pages -- each fetches half of a page, a 64-thread named barrier joins the pair -- so
+// the KV pages cross HBM and L2 once per chain, not once per tile (two tiles in two CTAs: 325 us against 213 us for 16 rows
+// at 8 x 32K context, 1.4x the DRAM bytes).
+template <int HD, int NS, int MT>
+__global__ void __launch_bounds__(128 * MT) attn_verify_kernel(const AttnParams P) {
     PDL_ENTRY();
     constexpr int KS = HD / 16, ND = HD / 8, CH = HD / 8;       // k-steps of QK^T, d n-tiles of PV, 16-byte chunks per row
     constexpr int KL = 4;                                        // the four warps take the segment's pages round-robin
     constexpr int PAGE_BYTES = ATT_PAGE * HD * 2;
     extern __shared__ __align__(128) unsigned char smem[];
-    // layout: Q tile [16][HD] | per warp: NS stages x (K page, V page) ; merge area aliases the stages
+    // layout: Q tile [16 * MT][HD] | per page lane: NS stages x (K page, V page) ; merge area aliases the stages
     unsigned char *q_s = smem;
-    unsigned char *stage = smem + 16 * HD * 2;
-    __shared__ int qpos_s[16];
-    __shared__ float ml_s[4][16][2];
+    unsigned char *stage = smem + 16 * MT * HD * 2;
+    __shared__ int qpos_s[16 * MT];
+    __shared__ float ml_s[4 * MT][16][2];
 
     const int lane = threadIdx.x & 31, w = threadIdx.x >> 5, g = lane >> 2, c = lane & 3;
-    const uint32_t seg = blockIdx.x, kvh = blockIdx.y, span = blockIdx.z / P.n_mtiles, mt = blockIdx.z % P.n_mtiles;
+    const uint32_t seg = blockIdx.x, kvh = blockIdx.y, span = blockIdx.z / P.n_mtiles, mt = (blockIdx.z % P.n_mtiles) * MT;   // first m-tile of this CTA
     const uint32_t group = P.q_heads / P.kv_heads;
     const uint32_t t0 = P.row_start ? P.row_start[span] : span;
     const uint32_t cnt = P.row_count ? P.row_count[span] : 1u;
@@ -94,7 +98,7 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
     if (pg0 >= pages) return;  // the combine kernel only reads the segments below ceil(pages / seg_pages)
 
     // stage Q (rows p*group + gq; padding rows zero, their position -1 masks every key)
-    for (uint32_t i = threadIdx.x; i < 16 * CH; i += 128) {
+    for (uint32_t i = threadIdx.x; i < 16 * MT * CH; i += 128 * MT) {
         uint32_t r = i / CH, ch = i % CH;
         uint4 v = make_uint4(0, 0, 0, 0);
         if (mt * 16 + r < R) {
@@ -103,11 +107,16 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
         }
         *reinterpret_cast<uint4 *>(q_s + tile_off<HD>(r, ch)) = v;
     }
-    if (threadIdx.x < 16) qpos_s[threadIdx.x] = mt * 16 + threadIdx.x < R ? (int)P.positions[t0 + (mt * 16 + threadIdx.x) / group] : -1;
+    if (threadIdx.x < 16 * MT) qpos_s[threadIdx.x] = mt * 16 + threadIdx.x < R ? (int)P.positions[t0 + (mt * 16 + threadIdx.x) / group] : -1;
     __syncthreads();
 
-    const int mi = 0, kl = w;
-    unsigned char *my_stage = stage + (size_t)w * NS * 2 * PAGE_BYTES;
+    const int mi = w >> 2, kl = w & 3;   // m-tile of this warp within the CTA, page lane
+    unsigned char *my_stage = stage + (size_t)kl * NS * 2 * PAGE_BYTES;
+    // the MT warps of a page lane meet at hardware barrier 1 + kl (barrier 0 is the CTA's)
+    auto lane_sync = [&]() {
+        if (MT == 1) __syncwarp();
+        else asm volatile("bar.sync %0, %1;" ::"r"(1 + kl), "r"(32 * MT) : "memory");
+    };
     const uint32_t q_base = smem_u32(q_s), st_base = smem_u32(my_stage);
     const uint32_t *bt = P.block_table + (size_t)seq * P.bpr;
 
@@ -115,7 +124,7 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
         uint32_t slot0 = bt[pg] * ATT_PAGE;
         uint32_t kdst = st_base + buf * 2 * PAGE_BYTES, vdst = kdst + PAGE_BYTES;
 #pragma unroll 4
-        for (uint32_t i = lane; i < ATT_PAGE * CH; i += 32) {
+        for (uint32_t i = lane + 32 * mi; i < ATT_PAGE * CH; i += 32 * MT) {
             uint32_t key = i / CH, ch = i % CH;
             size_t src = (size_t)(slot0 + key) * he + kvh * HD + ch * 8;
             uint32_t nbytes = (pg * ATT_PAGE + key) < L ? 16u : 0u;  // zero-fill rows past the sequence end
@@ -129,6 +138,7 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
     for (int i = 0; i < ND; i++) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.0f, 0.0f};
     const int pos_lo = qpos_s[mi * 16 + g], pos_hi = qpos_s[mi * 16 + g + 8];
+    const bool live = (mt + mi) * 16 < R;   // a short chain leaves the second tile's warps with copies only
 
     uint32_t pg = pg0 + kl;
     int buf = 0;
@@ -141,8 +151,9 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
         if (pg + (NS - 1) * KL < pg1) load_page(pg + (NS - 1) * KL, (buf + NS - 1) % NS);
         cp_async_commit();
         cp_async_wait<NS - 1>();
-        __syncwarp();
+        lane_sync();
         const uint32_t k_s = st_base + buf * 2 * PAGE_BYTES, v_s = k_s + PAGE_BYTES;
+        if (live) {
         // S = Q K^T for 16 keys
         float s[2][4] = {{0, 0, 0, 0}, {0, 0, 0, 0}};
 #pragma unroll
@@ -198,7 +209,8 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
             mma16816(o[2 * nd], pa[0], pa[1], pa[2], pa[3], b0, b1);
             mma16816(o[2 * nd + 1], pa[0], pa[1], pa[2], pa[3], b2, b3);
         }
-        __syncwarp();
+        }   // live
+        lane_sync();   // the stage may be refilled
         buf = (buf + 1) % NS;
     }
     cp_async_wait<0>();
@@ -208,7 +220,7 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
     }
     __syncthreads();  // every warp is done with its stages: the merge area may alias them
-    float *om = reinterpret_cast<float *>(stage);  // [4 warps][16 rows][HD + 4]
+    float *om = reinterpret_cast<float *>(stage);  // [4 * MT warps][16 rows][HD + 4]
     constexpr int OST = HD + 4;
 #pragma unroll
     for (int i = 0; i < ND; i++) {
@@ -220,17 +232,19 @@ __global__ void __launch_bounds__(128) attn_verify_kernel(const AttnParams P) {
         ml_s[w][g + 8][0] = m_run[1]; ml_s[w][g + 8][1] = l_run[1];
     }
     __syncthreads();
-    // merge the four warps in warp order and emit the segment's partial
-    for (uint32_t i = threadIdx.x; i < 16 * (HD / 4); i += 128) {
-        uint32_t rr = i / (HD / 4), d4 = (i % (HD / 4)) * 4;
-        uint32_t row = mt * 16 + rr;
+    // merge the four warps of an m-tile in warp order and emit the segment's partial
+    for (uint32_t i = threadIdx.x; i < 16 * MT * (HD / 4); i += 128 * MT) {
+        uint32_t r32 = i / (HD / 4), d4 = (i % (HD / 4)) * 4;
+        uint32_t row = mt * 16 + r32;
         if (row >= R) continue;
+        const uint32_t rr = r32 % 16, w0 = (r32 / 16) * KL;   // row within its m-tile, first warp of that tile
         float M = -INFINITY;
 #pragma unroll
-        for (int ww = 0; ww < KL; ww++) M = fmaxf(M, ml_s[ww][rr][0]);
+        for (int wi = 0; wi < KL; wi++) M = fmaxf(M, ml_s[w0 + wi][rr][0]);
         float acc[4] = {0, 0, 0, 0}, Lsum = 0.0f;
 #pragma unroll
-        for (int ww = 0; ww < KL; ww++) {
+        for (int wi = 0; wi < KL; wi++) {
+            const uint32_t ww = w0 + wi;
             float mw = ml_s[ww][rr][0];
             float f = mw == -INFINITY ? 0.0f : exp2f((mw - M) * P.scale_log2);
             Lsum += f * ml_s[ww][rr][1];
@@ -286,44 +300,60 @@ __global__ void attn_combine_kernel(const AttnParams P) {
     *reinterpret_cast<uint2 *>(P.out + oi) = make_uint2((uint32_t)r[0] | ((uint32_t)r[1] << 16), (uint32_t)r[2] | ((uint32_t)r[3] << 16));
 }
 
-template <int HD, int NS>
+template <int HD, int NS, int MT>
 static size_t attn_smem_bytes() {
-    size_t smem = 16 * HD * 2 + 4 * NS * 2 * (size_t)ATT_PAGE * HD * 2;
-    size_t merge = 16 * HD * 2 + 4 * 16 * (size_t)(HD + 4) * 4;
+    size_t smem = 16 * MT * HD * 2 + 4 * NS * 2 * (size_t)ATT_PAGE * HD * 2;
+    size_t merge = 16 * MT * HD * 2 + 4 * MT * 16 * (size_t)(HD + 4) * 4;
     return smem < merge ? merge : smem;
 }
 // The shared-memory opt-in is a per-device function attribute: one flag per device ordinal, set once (writing it twice from
 // two threads stores the same value).
-static bool g_attn_ready[6][64];
-template <int HD, int NS>
+static bool g_attn_ready[12][64];
+template <int HD, int NS, int MT>
 static int32_t attn_prepare(int which) {
+    which += 6 * (MT - 1);
     int dev = 0;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { wb_set_error("attn: cudaGetDevice failed or device ordinal >= 64"); return WB_ERR_CUDA; }
     if (g_attn_ready[which][dev]) return WB_OK;
-    const size_t smem = attn_smem_bytes<HD, NS>();
-    cudaError_t e = cudaFuncSetAttribute(attn_verify_kernel<HD, NS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    const size_t smem = attn_smem_bytes<HD, NS, MT>();
+    cudaError_t e = cudaFuncSetAttribute(attn_verify_kernel<HD, NS, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { wb_set_error("attn: cannot reserve %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); return WB_ERR_CUDA; }
     g_attn_ready[which][dev] = true;
     return WB_OK;
 }
 
+// tiles = m-tiles of 16 query rows of the longest chain (1 or 2): both sit in one CTA
 template <int HD, int NS>
-static int32_t attn_launch(const AttnParams &p, int which, cudaStream_t st) {
-    if (int32_t rc = attn_prepare<HD, NS>(which)) return rc;
+static int32_t attn_launch(const AttnParams &p, uint32_t tiles, int which, cudaStream_t st) {
     dim3 grid(p.max_segs, p.kv_heads, p.n_spans * p.n_mtiles);
-    WB_LAUNCH((attn_verify_kernel<HD, NS>), grid, 128, attn_smem_bytes<HD, NS>(), st, p);
+    if (tiles == 1) {
+        if (int32_t rc = attn_prepare<HD, NS, 1>(which)) return rc;
+        WB_LAUNCH((attn_verify_kernel<HD, NS, 1>), grid, 128, (attn_smem_bytes<HD, NS, 1>()), st, p);
+    } else {
+        if (int32_t rc = attn_prepare<HD, NS, 2>(which)) return rc;
+        WB_LAUNCH((attn_verify_kernel<HD, NS, 2>), grid, 256, (attn_smem_bytes<HD, NS, 2>()), st, p);
+    }
     WB_LAUNCH_CHECK();
-    dim3 g2(16 * p.n_mtiles, p.kv_heads, p.n_spans);
+    dim3 g2(16 * tiles, p.kv_heads, p.n_spans);
     WB_LAUNCH((attn_combine_kernel<HD>), g2, HD / 4, 0, st, p);
     WB_LAUNCH_CHECK();
     return WB_OK;
 }
 
+template <int HD>
+static int32_t attn_prepare_all(int which) {
+    int32_t rc = attn_prepare<HD, 2, 1>(which);
+    if (!rc) rc = attn_prepare<HD, 3, 1>(which + 3);
+    if (!rc) rc = attn_prepare<HD, 2, 2>(which);
+    if (!rc) rc = attn_prepare<HD, 3, 2>(which + 3);
+    return rc;
+}
+
 int32_t wb_attn_init(uint32_t head_dim) {
     switch (head_dim) {
-        case 256: { int32_t rc = attn_prepare<256, 2>(0); return rc ? rc : attn_prepare<256, 3>(3); }
-        case 128: { int32_t rc = attn_prepare<128, 2>(1); return rc ? rc : attn_prepare<128, 3>(4); }
-        case 64: { int32_t rc = attn_prepare<64, 2>(2); return rc ? rc : attn_prepare<64, 3>(5); }
+        case 256: return attn_prepare_all<256>(0);
+        case 128: return attn_prepare_all<128>(1);
+        case 64: return attn_prepare_all<64>(2);
         default: wb_set_error("attn: head_dim %u not built", head_dim); return WB_ERR_SHAPE;
     }
 }
@@ -350,7 +380,8 @@ int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, 
     AttnParams p{};
     p.seg_pages = seg_pages;
     p.max_segs = ((max_ctx + ATT_PAGE - 1) / ATT_PAGE + seg_pages - 1) / seg_pages;
-    p.n_mtiles = (max_count * group + 15) / 16;
+    const uint32_t tiles = (max_count * group + 15) / 16;   // 1 or 2, both reduced by one CTA
+    p.n_mtiles = 1;
     uint64_t need = wein_b200_attn_scratch_bytes(n_spans, kv_heads, head_dim, p.max_segs);
     if (need > scratch_bytes) { wb_set_error("attn_verify: scratch of %llu bytes needed, %llu given", (unsigned long long)need, (unsigned long long)scratch_bytes); return WB_ERR_CAPACITY; }
     p.q = (const bf16_t *)q; p.k_cache = (const bf16_t *)k_cache; p.v_cache = (const bf16_t *)v_cache; p.gate = (const bf16_t *)gate;
@@ -361,9 +392,9 @@ int32_t wb_attn_verify(const void *q, const void *k_cache, const void *v_cache, 
     p.scale_log2 = q_scale * 1.4426950408889634f;
     p.bpr = bpr; p.q_heads = q_heads; p.kv_heads = kv_heads; p.n_spans = n_spans; p.status = status;
     switch (head_dim) {
-        case 256: return deep ? attn_launch<256, 3>(p, 3, st) : attn_launch<256, 2>(p, 0, st);
-        case 128: return deep ? attn_launch<128, 3>(p, 4, st) : attn_launch<128, 2>(p, 1, st);
-        case 64: return deep ? attn_launch<64, 3>(p, 5, st) : attn_launch<64, 2>(p, 2, st);
+        case 256: return deep ? attn_launch<256, 3>(p, tiles, 3, st) : attn_launch<256, 2>(p, tiles, 0, st);
+        case 128: return deep ? attn_launch<128, 3>(p, tiles, 4, st) : attn_launch<128, 2>(p, tiles, 1, st);
+        case 64: return deep ? attn_launch<64, 3>(p, tiles, 5, st) : attn_launch<64, 2>(p, tiles, 2, st);
         default: wb_set_error("attn_verify: head_dim %u not built (64, 128, 256)", head_dim); return WB_ERR_SHAPE;
     }
 }

@@ -101,6 +101,10 @@ def test_attn_verify_batch_shape_invariance_and_gate(ops):
         # one chain alone
         one = _run_attn(ops, c, 1, cnt, 1500 + cnt, 4, spans=(c["row_start"][1:2], c["row_count"][1:2]))
         assert np.array_equal(one[cnt * n:2 * cnt * n], full[cnt * n:2 * cnt * n])
+        # a short chain next to long ones (the second m-tile of its CTA has no rows)
+        short = _run_attn(ops, c, 3, cnt, 1500 + cnt, 4, spans=(c["row_start"], np.array([cnt, 2, cnt], np.uint32)))
+        assert np.array_equal(short[:cnt * n], full[:cnt * n]) and np.array_equal(short[2 * cnt * n:], full[2 * cnt * n:])
+        assert np.array_equal(short[cnt * n:(cnt + 2) * n], full[cnt * n:(cnt + 2) * n])
         gate = rand_bf16(rs, c["q"].size, 2.0)
         gated = _run_attn(ops, c, 3, cnt, 1500 + cnt, 4, gate=gate)
         assert np.array_equal(gated, orc.sigmul(full, gate))
