@@ -35,9 +35,9 @@ WORKLOADS = {
     "c4": dict(batch=8, k=4, prompt=32768, temp=0.0, top_k=0, top_p=1.0,
                desc="same model, long context: batch 8, 32768-token paged bf16 KV (16-token pages) + f32 recurrent state, k=4"),
 }
-# ncu capture of the headline's dominant launch (wgemm_kernel, gate|up + SwiGLU, m = 4): dram__bytes_read.sum + dram__bytes_write.sum
-# per launch as recorded in the committed capture summary of that kernel and shape; null for shapes without a capture
-NCU_TRAFFIC = {("wgemm", 4): 97.6e6}
+# ncu captures of the dominant launch (gate|up + SwiGLU) per kernel and row count: dram__bytes_read.sum + dram__bytes_write.sum per
+# launch as recorded in the committed capture summaries of that kernel and shape; null for shapes without a capture
+NCU_TRAFFIC = {("wgemm", 4): 97.6e6, ("ugemm", 128): 98.8e6, ("ugemm", 40): 98.7e6}
 
 
 def peaks():

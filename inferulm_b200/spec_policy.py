@@ -96,6 +96,6 @@ class SpecPolicy:
 
 
 def batch_k(policies) -> int:
-    """The engine runs one draft length per round for the whole batch (the reference verifies chains of different lengths
-    in one forward): the batch drafts as far as its most optimistic request."""
+    """The round's shape: the batch drafts as far as its most optimistic request.  Every slot still verifies its own draft
+    length inside that round (`Engine.set_spec`), as the reference verifies chains of different lengths in one forward."""
     return max((p.k for p in policies), default=0)

@@ -67,7 +67,7 @@ def test_draft_sampling_matches_oracle(ops):
 
 
 def test_accept_greedy_bit_exact(ops):
-    """BASELINE unit: bf16 logits [4, 151936] ~ N(0,1), drafts = argmax of rows 0..2 with forced mismatch variants."""
+    """The acceptance unit of the reference's first benchmark configuration: bf16 logits [4, 151936] ~ N(0,1), drafts = argmax of rows 0..2 with forced mismatch variants."""
     rs = np.random.default_rng(0)
     B, k = 5, 3
     x = rand_bf16(rs, B * (k + 1) * V).reshape(B * (k + 1), V)

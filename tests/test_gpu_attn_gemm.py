@@ -70,7 +70,7 @@ def _run_attn(ops, c, n_spans, cnt, max_ctx, seg_pages, gate=None, spans=None):
 @pytest.mark.parametrize("ctx_lens,cnt,seg_pages", [([508], 4, 4), ([508], 4, 64), ([0, 3, 17, 300], 4, 2), ([1100, 40], 5, 4),
                                                     ([2000], 8, 16), ([15, 16, 31], 1, 1)])
 def test_attn_verify_vs_oracle(ops, ctx_lens, cnt, seg_pages):
-    """BASELINE unit shape (16 q / 4 kv heads, d = 256, 16-token pages, positions 508..511) and ragged
+    """The unit shape of the reference's first benchmark configuration (16 q / 4 kv heads, d = 256, 16-token pages, positions 508..511) and ragged
     variants: empty context, page boundaries, two m-tiles (k = 4 and 7 drafts), one or many segments."""
     rs = np.random.default_rng(len(ctx_lens) * 100 + cnt)
     c = _attn_case(rs, ctx_lens, cnt)
