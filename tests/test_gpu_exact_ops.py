@@ -350,6 +350,8 @@ def test_gdn_layer_two_launch_path_equals_one_launch(ops, state_f32, lite, spans
     cd = 2 * keyd + vald
     ld = cd + vald + 2 * vh
     counts = ([4, 1, 8, 3, 5, 4, 4, 2, 7, 4, 4, 6] * 4)[:spans]
+    if spans == 40:
+        counts[5] = counts[17] = counts[39] = 0   # refused slots: spans without rows, among them the last item of a CTA
     n = len(counts)
     T = sum(counts)
     row_start = np.concatenate([[0], np.cumsum(counts)[:-1]]).astype(np.uint32)
