@@ -367,8 +367,9 @@ ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ 
     } else {
         // k split over the cluster: output column c of the tile belongs to CTA c / cw.  Once every CTA of the cluster has left its
         // main loop (its ring is idle: every copy has landed and every MMA has read it), each CTA sends the columns of its f32
-        // partial straight from tensor memory into the owner's ring, [source rank][token][cw] (gate | up: 2 cw); after a second
-        // barrier the owner adds the partials of its columns in rank order from its own shared memory.
+        // partial straight from tensor memory into the owner's ring, [source rank][4-column piece][token] (gate | up: 2 cw
+        // columns): a warp's 32 tokens of one piece are 512 contiguous bytes of the owner's memory.  After a second barrier
+        // the owner adds the partials of its columns in rank order from its own shared memory.
         const uint32_t cw = P.cw, roww = P.swiglu ? 2 * cw : cw;   // floats per staged token row
         float *stg = reinterpret_cast<float *>(ring);
         tc_fence_before();
@@ -389,7 +390,7 @@ ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ 
                             const uint32_t col = c0 + h * 4;                            // tile column of this 4-wide piece
                             const uint32_t oc = P.swiglu && col >= NT / 2 ? col - NT / 2 : col;   // the output column it feeds
                             const uint32_t owner = oc / cw, off = oc - owner * cw + (P.swiglu && col >= NT / 2 ? cw : 0u);
-                            const uint32_t a = smem_u32(&stg[((size_t)rank * P.m + tok) * roww + off]);
+                            const uint32_t a = smem_u32(&stg[(((size_t)rank * (roww / 4) + off / 4) * P.m + tok) * 4]);
                             st_remote_f32x4(a, owner, __uint_as_float(v[h * 4]), __uint_as_float(v[h * 4 + 1]), __uint_as_float(v[h * 4 + 2]), __uint_as_float(v[h * 4 + 3]));
                         }
                     }
@@ -402,14 +403,15 @@ ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ 
         if (!abort_s && oc_hi > oc_lo) {   // (a peer that gave up sends nothing: the timeout counter flags the result)
             const uint32_t chunks = (oc_hi - oc_lo + 7) / 8;
             for (uint32_t it = tid; it < P.m * chunks; it += UG_THREADS) {
-                const uint32_t tok = it / chunks, ch = it - tok * chunks;
+                const uint32_t ch = it / P.m, tok = it - ch * P.m;   // consecutive threads: consecutive tokens of one piece
                 float a[8] = {0, 0, 0, 0, 0, 0, 0, 0}, b[8] = {0, 0, 0, 0, 0, 0, 0, 0};
                 for (uint32_t rk = 0; rk < P.ksplit; rk++) {
-                    const float *src = &stg[((size_t)rk * P.m + tok) * roww + ch * 8];
-                    const float4 x0 = *reinterpret_cast<const float4 *>(src), x1 = *reinterpret_cast<const float4 *>(src + 4);
+                    const float *src = &stg[(((size_t)rk * (roww / 4) + ch * 2) * P.m + tok) * 4];   // pieces 2 ch and 2 ch + 1
+                    const float4 x0 = *reinterpret_cast<const float4 *>(src), x1 = *reinterpret_cast<const float4 *>(src + (size_t)P.m * 4);
                     a[0] += x0.x; a[1] += x0.y; a[2] += x0.z; a[3] += x0.w; a[4] += x1.x; a[5] += x1.y; a[6] += x1.z; a[7] += x1.w;
                     if (P.swiglu) {
-                        const float4 y0 = *reinterpret_cast<const float4 *>(src + cw), y1 = *reinterpret_cast<const float4 *>(src + cw + 4);
+                        const float *up = src + (size_t)(cw / 4) * P.m * 4;
+                        const float4 y0 = *reinterpret_cast<const float4 *>(up), y1 = *reinterpret_cast<const float4 *>(up + (size_t)P.m * 4);
                         b[0] += y0.x; b[1] += y0.y; b[2] += y0.z; b[3] += y0.w; b[4] += y1.x; b[5] += y1.y; b[6] += y1.z; b[7] += y1.w;
                     }
                 }
