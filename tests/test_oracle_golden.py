@@ -82,7 +82,7 @@ def test_deltanet_state_drift_known_answer():
     """The reference publishes, for the seeds of its drift test
     (crates/wein-kernel/tests/ops_i1.rs:324-334), bf16-state vs f32-state
     output drift rel2 1.26e-3, peak-normalised 4.2e-3, 6.5 % of words
-    different (bench-reports/BASELINE.md:109).  Both oracle state modes must
+    different (line 109 of the baseline report under its bench-reports/).  Both oracle state modes must
     reproduce those figures."""
     kh, vh, kd, vd, tokens = 1, 2, 128, 128, 256
     q = orc.vec_bf16(0xA5A5, tokens * kh * kd, 2.0)
