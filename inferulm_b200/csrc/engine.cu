@@ -342,8 +342,8 @@ extern "C" int32_t wein_b200_engine_create(const wein_b200_model_cfg *cfg, const
         const uint32_t want = (e->bpr + segs - 1) / segs;
         e->seg_pages = 4;
         while (e->seg_pages < want && e->seg_pages < 128) e->seg_pages *= 2;   // 256 pages: faster alone, slower in a round (1.7 waves)
-        if (want >= 64) {
-            // long contexts: a segment CTA fills an SM (one CTA per SM at these shared-memory sizes), so what counts is that the
+        if (want >= 32) {
+            // longer contexts: a segment CTA fills an SM (one CTA per SM at these shared-memory sizes), so what counts is that the
             // grid is a whole number of waves: the segment length (a multiple of 8 pages) with the least waves x (pages + the
             // fixed cost of a CTA, about 6 pages' worth).  8 chains x 32K tokens: 56 pages = 37 segments x 32 = 8 full waves on 148 SMs.
             uint64_t best = ~0ull;
