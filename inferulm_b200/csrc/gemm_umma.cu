@@ -73,7 +73,8 @@ struct UgParams {
     uint32_t cw;                    // k split: output columns of a tile owned by each CTA of the cluster (a multiple of 8)
     uint32_t stages;                // ring depth of each stream
     uint32_t swiglu, half_n;        // swiglu: output [m, half_n], tile columns [0, nt/2) gate, [nt/2, nt) the matching up rows
-    uint32_t tmem_cols;             // power of two >= UG_NS * passes * nt
+    uint32_t acc_stride;            // tensor-memory columns between the streams' accumulators: power of two >= passes * nt
+    uint32_t tmem_cols;             // UG_NS * acc_stride
     uint32_t vec_ok;                // C rows may be written in 16-byte pieces (C 16-byte aligned, ldc a multiple of 8)
 };
 
@@ -191,7 +192,7 @@ ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ 
     // k blocks of this CTA: nkb split into ksplit contiguous parts, the first `rem` parts one block longer
     const uint32_t per = P.nkb / P.ksplit, rem = P.nkb % P.ksplit;
     const uint32_t kb_lo = rank * per + min(rank, rem), my_kb = per + (rank < rem ? 1u : 0u);
-    const uint32_t acc_cols = P.passes * NT;                 // tensor-memory columns of one stream's accumulator(s)
+    const uint32_t acc_cols = P.acc_stride;                  // tensor-memory columns between the streams' accumulators
 
     if (tid == 0) {
         for (uint32_t j = 0; j < UG_NS; j++) {
@@ -315,13 +316,33 @@ ugemm_kernel(const __grid_constant__ CUtensorMap tm_w0, const __grid_constant__ 
     };
     if (P.ksplit == 1) {
         if (go) {
-            const uint32_t c_lo = half * (ocols / 2), c_hi = c_lo + ocols / 2;   // ocols is a multiple of 32
+            // the two warps of a lane quadrant split the tile's columns at a multiple of 32 (ocols is a multiple of 16; with
+            // swiglu, where the halves must be equal, of 32)
+            const uint32_t split = P.swiglu ? ocols / 2 : (ocols + 63) / 64 * 32;
+            const uint32_t c_lo = half ? split : 0u, c_hi = half ? ocols : split;
             for (uint32_t p = 0; p < P.passes; p++) {
                 if (p * 128 + q * 32 >= P.m) break;                 // no token of this warp's quadrant in this block (warp-uniform)
                 const uint32_t tok = p * 128 + q * 32 + lane;
                 if (!P.swiglu) {
-                    // plain rows: 32 columns per step (one load per stream, one wait), 64 contiguous bytes of the C row
+                    // plain rows: 32 columns per step (one load per stream, one wait), 64 contiguous bytes of the C row; a tile
+                    // whose width is an odd multiple of 16 ends with a 16-column step
                     for (uint32_t c0 = c_lo; c0 < c_hi; c0 += 32) {
+                        if (c_hi - c0 < 32) {
+                            uint32_t v[16], w[16];
+                            acc_issue(p * NT + c0, v, w);
+                            tmem_ld_wait();
+                            acc_sum(v, w);
+                            if (tok < P.m) {
+#pragma unroll
+                                for (int h = 0; h < 2; h++) {
+                                    float o[8];
+#pragma unroll
+                                    for (int e = 0; e < 8; e++) o[e] = __uint_as_float(v[h * 8 + e]);
+                                    store8(tok, c0 + h * 8, o);
+                                }
+                            }
+                            break;
+                        }
                         uint32_t v[32], w[32];
                         if (n_acc >= 1) tmem_ld32(tq + p * NT + c0, v);
                         if (n_acc == 2) tmem_ld32(tq + acc_cols + p * NT + c0, w);
@@ -537,7 +558,7 @@ int32_t wb_tensor_map_2d(void *tm, bool f32, const void *base, uint64_t inner, u
 
 
 // Launch geometry of one chunk of mc <= 256 token rows.
-struct UgGeom { uint32_t nt, tiles, nkb, ksplit, cw, passes, x_rows, x_bytes, stages, tmem_cols; size_t smem; };
+struct UgGeom { uint32_t nt, tiles, nkb, ksplit, cw, passes, x_rows, x_bytes, stages, acc_stride, tmem_cols; size_t smem; };
 static bool ug_geometry(uint32_t mc, uint32_t n, uint32_t k, bool swiglu, const UgDevice &d, UgGeom *g) {
     const uint32_t out_cols = swiglu ? n / 2 : n;
     g->nkb = (k + UG_BK - 1) / UG_BK;
@@ -551,6 +572,18 @@ static bool ug_geometry(uint32_t mc, uint32_t n, uint32_t k, bool swiglu, const 
     const uint32_t tiles256 = (tiles128 + 1) / 2;
     g->nt = ((uint64_t)tiles256 * g->ksplit >= (uint64_t)d.sms && UG_NS * g->passes * 256 <= 512) ? 256 : 128;
     g->tiles = g->nt == 256 ? tiles256 : tiles128;
+    if (!swiglu && g->ksplit == 1) {
+        // A plain product without k split may take any tile width that is a multiple of 16: the width with the least
+        // waves x (rows of a tile + the fixed cost of a CTA, about 5 us of streaming = 215 KB of weight rows), so that 12,352
+        // rows are 129 tiles of 96 rather than 97 of 128 on 148 SMs, and 151,936 rows 731 of 208 (5 waves) rather than 594
+        // of 256 (5 waves with 2 CTAs in the last).  At least 80 rows keep the two MMA threads ahead of an SM's share of HBM.
+        const uint32_t fixed = 215u * 1024u / (k * 2u) + 1u, max_nt = UG_NS * g->passes * 256 <= 512 ? 256u : 128u;
+        uint64_t best = ~0ull;
+        for (uint32_t nt = 80; nt <= max_nt; nt += 16) {
+            const uint64_t tiles = (out_cols + nt - 1) / nt, waves = (tiles + d.sms - 1) / d.sms, cost = waves * (nt + fixed);
+            if (cost < best || (cost == best && nt == 128)) { best = cost; g->nt = nt; g->tiles = (uint32_t)tiles; }
+        }
+    }
     const uint32_t ocols = swiglu ? g->nt / 2 : g->nt;
     g->cw = ((ocols + g->ksplit - 1) / g->ksplit + 7) / 8 * 8;
     // Shared memory: one CTA per SM with as many stages as fit (measured: CTAs of half an SM with fewer stages each were slower
@@ -567,8 +600,9 @@ static bool ug_geometry(uint32_t mc, uint32_t n, uint32_t k, bool swiglu, const 
     g->smem = 1024 + (size_t)UG_NS * stages * stage + tail;
     if (g->smem < (size_t)UG_SMEM_SOLO) g->smem = UG_SMEM_SOLO;   // never two of these CTAs on one SM (see the tensor-memory claim in the kernel)
     uint32_t cols = 32;
-    while (cols < UG_NS * g->passes * g->nt) cols *= 2;
-    g->tmem_cols = cols;
+    while (cols < g->passes * g->nt) cols *= 2;
+    g->acc_stride = cols;
+    g->tmem_cols = UG_NS * cols;
     return true;
 }
 
@@ -590,7 +624,7 @@ int32_t wb_ugemm(const void *a, const void *w, void *c, uint32_t m, uint32_t n, 
         UgParams p{};
         p.C = (bf16_t *)c + (size_t)m0 * ldc;
         p.m = mc; p.n = n; p.k = k; p.ldc = ldc;
-        p.nt = g.nt; p.passes = g.passes; p.x_bytes = g.x_bytes; p.nkb = g.nkb; p.ksplit = g.ksplit; p.cw = g.cw; p.stages = g.stages; p.tmem_cols = g.tmem_cols;
+        p.acc_stride = g.acc_stride; p.nt = g.nt; p.passes = g.passes; p.x_bytes = g.x_bytes; p.nkb = g.nkb; p.ksplit = g.ksplit; p.cw = g.cw; p.stages = g.stages; p.tmem_cols = g.tmem_cols;
         p.swiglu = swiglu ? 1 : 0; p.half_n = n / 2;
         p.vec_ok = (ldc % 8 == 0 && ((uintptr_t)p.C & 15u) == 0) ? 1 : 0;
         const uint32_t wbox = swiglu ? g.nt / 2 : g.nt;
