@@ -168,7 +168,7 @@ int32_t wein_b200_attn_verify(const void *q, const void *k_cache, const void *v_
 /* GemmOp::run_wt (ops/mod.rs:3378-3449): C[m,n] = A[m,k] W[n,k]^T, bf16, f32 accumulate; k a multiple of 32, operands 16-byte
  * aligned.  Two hand-written weight-streaming kernels, no library call (the reference sends m > 1 to cuBLASLt,
  * cuda/cublaslt.rs:249-257): m <= 32 runs the register-streaming mma.sync kernel, larger m the tensor-memory kernel
- * (tcgen05.mma with the tokens as the M operand and 128 / 256 weight rows as N, tensor-map bulk copies, k split over a
+ * (tcgen05.mma with the tokens as the M operand and a tile of 80 - 256 weight rows as N, tensor-map bulk copies, k split over a
  * thread-block cluster for narrow n).  In both
  * the result of a row does not depend on the other rows of the call; the two kernels do not agree with each other bit for bit,
  * so forwards that must agree across row counts use the _tc entries (the tensor-memory kernel at every m) throughout.

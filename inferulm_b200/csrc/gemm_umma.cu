@@ -11,7 +11,7 @@
 // The product is bound by streaming W from HBM once (at most 256 flop per weight byte, the ridge is ~270).  Design:
 //  * the TOKENS are the M operand of the MMA (128 rows; only the rows up to m, rounded up to 8, are copied and kept in shared
 //    memory -- a token's result is row-local, so what the MMA reads past them only lands in accumulator rows nobody reads;
-//    a second block of 128 for m > 128) and a tile of NT = 128 or 256 WEIGHT rows is the N operand: D[128 tokens x NT] f32 lives in tensor memory.
+//    a second block of 128 for m > 128) and a tile of NT WEIGHT rows (a multiple of 16 up to 256) is the N operand: D[128 tokens x NT] f32 lives in tensor memory.
 //    Measured on B200: the thread that issues tcgen05.mma spends ~115 cycles per instruction whatever N is (16 or 128),
 //    plus ~100 per stage on barriers, so what bounds an SM's streaming rate is weight bytes per instruction: 8 KB at
 //    N = 256 against 4 KB with the weights as the M operand (which capped an SM at ~40 GB/s, below its share of HBM);
@@ -65,7 +65,7 @@ __global__ void silu_lut_kernel() {
 struct UgParams {
     bf16_t *C;
     uint32_t m, n, k, ldc;          // n = weight rows of the product (2 * inter with swiglu)
-    uint32_t nt;                    // weight rows per tile: N of the MMA (128 or 256; swiglu: nt/2 gate rows + nt/2 up rows)
+    uint32_t nt;                    // weight rows per tile: N of the MMA (a multiple of 16, 128 with swiglu or a k split; swiglu: nt/2 gate rows + nt/2 up rows)
     uint32_t passes;                // token blocks of 128 rows: 1 (m <= 128) or 2
     uint32_t x_bytes;               // bytes of the token rows a stage holds: passes == 2: 2 x 16 KB, else m rounded up to 8 rows x 128 B
     uint32_t nkb;                   // k blocks of 64 in the whole product
